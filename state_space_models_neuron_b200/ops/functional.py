@@ -1,0 +1,174 @@
+"""Public op entry points.
+
+Every function takes torch tensors.  CUDA tensors go to the hand-written sm_100a kernels in
+`ops/csrc` (through `ops/cuda_ops.py`; a missing native library is an error there, never a silent
+fallback).  CPU tensors run the plain PyTorch restatement in `ops/oracle.py`, differentiated by
+autograd, which is also what the kernel tests compare against.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from . import oracle
+
+
+def _cuda():
+    from . import cuda_ops
+    return cuda_ops
+
+
+# ---- GEMM ---------------------------------------------------------------------------------
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y = x @ weight^T (+ bias); weight is [out, in]."""
+    if x.is_cuda:
+        return _cuda().linear(x, weight, bias)
+    return F.linear(x, weight, bias)
+
+
+# ---- conv ---------------------------------------------------------------------------------
+def causal_conv1d_silu(x, weight, bias, initial_state=None):
+    """Depthwise causal conv (taps = weight.shape[-1]) + SiLU on channels-last x [B,L,C]."""
+    if x.is_cuda:
+        return _cuda().causal_conv1d_silu(x, weight, bias, initial_state)
+    return oracle.causal_conv1d_silu(x, weight, bias, initial_state)
+
+
+# ---- norms --------------------------------------------------------------------------------
+def gated_rmsnorm(y, z, weight, eps: float, group_size: Optional[int] = None):
+    if y.is_cuda:
+        return _cuda().gated_rmsnorm(y, z, weight, eps, group_size)
+    return oracle.gated_rmsnorm(y, z, weight, eps, group_size)
+
+
+def rmsnorm(x, weight, eps: float):
+    if x.is_cuda:
+        return _cuda().rmsnorm(x, weight, eps)
+    return oracle.rmsnorm(x, weight, eps)
+
+
+def add_rmsnorm(x, residual, weight, eps: float, residual_dtype=None):
+    """(residual + x) -> (normed in x.dtype, new residual).  residual may be None."""
+    if x.is_cuda:
+        return _cuda().add_rmsnorm(x, residual, weight, eps, residual_dtype)
+    rd = residual_dtype or x.dtype
+    r = x.to(rd) if residual is None else residual.to(rd) + x.to(rd)
+    return oracle.rmsnorm(r, weight, eps).to(x.dtype), r
+
+
+# ---- SSD scan -----------------------------------------------------------------------------
+def ssd_chunk_scan(x, dt_raw, A, Bm, Cm, D, dt_bias, chunk_size: int = 128,
+                   initial_state=None, return_final_state: bool = False):
+    """y = SSD(x, softplus(dt_raw + dt_bias), A, B, C) + D x.
+
+    x [B,L,H,P]; dt_raw [B,L,H]; A,D,dt_bias [H]; Bm,Cm [B,L,G,N].  Returns y (x's dtype) and, if
+    asked, the final state [B,H,P,N] in fp32.
+    """
+    if x.is_cuda:
+        return _cuda().ssd_chunk_scan(x, dt_raw, A, Bm, Cm, D, dt_bias, chunk_size,
+                                      initial_state, return_final_state)
+    dt = oracle.softplus(dt_raw.float() + dt_bias.float())
+    y, S = oracle.ssd_chunked(x, dt, A, Bm, Cm, D, chunk_size, initial_state)
+    y = y.to(x.dtype)
+    return (y, S) if return_final_state else y
+
+
+def mamba2_mixer_core(zxBCdt, conv_w, conv_b, dt_bias, A_log, D, norm_w, *, d_inner: int,
+                      n_groups: int, d_state: int, head_dim: int, eps: float,
+                      norm_group_size: Optional[int], chunk_size: int = 128,
+                      recompute: bool = False, return_final_states: bool = False):
+    """Everything between in_proj and out_proj of a Mamba-2 mixer.
+
+    zxBCdt [B, L, d_inner + (d_inner + 2 G N) + H] is split into z | xBC | dt; then
+    conv+SiLU -> softplus(dt + bias) -> SSD scan -> gated group RMSNorm.
+    The counterpart of the reference's fused driver kernels (mamba2/fused_kernel.py:251-282 fwd,
+    285-420 bwd); `recompute` chooses between its two autograd variants (fused_kernel.py:423-471):
+    keep the intermediates of the forward pass, or rebuild them from zxBCdt in backward.
+    Returns out [B,L,d_inner] and optionally (conv_state [B,C,K], ssm_state [B,H,P,N]).
+    """
+    if zxBCdt.is_cuda:
+        return _cuda().mamba2_mixer_core(zxBCdt, conv_w, conv_b, dt_bias, A_log, D, norm_w, d_inner,
+                                         n_groups, d_state, head_dim, eps, norm_group_size, chunk_size,
+                                         recompute, return_final_states)
+    Bsz, L, _ = zxBCdt.shape
+    conv_dim = d_inner + 2 * n_groups * d_state
+    H = d_inner // head_dim
+    z = zxBCdt[..., :d_inner]
+    xBC = zxBCdt[..., d_inner:d_inner + conv_dim]
+    dt_raw = zxBCdt[..., d_inner + conv_dim:]
+    K = conv_w.shape[-1]
+    act = oracle.causal_conv1d_silu(xBC, conv_w.reshape(conv_dim, K), conv_b)
+    x = act[..., :d_inner].reshape(Bsz, L, H, head_dim)
+    Bm = act[..., d_inner:d_inner + n_groups * d_state].reshape(Bsz, L, n_groups, d_state)
+    Cm = act[..., d_inner + n_groups * d_state:].reshape(Bsz, L, n_groups, d_state)
+    A = -torch.exp(A_log.float())
+    dt = oracle.softplus(dt_raw.float() + dt_bias.float())
+    y, S = oracle.ssd_chunked(x, dt, A, Bm, Cm, D, chunk_size)
+    y = y.reshape(Bsz, L, d_inner).to(zxBCdt.dtype)
+    out = oracle.gated_rmsnorm(y, z, norm_w, eps, norm_group_size)
+    if return_final_states:
+        tail = xBC[:, -K:, :] if L >= K else torch.cat(
+            [xBC.new_zeros(Bsz, K - L, conv_dim), xBC], dim=1)
+        return out, (tail.transpose(1, 2).contiguous(), S)
+    return out
+
+
+# ---- decode -------------------------------------------------------------------------------
+def ssm_decode_step(zxBCdt, conv_state, ssm_state, conv_w, conv_b, dt_bias, A_log, D, norm_w, *,
+                    d_inner: int, n_groups: int, d_state: int, head_dim: int, eps: float,
+                    norm_group_size: Optional[int]):
+    """One token through conv state roll, SSM state update and the gated norm.
+
+    zxBCdt [B, d_inner + C + H]; conv_state [B,C,K] and ssm_state [B,H,P,N] are updated in place.
+    Fuses what the reference does in three places: the decode kernel
+    (mamba2/mamba2_kernel_inference.py:26-104), softplus in torch (mamba2/mamba2_mixer.py:267) and the
+    torch gated norm (mamba2/mamba2_mixer.py:279).
+    """
+    if zxBCdt.is_cuda:
+        return _cuda().ssm_decode_step(zxBCdt, conv_state, ssm_state, conv_w, conv_b, dt_bias, A_log, D,
+                                       norm_w, d_inner, n_groups, d_state, head_dim, eps, norm_group_size)
+    conv_dim = d_inner + 2 * n_groups * d_state
+    z = zxBCdt[:, :d_inner]
+    xBC = zxBCdt[:, d_inner:d_inner + conv_dim]
+    dt_raw = zxBCdt[:, d_inner + conv_dim:]
+    A = -torch.exp(A_log.float())
+    y = oracle.decode_step(xBC, dt_raw, conv_state, ssm_state, conv_w, conv_b, dt_bias, A, D,
+                           d_inner, n_groups, d_state, head_dim)
+    return oracle.gated_rmsnorm(y.to(zxBCdt.dtype), z, norm_w, eps, norm_group_size)
+
+
+# ---- attention ----------------------------------------------------------------------------
+def attention(q, k, v, causal: bool = True):
+    """GQA flash attention; q [B,L,Hq,Dh], k/v [B,L,Hkv,Dh]."""
+    if q.is_cuda:
+        return _cuda().attention(q, k, v, causal)
+    return oracle.attention(q, k, v, causal)
+
+
+def gelu(x):
+    if x.is_cuda:
+        return _cuda().gelu(x)
+    return F.gelu(x)
+
+
+# ---- cross entropy ------------------------------------------------------------------------
+def ce_partials(logits, labels, vocab_start: int):
+    if logits.is_cuda:
+        return _cuda().ce_partials(logits, labels, vocab_start)
+    return oracle.ce_partials(logits, labels, vocab_start)
+
+
+def ce_backward(logits, labels, row_max, row_sum, grad_rows, vocab_start: int, ignore_index: int):
+    """d loss / d logits for the local vocab shard: (softmax - onehot) * grad_rows."""
+    if logits.is_cuda:
+        return _cuda().ce_backward(logits, labels, row_max, row_sum, grad_rows, vocab_start, ignore_index)
+    lf = logits.float()
+    p = torch.exp(lf - row_max[:, None]) / row_sum[:, None]
+    local = labels - vocab_start
+    inside = (local >= 0) & (local < logits.shape[-1])
+    idx = torch.where(inside, local, torch.zeros_like(local))
+    p.scatter_add_(1, idx[:, None], -inside.to(p.dtype)[:, None])
+    g = torch.where(labels != ignore_index, grad_rows.float(), torch.zeros_like(grad_rows, dtype=torch.float32))
+    return (p * g[:, None]).to(logits.dtype)

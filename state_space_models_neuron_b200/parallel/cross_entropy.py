@@ -1,0 +1,50 @@
+"""Vocabulary-parallel cross entropy.
+
+Semantics of `neuronx_distributed.parallel_layers.loss_functions.parallel_cross_entropy` as the
+reference uses it (mamba2/modeling_mamba2.py:505-510): logits are `[..., V/TP]` shards, the
+per-row maximum, the sum of exponentials and the target logit are combined across the TP group,
+the backward pass is (softmax - onehot) on the local shard.  The three reductions of the
+reference are packed into two collectives (one MAX, one SUM over a packed [sum-exp, target] pair).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from . import state as ps
+from .. import ops
+
+
+class _ParallelCrossEntropy(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, labels, vocab_start, ignore_index):
+        shape = logits.shape
+        V = shape[-1]
+        lg = logits.reshape(-1, V)
+        lb = labels.reshape(-1)
+        tp, grp = ps.get_tensor_model_parallel_size(), ps.get_tensor_model_parallel_group()
+        m, s, tgt = ops.ce_partials(lg, lb, vocab_start)
+        if tp > 1:
+            gm = m.clone()
+            dist.all_reduce(gm, op=dist.ReduceOp.MAX, group=grp)
+            packed = torch.stack([s * torch.exp(m - gm), tgt], dim=0)
+            dist.all_reduce(packed, group=grp)
+            s, tgt, m = packed[0], packed[1], gm
+        valid = lb != ignore_index
+        loss = torch.where(valid, torch.log(s) + m - tgt, torch.zeros_like(s))
+        ctx.save_for_backward(lg, lb, m, s)
+        ctx.vocab_start, ctx.ignore_index, ctx.shape = vocab_start, ignore_index, shape
+        return loss.reshape(shape[:-1])
+
+    @staticmethod
+    def backward(ctx, g):
+        lg, lb, m, s = ctx.saved_tensors
+        grad = ops.ce_backward(lg, lb, m, s, g.reshape(-1), ctx.vocab_start, ctx.ignore_index)
+        return grad.reshape(ctx.shape), None, None, None
+
+
+def parallel_cross_entropy(logits: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100) -> torch.Tensor:
+    """Per-token loss (no reduction) for vocab-sharded logits and global label ids."""
+    tp, r = ps.get_tensor_model_parallel_size(), ps.get_tensor_model_parallel_rank()
+    vocab_start = r * logits.shape[-1] if tp > 1 else 0
+    return _ParallelCrossEntropy.apply(logits, labels, vocab_start, ignore_index)
