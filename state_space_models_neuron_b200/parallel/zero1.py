@@ -1,0 +1,235 @@
+"""ZeRO-1 optimizer: optimizer state and fp32 master weights sharded over the data-parallel group.
+
+Replaces what the reference obtains from `nxd.initialize_parallel_optimizer(...)` with
+`zero_one_enabled` plus `AdamW_FP32OptimParams` (train.py:71-77,123-138; utils.py:26-33):
+  * model parameters live in one flat buffer per rank, gradients accumulate in a flat fp32 buffer
+    (`param.main_grad`, fp32 gradient accumulation across micro-steps),
+  * step = [TP all-reduce of sequence-parallel-tagged grads] -> DP reduce-scatter (average) ->
+    global grad-norm over DP x TP -> clip -> AdamW on the rank's fp32 master shard -> DP all-gather of
+    the updated low-precision parameters,
+  * with `shard=False` the same code is plain data parallelism (all-reduce, full state everywhere).
+The flat layout orders parameters as [TP-sharded | TP-replicated] x [decay | no decay] so that every
+rank's shard is a handful of homogeneous segments; the AdamW update and the norm run as one fused
+kernel per segment on GPUs (`ops/csrc/optim.cu`) and as torch ops on CPU.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Iterable, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from . import state as ps
+
+_ALIGN = 128  # elements; keeps every parameter 256-byte aligned in the bf16 buffer
+
+
+def _ceil_to(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+class Zero1Optimizer(torch.optim.Optimizer):
+    def __init__(self, param_groups: Iterable[dict], lr: float = 1e-3, betas: Tuple[float, float] = (0.9, 0.999),
+                 eps: float = 1e-8, weight_decay: float = 0.0, shard: bool = True,
+                 max_grad_norm: Optional[float] = 1.0, master_dtype: torch.dtype = torch.float32,
+                 grad_dtype: torch.dtype = torch.float32):
+        defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
+        super().__init__(param_groups, defaults)
+        self.dp_size = ps.get_data_parallel_size()
+        self.dp_rank = ps.get_data_parallel_rank()
+        self.dp_group = ps.get_data_parallel_group()
+        self.tp_size = ps.get_tensor_model_parallel_size()
+        self.tp_rank = ps.get_tensor_model_parallel_rank()
+        self.tp_group = ps.get_tensor_model_parallel_group()
+        self.shard = bool(shard) and self.dp_size > 1
+        self.max_grad_norm = max_grad_norm
+        self.master_dtype = master_dtype
+        self.grad_dtype = grad_dtype
+        self.step_count = 0
+        self.last_grad_norm: Optional[torch.Tensor] = None
+        self._build_flat_buffers()
+
+    # ------------------------------------------------------------------------------------
+    def _build_flat_buffers(self) -> None:
+        entries = []  # (sort key, group index, param)
+        seen = set()
+        for gi, g in enumerate(self.param_groups):
+            for p in g["params"]:
+                if id(p) in seen or not p.requires_grad:
+                    continue
+                seen.add(id(p))
+                replicated = not getattr(p, "tensor_model_parallel", False)
+                entries.append(((int(replicated), gi), gi, p))
+        entries.sort(key=lambda e: e[0])
+        if not entries:
+            raise ValueError("optimizer got no trainable parameters")
+        p0 = entries[0][2]
+        self.device, self.param_dtype = p0.device, p0.dtype
+        off = 0
+        self.layout: List[Tuple[torch.nn.Parameter, int, int, int, bool]] = []  # (p, start, numel, group, replicated)
+        for key, gi, p in entries:
+            if p.dtype != self.param_dtype or p.device != self.device:
+                raise ValueError("all parameters must share one dtype and device")
+            self.layout.append((p, off, p.numel(), gi, bool(key[0])))
+            off += _ceil_to(p.numel(), _ALIGN)
+        unit = _ALIGN * (self.dp_size if self.shard else 1)
+        self.total = _ceil_to(off, unit)
+        self.flat_params = torch.zeros(self.total, dtype=self.param_dtype, device=self.device)
+        self.flat_grads = torch.zeros(self.total, dtype=self.grad_dtype, device=self.device)
+        for p, start, n, gi, rep in self.layout:
+            self.flat_params[start:start + n].copy_(p.data.reshape(-1))
+            p.data = self.flat_params[start:start + n].view(p.shape)
+            p.main_grad = self.flat_grads[start:start + n].view(p.shape)
+            p.grad = None
+            p.register_post_accumulate_grad_hook(self._accumulate_hook)
+        self.shard_size = self.total // self.dp_size if self.shard else self.total
+        self.shard_start = self.shard_size * self.dp_rank if self.shard else 0
+        s, e = self.shard_start, self.shard_start + self.shard_size
+        self.master = self.flat_params[s:e].to(self.master_dtype).clone()
+        self.exp_avg = torch.zeros_like(self.master)
+        self.exp_avg_sq = torch.zeros_like(self.master)
+        self.shard_grad = torch.zeros(self.shard_size, dtype=torch.float32, device=self.device) \
+            if self.shard else None
+        # homogeneous segments of the local shard: (lo, hi, group index, replicated), shard-relative
+        segs: List[List] = []
+        for p, start, n, gi, rep in self.layout:
+            lo, hi = max(start, s), min(start + _ceil_to(n, _ALIGN), e)
+            if lo >= hi:
+                continue
+            if segs and segs[-1][1] == lo - s and segs[-1][2] == gi and segs[-1][3] == rep:
+                segs[-1][1] = hi - s
+            else:
+                segs.append([lo - s, hi - s, gi, rep])
+        self.segments = [tuple(x) for x in segs]
+        self._norm_buf = torch.zeros(1, dtype=torch.float32, device=self.device)
+
+    @staticmethod
+    def _accumulate_hook(p: torch.nn.Parameter) -> None:
+        if p.grad is not None:
+            p.main_grad.add_(p.grad.to(p.main_grad.dtype))
+            p.grad = None
+
+    # ------------------------------------------------------------------------------------
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        self.flat_grads.zero_()
+        for p, *_ in self.layout:
+            p.grad = None
+
+    def _allreduce_sequence_parallel_grads(self) -> None:
+        """Sum over the TP group the grads of TP-replicated parameters that only saw a slice of
+        the sequence (norm weights), as one flat bucket."""
+        if self.tp_size == 1:
+            return
+        tagged = [p for p, *_ in self.layout if getattr(p, "sequence_parallel_enabled", False)]
+        if not tagged:
+            return
+        bucket = torch.cat([p.main_grad.reshape(-1) for p in tagged])
+        dist.all_reduce(bucket, group=self.tp_group)
+        off = 0
+        for p in tagged:
+            p.main_grad.copy_(bucket[off:off + p.numel()].view(p.shape))
+            off += p.numel()
+
+    def _reduce_gradients(self) -> torch.Tensor:
+        """Average over DP; returns this rank's fp32 gradient shard."""
+        if self.dp_size == 1:
+            return self.flat_grads
+        if not self.shard:
+            dist.all_reduce(self.flat_grads, group=self.dp_group)
+            self.flat_grads.mul_(1.0 / self.dp_size)
+            return self.flat_grads
+        if dist.get_backend(self.dp_group) == "gloo":
+            dist.all_reduce(self.flat_grads, group=self.dp_group)
+            self.shard_grad.copy_(self.flat_grads[self.shard_start:self.shard_start + self.shard_size])
+        else:
+            dist.reduce_scatter_tensor(self.shard_grad, self.flat_grads, group=self.dp_group)
+        self.shard_grad.mul_(1.0 / self.dp_size)
+        return self.shard_grad
+
+    def _grad_norm_sq(self, g: torch.Tensor) -> torch.Tensor:
+        """Sum of squares over all distinct gradient elements of the whole model."""
+        total = self._norm_buf.zero_()
+        for lo, hi, gi, rep in self.segments:
+            if rep and self.tp_rank != 0:
+                continue
+            seg = g[lo:hi]
+            if seg.is_cuda:
+                from ..ops import cuda_ops
+                cuda_ops.sumsq_accumulate(seg, total)
+            else:
+                total += seg.float().pow(2).sum()
+        if self.shard:
+            dist.all_reduce(total, group=self.dp_group)
+        if self.tp_size > 1:
+            dist.all_reduce(total, group=self.tp_group)
+        return total
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        self._allreduce_sequence_parallel_grads()
+        g = self._reduce_gradients()
+        self.step_count += 1
+        clip = torch.ones(1, dtype=torch.float32, device=self.device)
+        if self.max_grad_norm is not None:
+            norm = torch.sqrt(self._grad_norm_sq(g))
+            self.last_grad_norm = norm
+            clip = torch.clamp(self.max_grad_norm / (norm + 1e-6), max=1.0)
+        s = self.shard_start
+        out = self.flat_params[s:s + self.shard_size]
+        for lo, hi, gi, rep in self.segments:
+            grp = self.param_groups[gi]
+            b1, b2 = grp["betas"]
+            self._adamw(self.master[lo:hi], self.exp_avg[lo:hi], self.exp_avg_sq[lo:hi], g[lo:hi], out[lo:hi],
+                        clip, grp["lr"], b1, b2, grp["eps"], grp["weight_decay"], self.step_count)
+        if self.shard:
+            dist.all_gather_into_tensor(self.flat_params, out.contiguous(), group=self.dp_group) \
+                if dist.get_backend(self.dp_group) != "gloo" else self._gloo_all_gather(out)
+        return None
+
+    def _gloo_all_gather(self, out: torch.Tensor) -> None:
+        parts = [torch.empty_like(out) for _ in range(self.dp_size)]
+        dist.all_gather(parts, out.contiguous(), group=self.dp_group)
+        self.flat_params.copy_(torch.cat(parts))
+
+    @staticmethod
+    def _adamw(master, m, v, g, out, clip, lr, b1, b2, eps, wd, step) -> None:
+        if master.is_cuda:
+            from ..ops import cuda_ops
+            cuda_ops.adamw_step(master, m, v, g, out, clip, lr, b1, b2, eps, wd, step)
+            return
+        gf = g.float() * clip
+        mf, vf, w = m.float(), v.float(), master.float()
+        mf.mul_(b1).add_(gf, alpha=1 - b1)
+        vf.mul_(b2).addcmul_(gf, gf, value=1 - b2)
+        bc1, bc2 = 1 - b1 ** step, 1 - b2 ** step
+        w.mul_(1 - lr * wd)
+        w.addcdiv_(mf / bc1, (vf / bc2).sqrt_().add_(eps), value=-lr)
+        m.copy_(mf), v.copy_(vf), master.copy_(w)
+        out.copy_(w)
+
+    # ------------------------------------------------------------------------------------
+    def state_dict(self) -> Dict:
+        """Per-DP-rank shard of the optimizer state (saved one file per DP rank under ZeRO-1)."""
+        return {
+            "step": self.step_count, "shard_start": self.shard_start, "shard_size": self.shard_size,
+            "total": self.total, "dp_size": self.dp_size if self.shard else 1,
+            "master": self.master.cpu(), "exp_avg": self.exp_avg.cpu(), "exp_avg_sq": self.exp_avg_sq.cpu(),
+            "param_groups": [{k: v for k, v in g.items() if k != "params"} for g in self.param_groups],
+        }
+
+    def load_state_dict(self, sd: Dict) -> None:
+        if sd["total"] != self.total or sd["shard_size"] != self.shard_size or sd["shard_start"] != self.shard_start:
+            raise ValueError("optimizer checkpoint was written with a different parallel layout")
+        self.step_count = int(sd["step"])
+        self.master.copy_(sd["master"])
+        self.exp_avg.copy_(sd["exp_avg"])
+        self.exp_avg_sq.copy_(sd["exp_avg_sq"])
+        for g, saved in zip(self.param_groups, sd["param_groups"]):
+            g.update(saved)
+
+    def sync_master_from_params(self) -> None:
+        """Re-seed the fp32 master shard from the model parameters (after loading a model-only
+        checkpoint)."""
+        s = self.shard_start
+        self.master.copy_(self.flat_params[s:s + self.shard_size].to(self.master_dtype))
