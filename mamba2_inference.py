@@ -1,0 +1,132 @@
+"""Decode validation and generation benchmark.
+
+Mode `check` (the reference's mamba2_inference_no_tp.py:97-133): logits of one full forward pass
+against logits produced token by token with `model.step` from an empty cache, plus prefill-then-decode
+hand-off; prints error statistics and exits non-zero if `allclose(atol 1e-3, rtol 3e-2)` fails.
+Mode `bench`: prefill a prompt through the chunked scan, decode N tokens with cached conv/SSM states,
+report decode tokens/s and p50 per-token latency (device-timed).  Works with TP > 1 under torchrun.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+
+import torch
+import torch.distributed as dist
+
+from state_space_models_neuron_b200.models import Mamba2Cache, Mamba2ForCausalLM, get_config
+from state_space_models_neuron_b200.parallel import state as ps
+from state_space_models_neuron_b200.parallel.layers import set_init_seed
+
+
+def print_stats(name, a, b, atol=1e-3, rtol=3e-2) -> bool:
+    a, b = a.float(), b.float()
+    err = (a - b).abs()
+    rel = err / (b.abs() + 1e-6)
+    ok = bool(torch.allclose(a, b, atol=atol, rtol=rtol))
+    print(f"{name}: max abs {err.max().item():.3e}  mean abs {err.mean().item():.3e}  max rel {rel.max().item():.3e}"
+          f"  mean rel {rel.mean().item():.3e}  allclose(atol={atol}, rtol={rtol})={ok}")
+    return ok
+
+
+def build(args, device):
+    dtype = torch.float32 if args.dtype == "float32" else torch.bfloat16
+    config = get_config(args.model, args.vocab_size, n_groups=args.n_groups, dtype=dtype, head_dim=args.head_dim,
+                        rmsnorm_within_groups=not args.rmsnorm_across_groups)
+    set_init_seed(args.seed)
+    if args.checkpoint_path:
+        model = Mamba2ForCausalLM.from_pretrained(args.checkpoint_path, dtype=dtype)
+    else:
+        model = Mamba2ForCausalLM(config, device=device).to(dtype)
+    return model.to(device).eval(), dtype
+
+
+@torch.no_grad()
+def check(args, device) -> bool:
+    model, dtype = build(args, device)
+    g = torch.Generator().manual_seed(args.seed)
+    ids = torch.randint(0, args.vocab_size, (args.batch, args.seq_len), generator=g).to(device)
+    full = model(input_ids=ids).logits
+    if torch.isnan(full).any() or torch.isinf(full).any():
+        print("NaN/Inf in full-forward logits")
+        return False
+    cache = Mamba2Cache(model.config, args.batch, dtype=dtype, device=device)
+    steps = [model.step(ids[:, i:i + 1], cache) for i in range(args.seq_len)]
+    step_logits = torch.cat(steps, dim=1)
+    ok = print_stats("step-by-step vs forward", step_logits, full)
+    half = (args.seq_len // 2) // 128 * 128
+    if half >= 128:
+        _, cache2 = model.prefill(ids[:, :half])
+        tail = torch.cat([model.step(ids[:, i:i + 1], cache2) for i in range(half, args.seq_len)], dim=1)
+        ok = print_stats("prefill+decode vs forward", tail, full[:, half:]) and ok
+    return ok
+
+
+@torch.no_grad()
+def bench(args, device) -> dict:
+    model, dtype = build(args, device)
+    g = torch.Generator().manual_seed(args.seed)
+    prompt = torch.randint(0, args.vocab_size, (args.batch, args.seq_len), generator=g).to(device)
+    logits, cache = model.prefill(prompt)
+    tok = logits[:, -1].argmax(-1, keepdim=True)
+    for _ in range(args.warmup):
+        tok = model.step(tok, cache).argmax(-1)
+    cuda = device.type == "cuda"
+    times = []
+    if cuda:
+        torch.cuda.synchronize()
+    import time
+    for _ in range(args.decode_tokens):
+        if cuda:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        t0 = time.perf_counter()
+        tok = model.step(tok, cache).argmax(-1)
+        if cuda:
+            e1.record()
+            e1.synchronize()
+            times.append(e0.elapsed_time(e1) / 1e3)
+        else:
+            times.append(time.perf_counter() - t0)
+    t = torch.tensor(times, dtype=torch.float64)
+    total = torch.tensor([t.sum().item()], device=device)
+    if dist.is_initialized():
+        dist.all_reduce(total, op=dist.ReduceOp.MAX)
+    res = {"metric": "decode tokens/s", "value": args.batch * args.decode_tokens / total.item(),
+           "p50_latency_ms": t.median().item() * 1e3, "batch": args.batch, "prefill": args.seq_len,
+           "decode_tokens": args.decode_tokens, "tp": ps.get_tensor_model_parallel_size(), "model": args.model}
+    if ps.is_master():
+        print(json.dumps(res))
+    return res
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--mode", default="check", choices=["check", "bench"])
+    ap.add_argument("--model", default="Mamba130M")
+    ap.add_argument("--vocab_size", type=int, default=50288)
+    ap.add_argument("--dtype", default="bfloat16", choices=["float32", "bfloat16"])
+    ap.add_argument("--batch", type=int, default=2)
+    ap.add_argument("--seq_len", type=int, default=256)
+    ap.add_argument("--decode_tokens", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--n_groups", type=int, default=1)
+    ap.add_argument("--head_dim", type=int, default=64)
+    ap.add_argument("--tp", type=int, default=1)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--rmsnorm_across_groups", action="store_true")
+    ap.add_argument("--checkpoint_path", default=None)
+    ap.add_argument("--device", default=None)
+    args = ap.parse_args(argv)
+    ps.initialize_model_parallel(args.tp)
+    device = torch.device(args.device) if args.device else (
+        torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu"))
+    if args.mode == "check":
+        ok = check(args, device)
+        sys.exit(0 if ok else 1)
+    bench(args, device)
+
+
+if __name__ == "__main__":
+    main()

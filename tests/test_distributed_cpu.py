@@ -1,0 +1,102 @@
+"""TP / SP / ZeRO-1 equivalence on gloo CPU ranks: T-rank results equal single-rank results."""
+import os
+import tempfile
+
+import pytest
+import torch
+
+from tests.dist_utils import run_ranks
+
+
+def _cfg(sp=False, hybrid=False):
+    from state_space_models_neuron_b200.models import Mamba2Config, Mamba2HybridConfig
+    kw = dict(num_heads=4, head_dim=32, vocab_size=256, hidden_size=64, state_size=32, num_hidden_layers=2,
+              n_groups=2, tie_word_embeddings=True, initializer_range=0.05, sequence_parallel_enabled=sp,
+              dtype=torch.float32)
+    if hybrid:
+        return Mamba2HybridConfig(**{**kw, "num_hidden_layers": 4}, attn_num_heads=4, attn_head_dim=16,
+                                  attn_key_value_heads=2, mlp_hidden_size=128, hybrid_attention_ratio=0.25,
+                                  hybrid_mlp_ratio=0.25, residual_in_fp32=False)
+    return Mamba2Config(**kw)
+
+
+def _reference_run(hybrid, steps, path):
+    """single process, TP=1: losses, merged params after `steps` optimizer steps."""
+    from state_space_models_neuron_b200 import parallel as nxd
+    from state_space_models_neuron_b200.models import Mamba2ForCausalLM, Mamba2HybridForCausalLM
+    from state_space_models_neuron_b200.parallel import state as ps
+    ps.initialize_model_parallel(1)
+    cfg = nxd.parallel_config(1, {"zero_one_enabled": False}, device="cpu", init_seed=7)
+    cls = Mamba2HybridForCausalLM if hybrid else Mamba2ForCausalLM
+    model = nxd.initialize_parallel_model(cfg, lambda: cls(_cfg(False, hybrid)))
+    opt = nxd.initialize_parallel_optimizer(cfg, nxd.AdamW_FP32OptimParams,
+                                            [{"params": list(model.parameters()), "weight_decay": 0.1}], lr=1e-2)
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, 256, (4, 128), generator=g)
+    losses = []
+    for _ in range(steps):
+        opt.zero_grad()
+        loss = model(input_ids=ids, labels=ids).loss
+        loss.backward()
+        opt.step()
+        losses.append(loss.item())
+    torch.save({"losses": losses, "sd": {k: v.clone() for k, v in model.state_dict().items()}, "ids": ids}, path)
+
+
+def _tp_worker(rank, world, tp, sp, zero1, hybrid, steps, ref_path, out_dir):
+    from state_space_models_neuron_b200 import parallel as nxd
+    from state_space_models_neuron_b200.models import Mamba2ForCausalLM, Mamba2HybridForCausalLM
+    from state_space_models_neuron_b200.parallel import state as ps
+    from state_space_models_neuron_b200.parallel.layout import merge_state_dicts
+    ps.initialize_model_parallel(tp)
+    cfg = nxd.parallel_config(tp, {"zero_one_enabled": zero1}, sequence_parallel=sp, device="cpu", init_seed=7)
+    cls = Mamba2HybridForCausalLM if hybrid else Mamba2ForCausalLM
+    mcfg = _cfg(sp, hybrid)
+    model = nxd.initialize_parallel_model(cfg, lambda: cls(mcfg))
+    opt = nxd.initialize_parallel_optimizer(cfg, nxd.AdamW_FP32OptimParams,
+                                            [{"params": list(model.parameters()), "weight_decay": 0.1}], lr=1e-2)
+    ref = torch.load(ref_path, weights_only=False)
+    ids = ref["ids"]
+    dp, dpr = ps.get_data_parallel_size(), ps.get_data_parallel_rank()
+    mine = ids.chunk(dp)[dpr]
+    losses = []
+    for _ in range(steps):
+        opt.zero_grad()
+        loss = model(input_ids=mine, labels=mine).loss
+        loss.backward()
+        opt.step()
+        l = loss.detach().clone() / dp
+        if dp > 1:
+            torch.distributed.all_reduce(l, group=ps.get_data_parallel_group())
+        losses.append(l.item())
+    for a, b in zip(losses, ref["losses"]):
+        assert abs(a - b) < 2e-4, (losses, ref["losses"])
+    nxd.save_checkpoint(out_dir, "t", model, opt, None, {"config": mcfg.to_dict()})
+    if rank == 0:
+        shards = [torch.load(os.path.join(out_dir, "t", "model", f"dp_rank_00_tp_rank_{r:02d}_pp_rank_00.pt"),
+                             weights_only=False) for r in range(tp)]
+        merged = merge_state_dicts(shards, mcfg)
+        for k, v in ref["sd"].items():
+            assert torch.allclose(merged[k], v, atol=2e-4, rtol=1e-3), (k, (merged[k] - v).abs().max())
+
+
+@pytest.mark.parametrize("world,tp,sp,zero1,hybrid", [
+    (2, 2, True, False, False),
+    (2, 2, False, False, False),
+    (2, 1, False, True, False),
+    (4, 2, True, True, False),
+    (2, 2, True, False, True),
+])
+def test_parallel_training_matches_single_rank(world, tp, sp, zero1, hybrid):
+    with tempfile.TemporaryDirectory() as d:
+        ref = os.path.join(d, "ref.pt")
+        _run_reference(hybrid, 3, ref)
+        run_ranks(_tp_worker, world, tp, sp, zero1, hybrid, 3, ref, os.path.join(d, "ck"))
+
+
+def _ref_entry(rank, world, hybrid, steps, path):
+    _reference_run(hybrid, steps, path)
+
+
+def _run_reference(hybrid, steps, path):
+    run_ranks(_ref_entry, 1, hybrid, steps, path)
