@@ -1,0 +1,677 @@
+// Memory-bound kernels of the Mamba-2 block for sm_100a: causal depthwise conv1d + SiLU (fwd/bwd),
+// gated group RMSNorm (fwd/bwd), residual-add + RMSNorm (fwd/bwd), GELU (fwd/bwd), vocab-shard cross
+// entropy statistics and gradient, fused AdamW and sum of squares.  All io is 16-byte vectorised bf16,
+// all arithmetic fp32.  Reference counterparts: mamba2/conv1d_grouped.py:65-194 (conv),
+// mamba2/fused_kernel.py:76-175 (gated norm), mamba2/modeling_mamba2.py:94-103 (RMSNorm).
+#include "common.cuh"
+
+namespace ssm {
+
+struct alignas(16) bf16x8 { __nv_bfloat162 v[4]; };
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  f[0] = bf16_lo(u.x); f[1] = bf16_hi(u.x); f[2] = bf16_lo(u.y); f[3] = bf16_hi(u.y);
+  f[4] = bf16_lo(u.z); f[5] = bf16_hi(u.z); f[6] = bf16_lo(u.w); f[7] = bf16_hi(u.w);
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
+  uint4 u;
+  u.x = pack_bf16(f[0], f[1]); u.y = pack_bf16(f[2], f[3]); u.z = pack_bf16(f[4], f[5]); u.w = pack_bf16(f[6], f[7]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+__device__ __forceinline__ void load8f(const float* p, float (&f)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+__device__ __forceinline__ void store8f(float* p, const float (&f)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+  #pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+  #pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// Sum over the block; every thread gets the result.  `red` holds >= 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : -INFINITY;
+  t = warp_max(t);
+  return t;
+}
+
+// =====================================================================================
+// causal depthwise conv1d (4 taps) + SiLU, channels-last
+// =====================================================================================
+constexpr int CONV_TOK = 32;   // tokens per thread
+constexpr int CONV_K = 4;
+
+// x [B, L, C] with row stride xs (elements); out row stride os.  init [B, 3, C] (tokens preceding x) or null.
+__global__ void __launch_bounds__(128)
+conv1d_silu_fwd_kernel(const __nv_bfloat16* __restrict__ x, long long xs, const __nv_bfloat16* __restrict__ w,
+                       const __nv_bfloat16* __restrict__ bias, const __nv_bfloat16* __restrict__ init,
+                       __nv_bfloat16* __restrict__ out, long long os, int L, int C) {
+  const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c0 >= C) return;
+  const int t0 = blockIdx.y * CONV_TOK;
+  const int b = blockIdx.z;
+  float wt[CONV_K][8], bs[8];
+  #pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    #pragma unroll
+    for (int k = 0; k < CONV_K; ++k) wt[k][e] = __bfloat162float(w[(c0 + e) * CONV_K + k]);
+    bs[e] = bias ? __bfloat162float(bias[c0 + e]) : 0.f;
+  }
+  const __nv_bfloat16* xb = x + (long long)b * L * xs + c0;
+  __nv_bfloat16* ob = out + (long long)b * L * os + c0;
+  float h[3][8];   // x[t-3], x[t-2], x[t-1]
+  #pragma unroll
+  for (int k = 0; k < 3; ++k) {
+    const int t = t0 - 3 + k;
+    if (t >= 0) load8(xb + (long long)t * xs, h[k]);
+    else if (init != nullptr) load8(init + ((long long)b * 3 + (t + 3)) * C + c0, h[k]);
+    else {
+      #pragma unroll
+      for (int e = 0; e < 8; ++e) h[k][e] = 0.f;
+    }
+  }
+  #pragma unroll 4
+  for (int i = 0; i < CONV_TOK; ++i) {
+    const int t = t0 + i;
+    if (t >= L) break;
+    float cur[8], o[8];
+    load8(xb + (long long)t * xs, cur);
+    #pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float pre = bs[e] + wt[0][e] * h[0][e] + wt[1][e] * h[1][e] + wt[2][e] * h[2][e] + wt[3][e] * cur[e];
+      o[e] = silu_f(pre);
+      h[0][e] = h[1][e]; h[1][e] = h[2][e]; h[2][e] = cur[e];
+    }
+    store8(ob + (long long)t * os, o);
+  }
+}
+
+// Backward.  dy for channels [0, c_split) comes from dy16 (bf16, row stride ds16); channels >= c_split from
+// dy32 (fp32, row stride ds32, indexed by channel - c_split).  dx is written with row stride dxs.
+// part [gridDim.z * gridDim.y, C, 5] receives per-tile partial sums (dw[0..3], db).
+__global__ void __launch_bounds__(128)
+conv1d_silu_bwd_kernel(const __nv_bfloat16* __restrict__ x, long long xs, const __nv_bfloat16* __restrict__ w,
+                       const __nv_bfloat16* __restrict__ bias, const __nv_bfloat16* __restrict__ dy16, long long ds16,
+                       const float* __restrict__ dy32, long long ds32, int c_split,
+                       __nv_bfloat16* __restrict__ dx, long long dxs, float* __restrict__ part, int L, int C) {
+  const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c0 >= C) return;
+  const int t0 = blockIdx.y * CONV_TOK;
+  const int b = blockIdx.z;
+  float wt[CONV_K][8], bs[8];
+  #pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    #pragma unroll
+    for (int k = 0; k < CONV_K; ++k) wt[k][e] = __bfloat162float(w[(c0 + e) * CONV_K + k]);
+    bs[e] = bias ? __bfloat162float(bias[c0 + e]) : 0.f;
+  }
+  const __nv_bfloat16* xb = x + (long long)b * L * xs + c0;
+  const bool lo = c0 < c_split;
+  float xw[3][8];                 // sliding window x[t-3], x[t-2], x[t-1]
+  float dp[CONV_K][8];            // dpre[t-3 .. t]
+  float dw[CONV_K][8], db[8];
+  #pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    db[e] = 0.f;
+    #pragma unroll
+    for (int k = 0; k < CONV_K; ++k) { dw[k][e] = 0.f; dp[k][e] = 0.f; }
+  }
+  #pragma unroll
+  for (int k = 0; k < 3; ++k) {
+    const int t = t0 - 3 + k;
+    if (t >= 0) load8(xb + (long long)t * xs, xw[k]);
+    else {
+      #pragma unroll
+      for (int e = 0; e < 8; ++e) xw[k][e] = 0.f;
+    }
+  }
+  // walk t over [t0, t0 + CONV_TOK + 3): dpre[t] is produced at step t, dx[t-3] is emitted at step t
+  for (int i = 0; i < CONV_TOK + 3; ++i) {
+    const int t = t0 + i;
+    float cur[8], g[8], d[8];
+    const bool valid = t < L;
+    if (valid) {
+      load8(xb + (long long)t * xs, cur);
+      if (lo) load8(dy16 + ((long long)b * L + t) * ds16 + c0, g);
+      else load8f(dy32 + ((long long)b * L + t) * ds32 + (c0 - c_split), g);
+    }
+    #pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float dpre = 0.f;
+      if (valid) {
+        const float pre = bs[e] + wt[0][e] * xw[0][e] + wt[1][e] * xw[1][e] + wt[2][e] * xw[2][e] + wt[3][e] * cur[e];
+        const float s = sigmoid_f(pre);
+        dpre = g[e] * s * (1.f + pre * (1.f - s));
+        if (i < CONV_TOK) {
+          dw[0][e] += xw[0][e] * dpre; dw[1][e] += xw[1][e] * dpre; dw[2][e] += xw[2][e] * dpre;
+          dw[3][e] += cur[e] * dpre; db[e] += dpre;
+        }
+      } else {
+        cur[e] = 0.f;
+      }
+      dp[0][e] = dp[1][e]; dp[1][e] = dp[2][e]; dp[2][e] = dp[3][e]; dp[3][e] = dpre;
+      // dx[t-3] = w3*dpre[t-3] + w2*dpre[t-2] + w1*dpre[t-1] + w0*dpre[t]
+      d[e] = wt[3][e] * dp[0][e] + wt[2][e] * dp[1][e] + wt[1][e] * dp[2][e] + wt[0][e] * dp[3][e];
+      xw[0][e] = xw[1][e]; xw[1][e] = xw[2][e]; xw[2][e] = cur[e];
+    }
+    const int td = t - 3;
+    if (i >= 3 && td < L) store8(dx + ((long long)b * L + td) * dxs + c0, d);
+  }
+  float* pp = part + ((long long)(blockIdx.z * gridDim.y + blockIdx.y) * C + c0) * 5;
+  #pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    pp[e * 5 + 0] = dw[0][e]; pp[e * 5 + 1] = dw[1][e]; pp[e * 5 + 2] = dw[2][e]; pp[e * 5 + 3] = dw[3][e];
+    pp[e * 5 + 4] = db[e];
+  }
+}
+
+// =====================================================================================
+// gated group RMSNorm:  out = w * h * rsqrt(mean_g(h^2) + eps),  h = y * silu(z)
+// one block per (row, group); thread handles vectors v = tid, tid + blockDim, ... of 8 elements
+// =====================================================================================
+constexpr int NORM_MAXV = 4;
+
+__global__ void __launch_bounds__(256)
+gated_rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ y, long long ys, const __nv_bfloat16* __restrict__ z,
+                         long long zs, const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out,
+                         long long os, int gs, float eps) {
+  __shared__ float red[33];
+  const long long row = blockIdx.x;
+  const int g = blockIdx.y;
+  const int nvec = gs / 8;
+  const __nv_bfloat16* yr = y + row * ys + (long long)g * gs;
+  const __nv_bfloat16* zr = z ? z + row * zs + (long long)g * gs : nullptr;
+  float h[NORM_MAXV][8];
+  float ss = 0.f;
+  #pragma unroll
+  for (int i = 0; i < NORM_MAXV; ++i) {
+    const int v = threadIdx.x + i * blockDim.x;
+    if (v < nvec) {
+      float a[8];
+      load8(yr + v * 8, a);
+      if (zr) {
+        float zz[8];
+        load8(zr + v * 8, zz);
+        #pragma unroll
+        for (int e = 0; e < 8; ++e) a[e] *= silu_f(zz[e]);
+      }
+      #pragma unroll
+      for (int e = 0; e < 8; ++e) { h[i][e] = a[e]; ss += a[e] * a[e]; }
+    }
+  }
+  const float rstd = rsqrtf(block_sum(ss, red) / gs + eps);
+  #pragma unroll
+  for (int i = 0; i < NORM_MAXV; ++i) {
+    const int v = threadIdx.x + i * blockDim.x;
+    if (v < nvec) {
+      float ww[8], o[8];
+      load8(w + (long long)g * gs + v * 8, ww);
+      #pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = ww[e] * h[i][e] * rstd;
+      store8(out + row * os + (long long)g * gs + v * 8, o);
+    }
+  }
+}
+
+// grid (row_slices, groups); each block walks rows r = blockIdx.x, blockIdx.x + gridDim.x, ...
+// dwpart [gridDim.x, d] fp32 partial sums of dout * h * rstd.
+__global__ void __launch_bounds__(256)
+gated_rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ y, long long ys, const __nv_bfloat16* __restrict__ z,
+                         long long zs, const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ dout,
+                         long long dos, __nv_bfloat16* __restrict__ dy, long long dys, __nv_bfloat16* __restrict__ dz,
+                         long long dzs, float* __restrict__ dwpart, long long rows, int d, int gs, float eps) {
+  __shared__ float red[33];
+  const int g = blockIdx.y;
+  const int nvec = gs / 8;
+  float ww[NORM_MAXV][8], dwacc[NORM_MAXV][8];
+  #pragma unroll
+  for (int i = 0; i < NORM_MAXV; ++i) {
+    const int v = threadIdx.x + i * blockDim.x;
+    #pragma unroll
+    for (int e = 0; e < 8; ++e) dwacc[i][e] = 0.f;
+    if (v < nvec) load8(w + (long long)g * gs + v * 8, ww[i]);
+  }
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const long long off = (long long)g * gs;
+    float h[NORM_MAXV][8], dn[NORM_MAXV][8];
+    float ss = 0.f, dot = 0.f;
+    #pragma unroll
+    for (int i = 0; i < NORM_MAXV; ++i) {
+      const int v = threadIdx.x + i * blockDim.x;
+      if (v < nvec) {
+        float a[8], go[8];
+        load8(y + row * ys + off + v * 8, a);
+        load8(dout + row * dos + off + v * 8, go);
+        if (z) {
+          float zz[8];
+          load8(z + row * zs + off + v * 8, zz);
+          #pragma unroll
+          for (int e = 0; e < 8; ++e) a[e] *= silu_f(zz[e]);
+        }
+        #pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          h[i][e] = a[e]; dn[i][e] = go[e] * ww[i][e];
+          ss += a[e] * a[e]; dot += dn[i][e] * a[e];
+        }
+      }
+    }
+    const float rstd = rsqrtf(block_sum(ss, red) / gs + eps);
+    const float mdot = block_sum(dot, red) * rstd / gs;     // mean(dn * n), n = h * rstd
+    #pragma unroll
+    for (int i = 0; i < NORM_MAXV; ++i) {
+      const int v = threadIdx.x + i * blockDim.x;
+      if (v < nvec) {
+        float yy[8], zz[8], oy[8], oz[8];
+        load8(y + row * ys + off + v * 8, yy);
+        if (z) load8(z + row * zs + off + v * 8, zz);
+        #pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float n = h[i][e] * rstd;
+          const float dh = rstd * (dn[i][e] - n * mdot);
+          if (z) {
+            const float s = sigmoid_f(zz[e]);
+            oy[e] = dh * zz[e] * s;
+            oz[e] = dh * yy[e] * s * (1.f + zz[e] * (1.f - s));
+          } else {
+            oy[e] = dh; oz[e] = 0.f;
+          }
+        }
+        // dw += dout * n
+        float go[8];
+        load8(dout + row * dos + off + v * 8, go);
+        #pragma unroll
+        for (int e = 0; e < 8; ++e) dwacc[i][e] += go[e] * h[i][e] * rstd;
+        store8(dy + row * dys + off + v * 8, oy);
+        if (z) store8(dz + row * dzs + off + v * 8, oz);
+      }
+    }
+  }
+  #pragma unroll
+  for (int i = 0; i < NORM_MAXV; ++i) {
+    const int v = threadIdx.x + i * blockDim.x;
+    if (v < nvec) store8f(dwpart + (long long)blockIdx.x * d + (long long)g * gs + v * 8, dwacc[i]);
+  }
+}
+
+// =====================================================================================
+// residual add + RMSNorm:  r' = r + x ;  out = w * r' * rsqrt(mean(r'^2) + eps)
+// one block per row.  Residual stream may be bf16 or fp32.
+// =====================================================================================
+template <typename RT>
+__device__ __forceinline__ void load8r(const RT* p, float (&f)[8]);
+template <> __device__ __forceinline__ void load8r<__nv_bfloat16>(const __nv_bfloat16* p, float (&f)[8]) { load8(p, f); }
+template <> __device__ __forceinline__ void load8r<float>(const float* p, float (&f)[8]) { load8f(p, f); }
+template <typename RT>
+__device__ __forceinline__ void store8r(RT* p, const float (&f)[8]);
+template <> __device__ __forceinline__ void store8r<__nv_bfloat16>(__nv_bfloat16* p, const float (&f)[8]) { store8(p, f); }
+template <> __device__ __forceinline__ void store8r<float>(float* p, const float (&f)[8]) { store8f(p, f); }
+
+template <typename RT>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const RT* __restrict__ res, const __nv_bfloat16* __restrict__ w,
+                       __nv_bfloat16* __restrict__ out, RT* __restrict__ res_out, int D, float eps) {
+  __shared__ float red[33];
+  const long long row = blockIdx.x;
+  const int nvec = D / 8;
+  float r[NORM_MAXV][8];
+  float ss = 0.f;
+  #pragma unroll
+  for (int i = 0; i < NORM_MAXV; ++i) {
+    const int v = threadIdx.x + i * blockDim.x;
+    if (v < nvec) {
+      float a[8];
+      load8(x + row * D + v * 8, a);
+      if (res) {
+        float b[8];
+        load8r<RT>(res + row * D + v * 8, b);
+        #pragma unroll
+        for (int e = 0; e < 8; ++e) a[e] += b[e];
+      }
+      if (res_out) store8r<RT>(res_out + row * D + v * 8, a);
+      #pragma unroll
+      for (int e = 0; e < 8; ++e) { r[i][e] = a[e]; ss += a[e] * a[e]; }
+    }
+  }
+  const float rstd = rsqrtf(block_sum(ss, red) / D + eps);
+  #pragma unroll
+  for (int i = 0; i < NORM_MAXV; ++i) {
+    const int v = threadIdx.x + i * blockDim.x;
+    if (v < nvec) {
+      float ww[8], o[8];
+      load8(w + v * 8, ww);
+      #pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = ww[e] * r[i][e] * rstd;
+      store8(out + row * D + v * 8, o);
+    }
+  }
+}
+
+// d_sum = d_res_out + rmsnorm_bwd(d_out);  dwpart [gridDim.x, D].  res = the summed residual r' saved by fwd.
+template <typename RT>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_bwd_kernel(const RT* __restrict__ res, const __nv_bfloat16* __restrict__ w,
+                       const __nv_bfloat16* __restrict__ dout, const RT* __restrict__ dres_out,
+                       RT* __restrict__ dsum, float* __restrict__ dwpart, long long rows, int D, float eps) {
+  __shared__ float red[33];
+  const int nvec = D / 8;
+  float ww[NORM_MAXV][8], dwacc[NORM_MAXV][8];
+  #pragma unroll
+  for (int i = 0; i < NORM_MAXV; ++i) {
+    const int v = threadIdx.x + i * blockDim.x;
+    #pragma unroll
+    for (int e = 0; e < 8; ++e) dwacc[i][e] = 0.f;
+    if (v < nvec) load8(w + v * 8, ww[i]);
+  }
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    float r[NORM_MAXV][8], go[NORM_MAXV][8];
+    float ss = 0.f, dot = 0.f;
+    #pragma unroll
+    for (int i = 0; i < NORM_MAXV; ++i) {
+      const int v = threadIdx.x + i * blockDim.x;
+      if (v < nvec) {
+        load8r<RT>(res + row * D + v * 8, r[i]);
+        load8(dout + row * D + v * 8, go[i]);
+        #pragma unroll
+        for (int e = 0; e < 8; ++e) { ss += r[i][e] * r[i][e]; dot += go[i][e] * ww[i][e] * r[i][e]; }
+      }
+    }
+    const float rstd = rsqrtf(block_sum(ss, red) / D + eps);
+    const float mdot = block_sum(dot, red) * rstd / D;
+    #pragma unroll
+    for (int i = 0; i < NORM_MAXV; ++i) {
+      const int v = threadIdx.x + i * blockDim.x;
+      if (v < nvec) {
+        float o[8];
+        if (dres_out) load8r<RT>(dres_out + row * D + v * 8, o);
+        else {
+          #pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] = 0.f;
+        }
+        #pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float n = r[i][e] * rstd;
+          o[e] += rstd * (go[i][e] * ww[i][e] - n * mdot);
+          dwacc[i][e] += go[i][e] * n;
+        }
+        store8r<RT>(dsum + row * D + v * 8, o);
+      }
+    }
+  }
+  #pragma unroll
+  for (int i = 0; i < NORM_MAXV; ++i) {
+    const int v = threadIdx.x + i * blockDim.x;
+    if (v < nvec) store8f(dwpart + (long long)blockIdx.x * D + v * 8, dwacc[i]);
+  }
+}
+
+// =====================================================================================
+// GELU (erf) forward / backward, 8 elements per thread
+// =====================================================================================
+__global__ void gelu_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, long long n8) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    float a[8];
+    load8(x + i * 8, a);
+    #pragma unroll
+    for (int e = 0; e < 8; ++e) a[e] = 0.5f * a[e] * (1.f + erff(a[e] * 0.70710678118654752f));
+    store8(y + i * 8, a);
+  }
+}
+__global__ void gelu_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
+                                __nv_bfloat16* __restrict__ dx, long long n8) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    float a[8], g[8];
+    load8(x + i * 8, a);
+    load8(dy + i * 8, g);
+    #pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float cdf = 0.5f * (1.f + erff(a[e] * 0.70710678118654752f));
+      const float pdf = 0.3989422804014327f * __expf(-0.5f * a[e] * a[e]);
+      g[e] *= cdf + a[e] * pdf;
+    }
+    store8(dx + i * 8, g);
+  }
+}
+
+// =====================================================================================
+// vocab-shard cross entropy: per row (max, sum exp(l - max), target logit), and the gradient
+// =====================================================================================
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+ce_partials_kernel(const T* __restrict__ logits, long long ld, const long long* __restrict__ labels, int V,
+                   int vocab_start, float* __restrict__ omax, float* __restrict__ osum, float* __restrict__ otgt) {
+  __shared__ float red[33];
+  const long long row = blockIdx.x;
+  const T* lr = logits + row * ld;
+  float m = -INFINITY;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) m = fmaxf(m, to_f<T>(lr[i]));
+  m = block_max(m, red);
+  float s = 0.f;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) s += __expf(to_f<T>(lr[i]) - m);
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) {
+    const long long loc = labels[row] - vocab_start;
+    omax[row] = m; osum[row] = s;
+    otgt[row] = (loc >= 0 && loc < V) ? to_f<T>(lr[loc]) : 0.f;
+  }
+}
+
+// grad[row, i] = (exp(l - gmax) / gsum - [i == label]) * g[row];  gmax/gsum are the global statistics.
+template <typename T>
+__global__ void __launch_bounds__(256)
+ce_backward_kernel(const T* __restrict__ logits, long long ld, const long long* __restrict__ labels, int V,
+                   int vocab_start, long long ignore_index, const float* __restrict__ gmax,
+                   const float* __restrict__ gsum, const float* __restrict__ grow, T* __restrict__ grad, long long gld) {
+  const long long row = blockIdx.x;
+  const long long lab = labels[row];
+  const float g = (lab == ignore_index) ? 0.f : grow[row];
+  const float m = gmax[row], inv = 1.f / gsum[row];
+  const long long loc = lab - vocab_start;
+  const T* lr = logits + row * ld;
+  T* gr = grad + row * gld;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    float p = __expf(to_f<T>(lr[i]) - m) * inv;
+    if (i == loc) p -= 1.f;
+    p *= g;
+    if constexpr (sizeof(T) == 2) gr[i] = __float2bfloat16(p); else gr[i] = p;
+  }
+}
+
+// =====================================================================================
+// AdamW on a flat fp32 master shard + low-precision copy; sum of squares
+// =====================================================================================
+template <typename GT>
+__global__ void adamw_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
+                             const GT* __restrict__ g, __nv_bfloat16* __restrict__ out16, float* __restrict__ out32,
+                             long long n, const float* __restrict__ clip, float lr, float b1, float b2, float eps,
+                             float wd, float bc1, float bc2) {
+  const float c = clip ? *clip : 1.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float gi = to_f<GT>(g[i]) * c;
+    const float mi = b1 * m[i] + (1.f - b1) * gi;
+    const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
+    float wv = master[i] * (1.f - lr * wd);
+    wv -= lr * (mi / bc1) / (sqrtf(vi / bc2) + eps);
+    m[i] = mi; v[i] = vi; master[i] = wv;
+    if (out16) out16[i] = __float2bfloat16(wv);
+    if (out32) out32[i] = wv;
+  }
+}
+
+template <typename GT>
+__global__ void sumsq_kernel(const GT* __restrict__ g, long long n, float* __restrict__ total) {
+  __shared__ float red[33];
+  float s = 0.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float x = to_f<GT>(g[i]);
+    s += x * x;
+  }
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) atomicAdd(total, s);
+}
+
+}  // namespace ssm
+
+// ------------------------------------------------------------------------------------ C API
+using namespace ssm;
+#define BF(p) reinterpret_cast<const __nv_bfloat16*>(p)
+#define BFM(p) reinterpret_cast<__nv_bfloat16*>(p)
+
+extern "C" int ssm_conv1d_silu_fwd(const void* x, long long xs, const void* w, const void* bias, const void* init,
+                                   void* out, long long os, int B, int L, int C, cudaStream_t st) {
+  if (C % 8 || xs % 8 || os % 8) return -SSM_ERR_BAD_ARG;
+  dim3 grid((C / 8 + 127) / 128, (L + CONV_TOK - 1) / CONV_TOK, B);
+  conv1d_silu_fwd_kernel<<<grid, 128, 0, st>>>(BF(x), xs, BF(w), BF(bias), BF(init), BFM(out), os, L, C);
+  return (int)cudaGetLastError();
+}
+
+// part must hold B * ceil(L / 32) * C * 5 floats.
+extern "C" int ssm_conv1d_silu_bwd(const void* x, long long xs, const void* w, const void* bias, const void* dy16,
+                                   long long ds16, const void* dy32, long long ds32, int c_split, void* dx,
+                                   long long dxs, void* part, int B, int L, int C, cudaStream_t st) {
+  if (C % 8 || xs % 8 || dxs % 8 || c_split % 8) return -SSM_ERR_BAD_ARG;
+  dim3 grid((C / 8 + 127) / 128, (L + CONV_TOK - 1) / CONV_TOK, B);
+  conv1d_silu_bwd_kernel<<<grid, 128, 0, st>>>(BF(x), xs, BF(w), BF(bias), BF(dy16), ds16,
+                                               reinterpret_cast<const float*>(dy32), ds32, c_split, BFM(dx), dxs,
+                                               reinterpret_cast<float*>(part), L, C);
+  return (int)cudaGetLastError();
+}
+extern "C" int ssm_conv_tok_tile() { return CONV_TOK; }
+
+static int norm_threads(int n) {
+  int v = n / 8;
+  int t = 32;
+  while (t < 256 && t * NORM_MAXV < v) t <<= 1;
+  if (t * NORM_MAXV < v) return -1;
+  // prefer one vector per thread when the row is short
+  while (t < 256 && t < v) t <<= 1;
+  return t;
+}
+
+extern "C" int ssm_gated_rmsnorm_fwd(const void* y, long long ys, const void* z, long long zs, const void* w,
+                                     void* out, long long os, long long rows, int d, int gs, float eps, cudaStream_t st) {
+  const int t = norm_threads(gs);
+  if (gs % 8 || d % gs || t < 0 || ys % 8 || zs % 8 || os % 8) return -SSM_ERR_BAD_ARG;
+  dim3 grid((unsigned)rows, d / gs);
+  gated_rmsnorm_fwd_kernel<<<grid, t, 0, st>>>(BF(y), ys, BF(z), zs, BF(w), BFM(out), os, gs, eps);
+  return (int)cudaGetLastError();
+}
+// dwpart must hold row_slices * d floats.
+extern "C" int ssm_gated_rmsnorm_bwd(const void* y, long long ys, const void* z, long long zs, const void* w,
+                                     const void* dout, long long dos, void* dy, long long dys, void* dz, long long dzs,
+                                     void* dwpart, int row_slices, long long rows, int d, int gs, float eps,
+                                     cudaStream_t st) {
+  const int t = norm_threads(gs);
+  if (gs % 8 || d % gs || t < 0 || ys % 8 || zs % 8 || dos % 8 || dys % 8 || dzs % 8) return -SSM_ERR_BAD_ARG;
+  dim3 grid(row_slices, d / gs);
+  gated_rmsnorm_bwd_kernel<<<grid, t, 0, st>>>(BF(y), ys, BF(z), zs, BF(w), BF(dout), dos, BFM(dy), dys, BFM(dz), dzs,
+                                               reinterpret_cast<float*>(dwpart), rows, d, gs, eps);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ssm_add_rmsnorm_fwd(const void* x, const void* res, const void* w, void* out, void* res_out,
+                                   long long rows, int D, float eps, int res_fp32, cudaStream_t st) {
+  const int t = norm_threads(D);
+  if (D % 8 || t < 0) return -SSM_ERR_BAD_ARG;
+  if (res_fp32)
+    add_rmsnorm_fwd_kernel<float><<<(unsigned)rows, t, 0, st>>>(BF(x), reinterpret_cast<const float*>(res), BF(w), BFM(out),
+                                                                reinterpret_cast<float*>(res_out), D, eps);
+  else
+    add_rmsnorm_fwd_kernel<__nv_bfloat16><<<(unsigned)rows, t, 0, st>>>(BF(x), BF(res), BF(w), BFM(out), BFM(res_out), D, eps);
+  return (int)cudaGetLastError();
+}
+extern "C" int ssm_add_rmsnorm_bwd(const void* res, const void* w, const void* dout, const void* dres_out, void* dsum,
+                                   void* dwpart, int row_slices, long long rows, int D, float eps, int res_fp32,
+                                   cudaStream_t st) {
+  const int t = norm_threads(D);
+  if (D % 8 || t < 0) return -SSM_ERR_BAD_ARG;
+  if (res_fp32)
+    add_rmsnorm_bwd_kernel<float><<<row_slices, t, 0, st>>>(reinterpret_cast<const float*>(res), BF(w), BF(dout),
+                                                            reinterpret_cast<const float*>(dres_out),
+                                                            reinterpret_cast<float*>(dsum),
+                                                            reinterpret_cast<float*>(dwpart), rows, D, eps);
+  else
+    add_rmsnorm_bwd_kernel<__nv_bfloat16><<<row_slices, t, 0, st>>>(BF(res), BF(w), BF(dout), BF(dres_out), BFM(dsum),
+                                                                    reinterpret_cast<float*>(dwpart), rows, D, eps);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ssm_gelu_fwd(const void* x, void* y, long long n, cudaStream_t st) {
+  if (n % 8) return -SSM_ERR_BAD_ARG;
+  const long long n8 = n / 8;
+  const int blocks = (int)((n8 + 255) / 256 < 148 * 16 ? (n8 + 255) / 256 : 148 * 16);
+  gelu_fwd_kernel<<<blocks, 256, 0, st>>>(BF(x), BFM(y), n8);
+  return (int)cudaGetLastError();
+}
+extern "C" int ssm_gelu_bwd(const void* x, const void* dy, void* dx, long long n, cudaStream_t st) {
+  if (n % 8) return -SSM_ERR_BAD_ARG;
+  const long long n8 = n / 8;
+  const int blocks = (int)((n8 + 255) / 256 < 148 * 16 ? (n8 + 255) / 256 : 148 * 16);
+  gelu_bwd_kernel<<<blocks, 256, 0, st>>>(BF(x), BF(dy), BFM(dx), n8);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ssm_ce_partials(const void* logits, long long ld, int is_fp32, const void* labels, long long rows, int V,
+                               int vocab_start, void* omax, void* osum, void* otgt, cudaStream_t st) {
+  auto lb = reinterpret_cast<const long long*>(labels);
+  auto a = reinterpret_cast<float*>(omax); auto b = reinterpret_cast<float*>(osum); auto c = reinterpret_cast<float*>(otgt);
+  if (is_fp32) ce_partials_kernel<float><<<(unsigned)rows, 256, 0, st>>>(reinterpret_cast<const float*>(logits), ld, lb, V, vocab_start, a, b, c);
+  else ce_partials_kernel<__nv_bfloat16><<<(unsigned)rows, 256, 0, st>>>(BF(logits), ld, lb, V, vocab_start, a, b, c);
+  return (int)cudaGetLastError();
+}
+extern "C" int ssm_ce_backward(const void* logits, long long ld, int is_fp32, const void* labels, long long rows, int V,
+                               int vocab_start, long long ignore_index, const void* gmax, const void* gsum,
+                               const void* grow, void* grad, long long gld, cudaStream_t st) {
+  auto lb = reinterpret_cast<const long long*>(labels);
+  auto a = reinterpret_cast<const float*>(gmax); auto b = reinterpret_cast<const float*>(gsum);
+  auto c = reinterpret_cast<const float*>(grow);
+  if (is_fp32) ce_backward_kernel<float><<<(unsigned)rows, 256, 0, st>>>(reinterpret_cast<const float*>(logits), ld, lb, V, vocab_start, ignore_index, a, b, c, reinterpret_cast<float*>(grad), gld);
+  else ce_backward_kernel<__nv_bfloat16><<<(unsigned)rows, 256, 0, st>>>(BF(logits), ld, lb, V, vocab_start, ignore_index, a, b, c, BFM(grad), gld);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ssm_adamw(void* master, void* m, void* v, const void* g, int g_fp32, void* out16, void* out32,
+                         long long n, const void* clip, float lr, float b1, float b2, float eps, float wd, int step,
+                         cudaStream_t st) {
+  const float bc1 = 1.f - powf(b1, (float)step), bc2 = 1.f - powf(b2, (float)step);
+  const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+  auto M = reinterpret_cast<float*>(master); auto mm = reinterpret_cast<float*>(m); auto vv = reinterpret_cast<float*>(v);
+  auto cl = reinterpret_cast<const float*>(clip);
+  if (g_fp32) adamw_kernel<float><<<blocks, 256, 0, st>>>(M, mm, vv, reinterpret_cast<const float*>(g), BFM(out16), reinterpret_cast<float*>(out32), n, cl, lr, b1, b2, eps, wd, bc1, bc2);
+  else adamw_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(M, mm, vv, BF(g), BFM(out16), reinterpret_cast<float*>(out32), n, cl, lr, b1, b2, eps, wd, bc1, bc2);
+  return (int)cudaGetLastError();
+}
+extern "C" int ssm_sumsq(const void* g, int g_fp32, long long n, void* total, cudaStream_t st) {
+  const int blocks = (int)((n + 255) / 256 < 148 * 4 ? (n + 255) / 256 : 148 * 4);
+  if (g_fp32) sumsq_kernel<float><<<blocks, 256, 0, st>>>(reinterpret_cast<const float*>(g), n, reinterpret_cast<float*>(total));
+  else sumsq_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(BF(g), n, reinterpret_cast<float*>(total));
+  return (int)cudaGetLastError();
+}

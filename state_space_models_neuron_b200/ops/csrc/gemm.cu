@@ -1,0 +1,318 @@
+// bf16 GEMM for sm_100a: TMA -> 128B-swizzled shared memory -> tcgen05.mma with fp32 accumulators in
+// TMEM -> epilogue.  Persistent, warp-specialised:
+//     warp 0      TMA producer (one lane)            ring of STAGES {A,B} k-blocks, full/empty mbarriers
+//     warp 1      TMEM allocator + MMA issuer (lane 0), two accumulator buffers (2 x BN columns)
+//     warps 2..5  epilogue: tcgen05.ld -> (+bias, GELU) -> bf16 -> swizzled smem -> TMA store,
+//                 or fp32 direct store / fp32 red.add (gradient accumulation)
+// C[M,N] = A * B with A given as [M,K] row-major ("K-major") or [K,M] row-major ("MN-major") and B as
+// [N,K] row-major (K-major) or [K,N] row-major (MN-major); the MN-major forms serve the transposed products
+// of the backward pass (dX = dY W, dW = dY^T X) without any explicit transpose.
+// This is the GEMM behind every Linear layer (the reference leaves those to the XLA compiler:
+// mamba2/mamba2_mixer.py:228,233; mamba2/modeling_mamba2.py:498).
+#include "common.cuh"
+
+namespace ssm {
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BK = 64;
+constexpr int GEMM_THREADS = 192;
+constexpr int EPI_BLOCK_COLS = 64;                       // bf16 columns per TMA store block (128 bytes)
+constexpr int EPI_BUF_BYTES = GEMM_BM * EPI_BLOCK_COLS * 2;  // 16 KiB
+
+struct GemmParams {
+  int M, N, K;
+  int a_mn, b_mn;        // operand majorness
+  int mode;              // 0: bf16 via TMA store, 1: fp32 store, 2: fp32 accumulate (red.add)
+  int act;               // 0 none, 1 GELU (mode 0 only)
+  const __nv_bfloat16* bias;  // [N] or null (mode 0 only)
+  float* c32;            // modes 1, 2
+  long long ldc32;
+  int* status;
+  int tiles_m, tiles_n;
+};
+
+template <int BN, int STAGES>
+struct GemmSmem {
+  static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;   // 16 KiB
+  static constexpr int B_BYTES = BN * GEMM_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int EPI_OFF = STAGES * STAGE_BYTES;
+  static constexpr int BAR_OFF = EPI_OFF + 2 * EPI_BUF_BYTES;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;      // barriers + alignment slack
+};
+
+__device__ __forceinline__ float gelu_f(float x) {
+  return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                  const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
+  using L = GemmSmem<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int kblocks = (p.K + GEMM_BK - 1) / GEMM_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], 4); }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+    if (p.mode == 0) tma_prefetch_desc(&tmap_c);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 2 * BN); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      int armed[STAGES];
+      #pragma unroll
+      for (int s = 0; s < STAGES; ++s) armed[s] = -1;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % p.tiles_m) * GEMM_BM;
+        const int n0 = (tile / p.tiles_m) * BN;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status)) { ok = false; break; }
+          uint8_t* sa = smem + stage * L::STAGE_BYTES;
+          uint8_t* sb = sa + L::A_BYTES;
+          mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
+          armed[stage] = (int)phase;
+          const int k0 = kb * GEMM_BK;
+          if (!p.a_mn) {
+            tma_load_2d(sa, &tmap_a, k0, m0, &full_bar[stage]);                 // box {64 k, 128 m}
+          } else {
+            tma_load_2d(sa, &tmap_a, m0, k0, &full_bar[stage]);                 // box {64 m, 64 k} x 2
+            tma_load_2d(sa + 8192, &tmap_a, m0 + 64, k0, &full_bar[stage]);
+          }
+          if (!p.b_mn) {
+            tma_load_2d(sb, &tmap_b, k0, n0, &full_bar[stage]);                 // box {64 k, BN n}
+          } else {
+            #pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(sb + j * 8192, &tmap_b, n0 + 64 * j, k0, &full_bar[stage]);  // box {64 n, 64 k}
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        // error path: let copies that are still in flight land before the CTA's shared memory goes away
+        #pragma unroll
+        for (int s = 0; s < STAGES; ++s)
+          if (armed[s] >= 0) mbar_wait(&full_bar[s], (uint32_t)armed[s], nullptr);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(GEMM_BM, BN, p.a_mn, p.b_mn);
+      const uint32_t a_step = p.a_mn ? (16 * 128) >> 4 : 32 >> 4;  // descriptor start-address step per UMMA_K=16
+      const uint32_t b_step = p.b_mn ? (16 * 128) >> 4 : 32 >> 4;
+      const uint32_t a_lbo = p.a_mn ? 8192u : 16u, b_lbo = p.b_mn ? 8192u : 16u;
+      int stage = 0; uint32_t phase = 0;
+      int acc = 0; uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, p.status)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, p.status)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * L::STAGE_BYTES);
+          const uint32_t sb = sa + L::A_BYTES;
+          const uint64_t da = make_smem_desc_sw128(sa, a_lbo, 1024);
+          const uint64_t db = make_smem_desc_sw128(sb, b_lbo, 1024);
+          #pragma unroll
+          for (int kk = 0; kk < GEMM_BK / 16; ++kk)
+            umma_bf16(d_tmem, da + (uint64_t)(kk * a_step), db + (uint64_t)(kk * b_step), idesc, (kb | kk) != 0);
+          umma_commit(&empty_bar[stage]);          // frees the smem stage once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(&tfull_bar[acc]);      // accumulator complete
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;                        // TMEM lane quarter this warp may access
+    const int epi_tid = threadIdx.x - 64;          // 0..127
+    const int row = q * 32 + lane;                 // row of the tile held by this thread
+    uint8_t* epi_buf = smem + L::EPI_OFF;
+    int acc = 0; uint32_t acc_phase = 0;
+    bool ok = true;
+    int stores_issued = 0;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int m0 = (tile % p.tiles_m) * GEMM_BM;
+      const int n0 = (tile / p.tiles_m) * BN;
+      if (!mbar_wait(&tfull_bar[acc], acc_phase, p.status)) { ok = false; }
+      {
+        // the four epilogue warps must agree on the outcome before they meet at named barriers
+        uint32_t mine = ok ? 1u : 0u, all;
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p, q;\n\t"
+            "setp.ne.u32 p, %1, 0;\n\t"
+            "bar.red.and.pred q, 1, 128, p;\n\t"
+            "selp.u32 %0, 1, 0, q;\n\t"
+            "}\n"
+            : "=r"(all) : "r"(mine) : "memory");
+        ok = all != 0;
+      }
+      tc_fence_after_sync();
+      if (ok) {
+        #pragma unroll 1
+        for (int j = 0; j < BN / EPI_BLOCK_COLS; ++j) {
+          const int nb = n0 + j * EPI_BLOCK_COLS;
+          if (nb >= p.N) break;
+          uint32_t v[2][32];
+          tmem_ld32(tmem_addr(tmem_base, q * 32, acc * BN + j * 64), v[0]);
+          tmem_ld32(tmem_addr(tmem_base, q * 32, acc * BN + j * 64 + 32), v[1]);
+          tmem_ld_wait();
+          if (p.mode == 0) {
+            uint8_t* buf = epi_buf + (stores_issued & 1) * EPI_BUF_BYTES;
+            if (epi_tid == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            #pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              #pragma unroll
+              for (int c = 0; c < 4; ++c) {           // 16-byte chunk = 8 bf16
+                float f[8];
+                #pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  float x = __uint_as_float(v[h][c * 8 + e]);
+                  const int col = nb + h * 32 + c * 8 + e;
+                  if (p.bias != nullptr && col < p.N) x += __bfloat162float(p.bias[col]);
+                  if (p.act == 1) x = gelu_f(x);
+                  f[e] = x;
+                }
+                uint4 o;
+                o.x = pack_bf16(f[0], f[1]); o.y = pack_bf16(f[2], f[3]);
+                o.z = pack_bf16(f[4], f[5]); o.w = pack_bf16(f[6], f[7]);
+                *reinterpret_cast<uint4*>(buf + sw128_offset(row, h * 4 + c)) = o;
+              }
+            }
+            fence_proxy_async_smem();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (epi_tid == 0) { tma_store_2d(&tmap_c, buf, nb, m0); tma_store_commit(); }
+            ++stores_issued;
+          } else {
+            const int r = m0 + row;
+            if (r < p.M) {
+              float* dst = p.c32 + (long long)r * p.ldc32 + nb;
+              #pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                #pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                  const int col = nb + h * 32 + c * 4;
+                  float4 o = make_float4(__uint_as_float(v[h][c * 4]), __uint_as_float(v[h][c * 4 + 1]),
+                                         __uint_as_float(v[h][c * 4 + 2]), __uint_as_float(v[h][c * 4 + 3]));
+                  float* d4 = dst + h * 32 + c * 4;
+                  if (col + 3 < p.N && ((reinterpret_cast<uintptr_t>(d4) & 15) == 0)) {
+                    if (p.mode == 1) *reinterpret_cast<float4*>(d4) = o;
+                    else asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(d4), "f"(o.x), "f"(o.y),
+                                      "f"(o.z), "f"(o.w) : "memory");
+                  } else {
+                    const float e4[4] = {o.x, o.y, o.z, o.w};
+                    for (int e = 0; e < 4; ++e)
+                      if (col + e < p.N) { if (p.mode == 1) d4[e] = e4[e]; else atomicAdd(d4 + e, e4[e]); }
+                  }
+                }
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+    if (epi_tid == 0) tma_store_wait_all();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
+}
+
+// ------------------------------------------------------------------------------------ host
+static int g_num_sms = 0;
+
+template <int BN, int STAGES>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, GemmParams p,
+                       cudaStream_t stream) {
+  using L = GemmSmem<BN, STAGES>;
+  static bool configured = false;
+  auto kern = gemm_bf16_tcgen05<BN, STAGES>;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  p.tiles_m = (p.M + GEMM_BM - 1) / GEMM_BM;
+  p.tiles_n = (p.N + BN - 1) / BN;
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < g_num_sms ? tiles : g_num_sms;
+  kern<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(ta, tb, tc, p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace ssm
+
+// C[M,N] = A * B.  a_mn = 0: A is [M,K] with row stride lda; a_mn = 1: A is [K,M] with row stride lda.
+// b_mn = 0: B is [N,K] with row stride ldb; b_mn = 1: B is [K,N] with row stride ldb.
+// mode 0: C bf16 [M, ldc] (ldc * 2 bytes must be a multiple of 16); 1: C fp32 store; 2: C fp32 += .
+// All leading dimensions in elements; operand bases 16-byte aligned, operand row strides multiples of 8.
+extern "C" int ssm_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                             long long ldb, long long ldc, int a_mn, int b_mn, int mode, const void* bias, int act,
+                             int* status, cudaStream_t stream) {
+  using namespace ssm;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
+    return -SSM_ERR_BAD_ARG;
+  if (mode == 0 && ((ldc % 8) || (reinterpret_cast<uintptr_t>(C) & 15))) return -SSM_ERR_BAD_ARG;
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const bool wide = N > 128;
+  const int BN = wide ? 256 : 128;
+  CUtensorMap ta, tb, tc;
+  int r;
+  if (!a_mn) r = make_tmap_2d_bf16(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, 64, 128);
+  else       r = make_tmap_2d_bf16(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, 64, 64);
+  if (r) return -100 - r;
+  if (!b_mn) r = make_tmap_2d_bf16(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, 64, BN);
+  else       r = make_tmap_2d_bf16(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, 64);
+  if (r) return -200 - r;
+  if (mode == 0) {
+    r = make_tmap_2d_bf16(&tc, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc * 2, 64, 128);
+    if (r) return -300 - r;
+  } else {
+    tc = ta;
+  }
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.a_mn = a_mn; p.b_mn = b_mn; p.mode = mode; p.act = act;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.c32 = mode == 0 ? nullptr : reinterpret_cast<float*>(C);
+  p.ldc32 = ldc; p.status = status; p.tiles_m = 0; p.tiles_n = 0;
+  return wide ? launch_gemm<256, 4>(ta, tb, tc, p, stream) : launch_gemm<128, 6>(ta, tb, tc, p, stream);
+}

@@ -1,0 +1,633 @@
+"""Autograd wrappers around the native sm_100a kernels (GPU path of `ops.functional`).
+
+Tensors are passed to the C ABI as raw device pointers on the current CUDA stream.  The kernels
+report asynchronous failures (a bounded wait that ran out) through a device status word; `check_status()`
+reads it (this synchronises) and raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import native
+
+_c = ctypes
+_status = {}
+_launches = [0]
+
+
+def launch_count() -> int:
+    """Number of native kernel launches issued by this process so far."""
+    return _launches[0]
+
+
+def _lib():
+    return native.lib()
+
+
+def _p(t: Optional[torch.Tensor]):
+    return _c.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _st():
+    return _c.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ll(v):
+    return _c.c_longlong(int(v))
+
+
+def status_tensor(device=None) -> torch.Tensor:
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if device not in _status:
+        _status[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[device]
+
+
+def check_status() -> None:
+    for dev, t in _status.items():
+        code = int(t.item())
+        if code != 0:
+            t.zero_()
+            raise RuntimeError(f"native kernel reported status {code} on {dev} "
+                               "(1: mbarrier wait timed out, 2: flag wait timed out, 3: bad argument)")
+
+
+def _run(name: str, *args):
+    fn = getattr(_lib(), name)
+    fn.restype = _c.c_int
+    code = fn(*args)
+    _launches[0] += 1
+    if code != 0:
+        raise RuntimeError(f"{name} failed with code {code} (negative: argument check, positive: cudaError_t)")
+
+
+def _require_bf16(*ts):
+    for t in ts:
+        if t is not None and t.dtype != torch.bfloat16:
+            raise TypeError(f"GPU kernels take bfloat16 activations/weights, got {t.dtype}")
+
+
+def _ceil8(n: int) -> int:
+    return (n + 7) // 8 * 8
+
+
+# ======================================================================================
+# GEMM
+# ======================================================================================
+def _as_operand(t: torch.Tensor) -> torch.Tensor:
+    """2D, unit inner stride, row stride % 8 == 0, 16-byte aligned base (TMA requirements)."""
+    if t.dim() != 2:
+        raise ValueError("GEMM operands are 2D")
+    if t.stride(1) != 1 or t.stride(0) % 8 or t.data_ptr() % 16:
+        cols = _ceil8(t.shape[1])
+        buf = torch.zeros(t.shape[0], cols, dtype=t.dtype, device=t.device) if cols != t.shape[1] else \
+            torch.empty(t.shape[0], cols, dtype=t.dtype, device=t.device)
+        buf[:, :t.shape[1]].copy_(t)
+        return buf[:, :t.shape[1]]
+    return t
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, a_mn: bool = False, b_mn: bool = False, out: Optional[torch.Tensor] = None,
+         out_dtype=torch.bfloat16, accumulate: bool = False, bias: Optional[torch.Tensor] = None,
+         gelu: bool = False) -> torch.Tensor:
+    """C[M,N] = A B on tcgen05.  a is [M,K] (or [K,M] when a_mn), b is [N,K] (or [K,N] when b_mn).
+    out: bf16 (fresh, row stride padded to 8) or fp32 (`accumulate` adds into `out`)."""
+    _require_bf16(a, b, bias)
+    a, b = _as_operand(a), _as_operand(b)
+    M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
+    N, Kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
+    if K != Kb:
+        raise ValueError(f"GEMM inner dimensions differ: {K} vs {Kb}")
+    if out is None:
+        if out_dtype == torch.bfloat16:
+            out = torch.empty(M, _ceil8(N), dtype=torch.bfloat16, device=a.device)[:, :N]
+        else:
+            out = torch.empty(M, N, dtype=torch.float32, device=a.device)
+    if out.dtype == torch.bfloat16:
+        mode = 0
+        if out.stride(1) != 1 or out.stride(0) % 8 or out.data_ptr() % 16:
+            raise ValueError("bf16 GEMM output needs unit inner stride, row stride % 8 == 0, 16-byte base")
+    else:
+        mode = 2 if accumulate else 1
+        if out.stride(1) != 1:
+            raise ValueError("fp32 GEMM output needs unit inner stride")
+    _run("ssm_gemm_bf16", _p(a), _p(b), _p(out), M, N, K, _ll(a.stride(0)), _ll(b.stride(0)), _ll(out.stride(0)),
+         int(a_mn), int(b_mn), mode, _p(bias), int(gelu), _p(status_tensor(a.device)), _st())
+    return out
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias):
+        K = x.shape[-1]
+        x2 = x.reshape(-1, K)
+        y = gemm(x2, w, bias=bias)
+        ctx.save_for_backward(x2, w)
+        ctx.has_bias = bias is not None
+        ctx.xshape = x.shape
+        return y.reshape(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        N = w.shape[0]
+        dy2 = dy.reshape(-1, N)
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, w, b_mn=True).reshape(ctx.xshape)          # dX = dY W
+        if ctx.needs_input_grad[1]:
+            mg = getattr(w, "main_grad", None)
+            if mg is not None and mg.dtype == torch.float32:
+                gemm(dy2, x2, a_mn=True, b_mn=True, out=mg, accumulate=True)   # main_grad += dY^T X
+            else:
+                dw = gemm(dy2, x2, a_mn=True, b_mn=True)
+                if not dw.is_contiguous():
+                    dw = dw.contiguous()
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.float().sum(0).to(dy.dtype)
+        return dx, dw, db
+
+
+def linear(x, w, bias=None):
+    _require_bf16(x, w)
+    return _Linear.apply(x, w, bias)
+
+
+# ======================================================================================
+# conv
+# ======================================================================================
+def _conv_fwd(xBC, w2, bias, init, out=None):
+    B, L, C = xBC.shape
+    assert xBC.stride(2) == 1 and xBC.stride(0) == L * xBC.stride(1)
+    if out is None:
+        out = torch.empty(B, L, C, dtype=xBC.dtype, device=xBC.device)
+    _run("ssm_conv1d_silu_fwd", _p(xBC), _ll(xBC.stride(1)), _p(w2), _p(bias), _p(init), _p(out), _ll(out.stride(1)),
+         B, L, C, _st())
+    return out
+
+
+def _conv_bwd(xBC, w2, bias, dy16, dy32, c_split, dx_out):
+    """dx_out [B,L,C] view (row stride may exceed C); returns (dw [C,K], db [C]) fp32."""
+    B, L, C = xBC.shape
+    tile = _lib().ssm_conv_tok_tile()
+    ntile = (L + tile - 1) // tile
+    part = torch.empty(B * ntile, C, 5, dtype=torch.float32, device=xBC.device)
+    _run("ssm_conv1d_silu_bwd", _p(xBC), _ll(xBC.stride(1)), _p(w2), _p(bias), _p(dy16),
+         _ll(dy16.stride(1) if dy16 is not None else 0), _p(dy32), _ll(dy32.stride(1) if dy32 is not None else 0),
+         int(c_split), _p(dx_out), _ll(dx_out.stride(1)), _p(part), B, L, C, _st())
+    s = part.sum(0)
+    return s[:, :4], s[:, 4]
+
+
+class _Conv(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias, init):
+        C = x.shape[-1]
+        w2 = w.reshape(C, -1).contiguous()
+        if not (x.stride(2) == 1 and x.stride(0) == x.shape[1] * x.stride(1) and x.stride(1) % 8 == 0):
+            x = x.contiguous()
+        init3 = None if init is None else init[:, -3:, :].contiguous()
+        out = _conv_fwd(x, w2, bias, init3)
+        ctx.save_for_backward(x, w2, bias)
+        ctx.wshape = w.shape
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w2, bias = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+        dw, db = _conv_bwd(x, w2, bias, dy, None, x.shape[-1], dx)
+        return dx, dw.to(w2.dtype).reshape(ctx.wshape), (None if bias is None else db.to(bias.dtype)), None
+
+
+def causal_conv1d_silu(x, weight, bias, initial_state=None):
+    _require_bf16(x, weight, bias)
+    if weight.shape[-1] != 4:
+        raise ValueError("the conv kernel is written for 4 taps")
+    return _Conv.apply(x, weight, bias, initial_state)
+
+
+# ======================================================================================
+# norms
+# ======================================================================================
+_ROW_SLICES = 296
+
+
+def _gated_fwd(y2, z2, w, eps, gs, out=None):
+    rows, d = y2.shape
+    if out is None:
+        out = torch.empty(rows, d, dtype=y2.dtype, device=y2.device)
+    _run("ssm_gated_rmsnorm_fwd", _p(y2), _ll(y2.stride(0)), _p(z2), _ll(z2.stride(0) if z2 is not None else 0), _p(w),
+         _p(out), _ll(out.stride(0)), _ll(rows), d, gs, _c.c_float(eps), _st())
+    return out
+
+
+def _gated_bwd(y2, z2, w, dout2, eps, gs, dy_out, dz_out):
+    rows, d = y2.shape
+    slices = int(min(rows, _ROW_SLICES))
+    part = torch.empty(slices, d, dtype=torch.float32, device=y2.device)
+    _run("ssm_gated_rmsnorm_bwd", _p(y2), _ll(y2.stride(0)), _p(z2), _ll(z2.stride(0) if z2 is not None else 0), _p(w),
+         _p(dout2), _ll(dout2.stride(0)), _p(dy_out), _ll(dy_out.stride(0)), _p(dz_out),
+         _ll(dz_out.stride(0) if dz_out is not None else 0), _p(part), slices, _ll(rows), d, gs, _c.c_float(eps), _st())
+    return part.sum(0)
+
+
+def _rows(t):
+    """[..., d] -> 2D view with unit inner stride (copy only if needed)."""
+    d = t.shape[-1]
+    if t.dim() == 2 and t.stride(1) == 1:
+        return t
+    if t.stride(-1) == 1 and t.dim() == 3 and t.stride(0) == t.shape[1] * t.stride(1):
+        return t.as_strided((t.shape[0] * t.shape[1], d), (t.stride(1), 1), t.storage_offset())
+    return t.reshape(-1, d).contiguous()
+
+
+class _GatedNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, y, z, w, eps, gs):
+        y2, z2 = _rows(y), (None if z is None else _rows(z))
+        out = _gated_fwd(y2, z2, w, eps, gs)
+        ctx.save_for_backward(y2, z2, w)
+        ctx.eps, ctx.gs, ctx.shape = eps, gs, y.shape
+        return out.reshape(y.shape)
+
+    @staticmethod
+    def backward(ctx, dout):
+        y2, z2, w = ctx.saved_tensors
+        d2 = _rows(dout.contiguous())
+        dy = torch.empty(y2.shape, dtype=y2.dtype, device=y2.device)
+        dz = None if z2 is None else torch.empty(y2.shape, dtype=y2.dtype, device=y2.device)
+        dw = _gated_bwd(y2, z2, w, d2, ctx.eps, ctx.gs, dy, dz)
+        return dy.reshape(ctx.shape), (None if dz is None else dz.reshape(ctx.shape)), dw.to(w.dtype), None, None
+
+
+def gated_rmsnorm(y, z, w, eps, group_size=None):
+    _require_bf16(y, z, w)
+    gs = y.shape[-1] if group_size is None else group_size
+    return _GatedNorm.apply(y, z, w, eps, gs)
+
+
+class _AddRMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, residual, w, eps, res_dtype):
+        D = x.shape[-1]
+        x2 = x.reshape(-1, D).contiguous()
+        rows = x2.shape[0]
+        r2 = None if residual is None else residual.reshape(-1, D).contiguous()
+        out = torch.empty_like(x2)
+        res_out = torch.empty(rows, D, dtype=res_dtype, device=x.device)
+        if r2 is not None and r2.dtype != res_dtype:
+            r2 = r2.to(res_dtype)
+        _run("ssm_add_rmsnorm_fwd", _p(x2), _p(r2), _p(w), _p(out), _p(res_out), _ll(rows), D, _c.c_float(eps),
+             int(res_dtype == torch.float32), _st())
+        ctx.save_for_backward(res_out, w)
+        ctx.eps, ctx.shape, ctx.has_res = eps, x.shape, residual is not None
+        ctx.x_dtype = x.dtype
+        return out.reshape(x.shape), res_out.reshape(x.shape)
+
+    @staticmethod
+    def backward(ctx, dout, dres):
+        res_out, w = ctx.saved_tensors
+        rows, D = res_out.shape
+        d2 = dout.reshape(rows, D).contiguous()
+        dr2 = None if dres is None else dres.reshape(rows, D).contiguous()
+        dsum = torch.empty_like(res_out)
+        slices = int(min(rows, _ROW_SLICES))
+        part = torch.empty(slices, D, dtype=torch.float32, device=res_out.device)
+        _run("ssm_add_rmsnorm_bwd", _p(res_out), _p(w), _p(d2), _p(dr2), _p(dsum), _p(part), slices, _ll(rows), D,
+             _c.c_float(ctx.eps), int(res_out.dtype == torch.float32), _st())
+        dsum = dsum.reshape(ctx.shape)
+        dx = dsum if dsum.dtype == ctx.x_dtype else dsum.to(ctx.x_dtype)
+        return dx, (dsum if ctx.has_res else None), part.sum(0).to(w.dtype), None, None
+
+
+def add_rmsnorm(x, residual, w, eps, residual_dtype=None):
+    _require_bf16(x, w)
+    rd = residual_dtype or x.dtype
+    return _AddRMSNorm.apply(x, residual, w, eps, rd)
+
+
+def rmsnorm(x, w, eps):
+    return add_rmsnorm(x, None, w, eps)[0]
+
+
+# ======================================================================================
+# GELU
+# ======================================================================================
+class _Gelu(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        xc = x.contiguous()
+        y = torch.empty_like(xc)
+        _run("ssm_gelu_fwd", _p(xc), _p(y), _ll(xc.numel()), _st())
+        ctx.save_for_backward(xc)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (xc,) = ctx.saved_tensors
+        dx = torch.empty_like(xc)
+        _run("ssm_gelu_bwd", _p(xc), _p(dy.contiguous()), _p(dx), _ll(xc.numel()), _st())
+        return dx
+
+
+def gelu(x):
+    _require_bf16(x)
+    if x.numel() % 8:
+        return torch.nn.functional.gelu(x)
+    return _Gelu.apply(x)
+
+
+# ======================================================================================
+# cross entropy
+# ======================================================================================
+def ce_partials(logits, labels, vocab_start):
+    rows, V = logits.shape
+    assert logits.stride(1) == 1
+    m = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    s, t = torch.empty_like(m), torch.empty_like(m)
+    _run("ssm_ce_partials", _p(logits), _ll(logits.stride(0)), int(logits.dtype == torch.float32),
+         _p(labels.contiguous()), _ll(rows), V, int(vocab_start), _p(m), _p(s), _p(t), _st())
+    return m, s, t
+
+
+def ce_backward(logits, labels, row_max, row_sum, grad_rows, vocab_start, ignore_index):
+    rows, V = logits.shape
+    ld = _ceil8(V)
+    grad = torch.empty(rows, ld, dtype=logits.dtype, device=logits.device)[:, :V]
+    if ld != V:
+        grad.as_strided((rows, ld - V), (ld, 1), V).zero_()
+    _run("ssm_ce_backward", _p(logits), _ll(logits.stride(0)), int(logits.dtype == torch.float32),
+         _p(labels.contiguous()), _ll(rows), V, int(vocab_start), _ll(ignore_index), _p(row_max), _p(row_sum),
+         _p(grad_rows.float().contiguous()), _p(grad), _ll(ld), _st())
+    return grad
+
+
+# ======================================================================================
+# optimizer
+# ======================================================================================
+def adamw_step(master, m, v, g, out, clip, lr, b1, b2, eps, wd, step):
+    if master.dtype != torch.float32:
+        raise TypeError("the fused AdamW keeps fp32 state")
+    out16 = out if out.dtype == torch.bfloat16 else None
+    out32 = out if out.dtype == torch.float32 else None
+    _run("ssm_adamw", _p(master), _p(m), _p(v), _p(g), int(g.dtype == torch.float32), _p(out16), _p(out32),
+         _ll(master.numel()), _p(clip), _c.c_float(lr), _c.c_float(b1), _c.c_float(b2), _c.c_float(eps),
+         _c.c_float(wd), int(step), _st())
+
+
+def sumsq_accumulate(g, total):
+    _run("ssm_sumsq", _p(g), int(g.dtype == torch.float32), _ll(g.numel()), _p(total), _st())
+
+
+# ======================================================================================
+# SSD scan and the fused mixer core
+# ======================================================================================
+_CT = 128
+
+
+def _ssd_dims(d_inner, head_dim, n_groups, d_state):
+    if d_state != 128:
+        raise ValueError("the GPU SSD kernels are written for d_state = 128")
+    if head_dim % 64:
+        raise ValueError("the GPU SSD kernels need head_dim to be a multiple of 64")
+    H = d_inner // head_dim
+    psplit = head_dim // 64
+    if H % n_groups:
+        raise ValueError("heads must be divisible by groups")
+    return H, psplit, H * psplit
+
+
+def _ssd_forward(conv_out, dt_raw2, dt_raw_stride, A, D, dt_bias, B, L, d_inner, G, H, Hv, init_state=None,
+                 want_final=False):
+    """conv_out [B*L, C] bf16 contiguous.  Returns y [B*L, d_inner], dt, l, S_in, final (or None)."""
+    dev = conv_out.device
+    C = conv_out.shape[1]
+    nc = L // _CT
+    st = status_tensor(dev)
+    dt = torch.empty(B, H, L, dtype=torch.float32, device=dev)
+    l = torch.empty_like(dt)
+    _run("ssm_ssd_dt_prep", _p(dt_raw2), _ll(dt_raw_stride), _p(dt_bias), _p(A), _p(dt), _p(l), B, L, H, _st())
+    s_local = torch.empty(B, Hv, nc, 128, 64, dtype=torch.float32, device=dev)
+    _run("ssm_ssd_chunk_state", _p(conv_out), _ll(C), C, d_inner, _p(conv_out), _ll(C), _p(dt), _p(l), _p(s_local),
+         B, L, H, Hv, G, 0, _p(st), _st())
+    s_in = torch.empty(B, Hv, nc, 128, 64, dtype=torch.bfloat16, device=dev)
+    final = torch.empty(B, Hv, 128, 64, dtype=torch.float32, device=dev) if want_final else None
+    _run("ssm_ssd_state_pass", _p(s_local), _p(l), _p(init_state), _p(s_in), _p(final), B, L, H, Hv, 0, _st())
+    y = torch.empty(B * L, d_inner, dtype=torch.bfloat16, device=dev)
+    _run("ssm_ssd_chunk_scan_fwd", _p(conv_out), _ll(C), C, _p(s_in), _p(y), _ll(d_inner), _p(dt), _p(l), _p(D),
+         B, L, H, Hv, G, d_inner, _p(st), _st())
+    return y, dt, l, s_in, final
+
+
+def _pick_hpc(hv_per_group, nc, G, B, target=296):
+    best = hv_per_group
+    for splits in range(1, hv_per_group + 1):
+        if hv_per_group % splits:
+            continue
+        best = hv_per_group // splits
+        if nc * G * B * splits >= target:
+            break
+    return best
+
+
+def _ssd_backward(conv_out, dy2, y2, dt, l, s_in, dt_raw2, dt_raw_stride, A, D, dt_bias, ddt_out, ddt_stride,
+                  B, L, d_inner, G, H, Hv):
+    """Returns dx [B*L, d_inner] bf16, dBC fp32 [B*L, 2*G*128], dA, dD, d_dt_bias (fp32 [H]);
+    d(dt_raw) goes to ddt_out (bf16, row stride ddt_stride, column h)."""
+    dev = conv_out.device
+    C = conv_out.shape[1]
+    nc = L // _CT
+    st = status_tensor(dev)
+    psplit = Hv // H
+    ds_local = torch.empty(B, Hv, nc, 128, 64, dtype=torch.float32, device=dev)
+    _run("ssm_ssd_chunk_state", _p(conv_out), _ll(C), C, d_inner + G * 128, _p(dy2), _ll(dy2.stride(0)), _p(dt), _p(l),
+         _p(ds_local), B, L, H, Hv, G, 1, _p(st), _st())
+    ds_out = torch.empty(B, Hv, nc, 128, 64, dtype=torch.bfloat16, device=dev)
+    _run("ssm_ssd_state_pass", _p(ds_local), _p(l), _p(None), _p(ds_out), _p(None), B, L, H, Hv, 1, _st())
+    dx = torch.empty(B * L, d_inner, dtype=torch.bfloat16, device=dev)
+    dBC = torch.zeros(B * L, 2 * G * 128, dtype=torch.float32, device=dev)
+    hpart = torch.empty(B * nc, Hv, 3, dtype=torch.float32, device=dev)
+    ddt32 = torch.empty(B, Hv, L, dtype=torch.float32, device=dev) if psplit > 1 else None
+    hpc = _pick_hpc(Hv // G, nc, G, B)
+    _run("ssm_ssd_chunk_scan_bwd", _p(conv_out), _ll(C), C, _p(dy2), _ll(dy2.stride(0)),
+         _p(s_in), _p(ds_out), _p(dx), _ll(d_inner), _p(dBC), _p(hpart), _p(ddt_out), _ll(ddt_stride), _p(ddt32),
+         _p(dt_raw2), _ll(dt_raw_stride), _p(dt_bias), _p(A), _p(dt), _p(l), _p(D), B, L, H, Hv, G, d_inner, hpc,
+         _p(st), _st())
+    hp = hpart.sum(0).reshape(H, psplit, 3).sum(1)
+    if ddt32 is not None:
+        summed = ddt32.reshape(B, H, psplit, L).sum(2).transpose(1, 2)           # [B, L, H]
+        ddt_out.as_strided((B, L, H), (L * ddt_stride, ddt_stride, 1)).copy_(summed)
+    return dx, dBC, hp[:, 0], hp[:, 1], hp[:, 2]
+
+
+def _final_states(final, xBC, H, psplit, K):
+    """kernel state layout [B,Hv,128 n,64 p] -> cache layout [B,H,P,N]; conv window [B,C,K]."""
+    B = final.shape[0]
+    ssm = final.reshape(B, H, psplit, 128, 64).permute(0, 1, 2, 4, 3).reshape(B, H, psplit * 64, 128).contiguous()
+    L = xBC.shape[1]
+    tail = xBC[:, -K:, :] if L >= K else torch.cat([xBC.new_zeros(B, K - L, xBC.shape[2]), xBC], dim=1)
+    return tail.transpose(1, 2).contiguous(), ssm
+
+
+class _MixerCore(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, zxBCdt, conv_w, conv_b, dt_bias, A_log, D, norm_w, d_inner, G, N, P, eps, gs, recompute,
+                want_final):
+        _require_bf16(zxBCdt, conv_w, conv_b, norm_w)
+        H, psplit, Hv = _ssd_dims(d_inner, P, G, N)
+        if not zxBCdt.is_contiguous():
+            zxBCdt = zxBCdt.contiguous()
+        B, L, W = zxBCdt.shape
+        C = d_inner + 2 * G * N
+        if W != d_inner + C + H or L % _CT or W % 8 or d_inner % 8:
+            raise ValueError("bad zxBCdt shape for the mixer core")
+        flat = zxBCdt.view(B * L, W)
+        z2, xBC, dt_raw2 = flat[:, :d_inner], zxBCdt[..., d_inner:d_inner + C], flat[:, d_inner + C:]
+        w2 = conv_w.reshape(C, -1).contiguous()
+        conv_out = _conv_fwd(xBC, w2, conv_b, None).view(B * L, C)
+        A = -torch.exp(A_log.float())
+        Df, bf = D.float(), dt_bias.float()
+        y, dt, l, s_in, final = _ssd_forward(conv_out, dt_raw2, W, A, Df, bf, B, L, d_inner, G, H, Hv,
+                                             want_final=want_final)
+        out = _gated_fwd(y, z2, norm_w, eps, gs)
+        ctx.dims = (B, L, W, C, d_inner, G, N, P, H, Hv, eps, gs, recompute)
+        if recompute:
+            ctx.save_for_backward(zxBCdt, w2, conv_b, dt_bias, A_log, D, norm_w)
+        else:
+            ctx.save_for_backward(zxBCdt, w2, conv_b, dt_bias, A_log, D, norm_w, conv_out, y, dt, l, s_in)
+        ctx.conv_w_shape = conv_w.shape
+        out = out.view(B, L, d_inner)
+        if want_final:
+            conv_state, ssm_state = _final_states(final, xBC, H, psplit, w2.shape[1])
+            ctx.mark_non_differentiable(conv_state, ssm_state)
+            return out, conv_state, ssm_state
+        return out
+
+    @staticmethod
+    def backward(ctx, dout, *unused):
+        B, L, W, C, d_inner, G, N, P, H, Hv, eps, gs, recompute = ctx.dims
+        saved = ctx.saved_tensors
+        zxBCdt, w2, conv_b, dt_bias, A_log, D, norm_w = saved[:7]
+        flat = zxBCdt.view(B * L, W)
+        z2, xBC, dt_raw2 = flat[:, :d_inner], zxBCdt[..., d_inner:d_inner + C], flat[:, d_inner + C:]
+        A = -torch.exp(A_log.float())
+        Df, bf = D.float(), dt_bias.float()
+        if recompute:
+            conv_out = _conv_fwd(xBC, w2, conv_b, None).view(B * L, C)
+            y, dt, l, s_in, _ = _ssd_forward(conv_out, dt_raw2, W, A, Df, bf, B, L, d_inner, G, H, Hv)
+        else:
+            conv_out, y, dt, l, s_in = saved[7:]
+        d_zx = torch.empty_like(zxBCdt)
+        dflat = d_zx.view(B * L, W)
+        dout2 = dout.reshape(B * L, d_inner)
+        if not dout2.is_contiguous():
+            dout2 = dout2.contiguous()
+        dy = torch.empty(B * L, d_inner, dtype=torch.bfloat16, device=dout.device)
+        dnorm_w = _gated_bwd(y, z2, norm_w, dout2, eps, gs, dy, dflat[:, :d_inner])
+        dx, dBC, dA, dD, dbias = _ssd_backward(conv_out, dy, y, dt, l, s_in, dt_raw2, W, A, Df, bf,
+                                               dflat[:, d_inner + C:], W, B, L, d_inner, G, H, Hv)
+        dw, db = _conv_bwd(xBC, w2, conv_b, dx.view(B, L, d_inner), dBC.view(B, L, 2 * G * N), d_inner,
+                           d_zx[..., d_inner:d_inner + C])
+        dA_log = (dA * A).to(A_log.dtype)
+        return (d_zx, dw.to(w2.dtype).reshape(ctx.conv_w_shape), None if conv_b is None else db.to(conv_b.dtype),
+                dbias.to(dt_bias.dtype), dA_log, dD.to(D.dtype), dnorm_w.to(norm_w.dtype),
+                None, None, None, None, None, None, None, None)
+
+
+def mamba2_mixer_core(zxBCdt, conv_w, conv_b, dt_bias, A_log, D, norm_w, d_inner, n_groups, d_state, head_dim, eps,
+                      norm_group_size, chunk_size, recompute, return_final_states):
+    if chunk_size != _CT:
+        raise ValueError("the GPU kernels use 128-token chunks")
+    gs = d_inner if norm_group_size is None else norm_group_size
+    res = _MixerCore.apply(zxBCdt, conv_w, conv_b, dt_bias, A_log, D, norm_w, d_inner, n_groups, d_state, head_dim,
+                           eps, gs, recompute, return_final_states)
+    if return_final_states:
+        return res[0], (res[1], res[2])
+    return res
+
+
+class _SSDScan(torch.autograd.Function):
+    """Stand-alone scan op (tests, custom models): packs x|B|C into the layout the kernels read."""
+
+    @staticmethod
+    def forward(ctx, x, dt_raw, A, Bm, Cm, D, dt_bias, want_final, init_state):
+        _require_bf16(x, Bm, Cm)
+        Bsz, L, H, P = x.shape
+        G, N = Bm.shape[2], Bm.shape[3]
+        d_inner = H * P
+        _, psplit, Hv = _ssd_dims(d_inner, P, G, N)
+        conv_out = torch.cat([x.reshape(Bsz, L, d_inner), Bm.reshape(Bsz, L, G * N), Cm.reshape(Bsz, L, G * N)],
+                             dim=-1).reshape(Bsz * L, -1).contiguous()
+        Hp = _ceil8(H)
+        dtr = torch.zeros(Bsz * L, Hp, dtype=torch.bfloat16, device=x.device)
+        dtr[:, :H] = dt_raw.reshape(Bsz * L, H).to(torch.bfloat16)
+        Af, Df, bf = A.float().contiguous(), D.float().contiguous(), dt_bias.float().contiguous()
+        init = None
+        if init_state is not None:   # [B,H,P,N] -> [B,Hv,128,64]
+            init = init_state.float().reshape(Bsz, H, psplit, 64, N).permute(0, 1, 2, 4, 3).reshape(
+                Bsz, Hv, N, 64).contiguous()
+        y, dt, l, s_in, final = _ssd_forward(conv_out, dtr, Hp, Af, Df, bf, Bsz, L, d_inner, G, H, Hv, init,
+                                             want_final)
+        ctx.save_for_backward(conv_out, y, dt, l, s_in, dtr, Af, Df, bf)
+        ctx.dims = (Bsz, L, H, P, G, N, Hv, Hp)
+        ctx.in_dtypes = (dt_raw.dtype, A.dtype, D.dtype, dt_bias.dtype)
+        yv = y.view(Bsz, L, H, P)
+        if want_final:
+            fin = final.reshape(Bsz, H, psplit, N, 64).permute(0, 1, 2, 4, 3).reshape(Bsz, H, P, N).contiguous()
+            ctx.mark_non_differentiable(fin)
+            return yv, fin
+        return yv
+
+    @staticmethod
+    def backward(ctx, dy, *unused):
+        conv_out, y, dt, l, s_in, dtr, Af, Df, bf = ctx.saved_tensors
+        Bsz, L, H, P, G, N, Hv, Hp = ctx.dims
+        d_inner = H * P
+        dy2 = dy.reshape(Bsz * L, d_inner).contiguous()
+        ddt = torch.zeros(Bsz * L, Hp, dtype=torch.bfloat16, device=dy.device)
+        dx, dBC, dA, dD, dbias = _ssd_backward(conv_out, dy2, y, dt, l, s_in, dtr, Hp, Af, Df, bf, ddt, Hp,
+                                               Bsz, L, d_inner, G, H, Hv)
+        t0, t1, t2, t3 = ctx.in_dtypes
+        return (dx.view(Bsz, L, H, P), ddt[:, :H].reshape(Bsz, L, H).to(t0), dA.to(t1),
+                dBC[:, :G * N].reshape(Bsz, L, G, N).to(dy.dtype), dBC[:, G * N:].reshape(Bsz, L, G, N).to(dy.dtype),
+                dD.to(t2), dbias.to(t3), None, None)
+
+
+def ssd_chunk_scan(x, dt_raw, A, Bm, Cm, D, dt_bias, chunk_size, initial_state, return_final_state):
+    if chunk_size != _CT:
+        raise ValueError("the GPU kernels use 128-token chunks")
+    return _SSDScan.apply(x, dt_raw, A, Bm, Cm, D, dt_bias, return_final_state, initial_state)
+
+
+# ======================================================================================
+# decode
+# ======================================================================================
+@torch.no_grad()
+def ssm_decode_step(zxBCdt, conv_state, ssm_state, conv_w, conv_b, dt_bias, A_log, D, norm_w, d_inner, n_groups,
+                    d_state, head_dim, eps, norm_group_size):
+    _require_bf16(zxBCdt, conv_state, conv_w, norm_w)
+    if ssm_state.dtype != torch.float32:
+        raise TypeError("the decode kernel keeps the SSM state in fp32")
+    B, W = zxBCdt.shape
+    C = d_inner + 2 * n_groups * d_state
+    H = d_inner // head_dim
+    if conv_state.shape[-1] != 4 or not conv_state.is_contiguous() or not ssm_state.is_contiguous():
+        raise ValueError("decode needs contiguous states and a 4-tap conv window")
+    if zxBCdt.stride(1) != 1:
+        zxBCdt = zxBCdt.contiguous()
+    dev = zxBCdt.device
+    act = torch.empty(B, C, dtype=torch.float32, device=dev)
+    xBC = zxBCdt[:, d_inner:d_inner + C]
+    _run("ssm_decode_conv_step", _p(xBC), _ll(zxBCdt.stride(0)), _p(conv_state), _p(conv_w.reshape(C, 4).contiguous()),
+         _p(conv_b), _p(act), B, C, _st())
+    y = torch.empty(B, d_inner, dtype=torch.bfloat16, device=dev)
+    A = -torch.exp(A_log.float())
+    _run("ssm_decode_ssm_step", _p(act), _p(zxBCdt[:, d_inner + C:]), _ll(zxBCdt.stride(0)), _p(dt_bias.float()),
+         _p(A), _p(D.float()), _p(ssm_state), _p(y), B, C, H, head_dim, d_state, n_groups, d_inner, _st())
+    gs = d_inner if norm_group_size is None else norm_group_size
+    return _gated_fwd(y, zxBCdt[:, :d_inner], norm_w, eps, gs)

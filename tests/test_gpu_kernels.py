@@ -1,0 +1,270 @@
+"""Numerics of each CUDA kernel against the fp32 PyTorch oracle of the same op (B200 only)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _close(a, b, atol=1e-3, rtol=3e-2, frac=0.999):
+    a, b = a.float(), b.float()
+    ok = (a - b).abs() <= atol + rtol * b.abs()
+    assert ok.float().mean().item() >= frac, f"only {ok.float().mean().item():.5f} close; max err {(a - b).abs().max().item():.4e}"
+
+
+@pytest.fixture(autouse=True)
+def _status():
+    yield
+    from state_space_models_neuron_b200.ops import cuda_ops
+    torch.cuda.synchronize()
+    cuda_ops.check_status()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 512, 256), (2048, 2320, 4096), (300, 6286, 1032), (64, 4096, 1024)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
+def test_gemm_bf16(M, N, K, a_mn, b_mn):
+    from state_space_models_neuron_b200.ops import cuda_ops
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    a = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    b = torch.randn(N, K, device="cuda", generator=g).bfloat16()
+    ref = a.float() @ b.float().t()
+    A = a.t().contiguous() if a_mn else a
+    Bm = b.t().contiguous() if b_mn else b
+    if (A.shape[1] % 8) or (Bm.shape[1] % 8):
+        pad = lambda t: torch.nn.functional.pad(t, (0, (-t.shape[1]) % 8))[:, :t.shape[1]]
+        A, Bm = pad(A), pad(Bm)
+    out = cuda_ops.gemm(A, Bm, a_mn=a_mn, b_mn=b_mn)
+    torch.cuda.synchronize()
+    cuda_ops.check_status()
+    _close(out, ref, atol=0.5, rtol=2e-2)
+    acc = torch.ones(M, N, device="cuda")
+    cuda_ops.gemm(A, Bm, a_mn=a_mn, b_mn=b_mn, out=acc, accumulate=True)
+    _close(acc, ref + 1.0, atol=0.5, rtol=2e-2)
+    f32 = cuda_ops.gemm(A, Bm, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
+    _close(f32, ref, atol=0.05, rtol=1e-3)
+
+
+def test_gemm_bias_gelu():
+    from state_space_models_neuron_b200.ops import cuda_ops
+    a = torch.randn(256, 512, device="cuda").bfloat16()
+    b = (torch.randn(384, 512, device="cuda") * 0.05).bfloat16()
+    bias = torch.randn(384, device="cuda").bfloat16()
+    out = cuda_ops.gemm(a, b, bias=bias, gelu=True)
+    ref = torch.nn.functional.gelu(a.float() @ b.float().t() + bias.float())
+    _close(out, ref, atol=2e-2, rtol=2e-2)
+
+
+def test_linear_autograd():
+    from state_space_models_neuron_b200 import ops
+    x = torch.randn(2, 128, 256, device="cuda").bfloat16().requires_grad_(True)
+    w = (torch.randn(520, 256, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    y = ops.linear(x, w)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    yr = torch.nn.functional.linear(xr, wr)
+    yr.backward(gy.float())
+    _close(y, yr, atol=2e-2)
+    _close(x.grad, xr.grad, atol=5e-2)
+    _close(w.grad, wr.grad, atol=0.3)
+
+
+@pytest.mark.parametrize("B,L,C", [(2, 256, 1280), (1, 200, 64)])
+def test_conv_fwd_bwd(B, L, C):
+    from state_space_models_neuron_b200 import ops
+    from state_space_models_neuron_b200.ops import oracle
+    big = torch.randn(B, L, C + 64, device="cuda").bfloat16()
+    x = big[..., 32:32 + C].detach().requires_grad_(True)   # strided view, like the xBC slice of zxBCdt
+    w = (torch.randn(C, 1, 4, device="cuda") * 0.5).bfloat16().requires_grad_(True)
+    b = torch.randn(C, device="cuda").bfloat16().requires_grad_(True)
+    y = ops.causal_conv1d_silu(x, w, b)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    xr, wr, br = [t.detach().float().requires_grad_(True) for t in (x, w, b)]
+    yr = oracle.causal_conv1d_silu(xr, wr.reshape(C, 4), br)
+    yr.backward(gy.float())
+    _close(y, yr, atol=2e-2)
+    _close(x.grad, xr.grad, atol=3e-2)
+    _close(w.grad, wr.grad, atol=0.5, rtol=3e-2)
+    _close(b.grad, br.grad, atol=0.5, rtol=3e-2)
+
+
+@pytest.mark.parametrize("rows,d,gs", [(300, 1024, 128), (64, 8192, 1024), (17, 512, 512), (32, 8192, 8192)])
+def test_gated_rmsnorm_fwd_bwd(rows, d, gs):
+    from state_space_models_neuron_b200 import ops
+    from state_space_models_neuron_b200.ops import oracle
+    y = torch.randn(1, rows, d, device="cuda").bfloat16().requires_grad_(True)
+    z = torch.randn(1, rows, d, device="cuda").bfloat16().requires_grad_(True)
+    w = (1 + 0.1 * torch.randn(d, device="cuda")).bfloat16().requires_grad_(True)
+    out = ops.gated_rmsnorm(y, z, w, 1e-5, gs)
+    go = torch.randn_like(out)
+    out.backward(go)
+    yr, zr, wr = [t.detach().float().requires_grad_(True) for t in (y, z, w)]
+    o2 = oracle.gated_rmsnorm(yr, zr, wr, 1e-5, gs)
+    o2.backward(go.float())
+    _close(out, o2, atol=2e-2)
+    _close(y.grad, yr.grad, atol=3e-2)
+    _close(z.grad, zr.grad, atol=3e-2)
+    _close(w.grad, wr.grad, atol=0.3, rtol=3e-2)
+
+
+@pytest.mark.parametrize("res_dtype", [None, torch.float32])
+def test_add_rmsnorm_fwd_bwd(res_dtype):
+    from state_space_models_neuron_b200 import ops
+    from state_space_models_neuron_b200.ops import oracle
+    D = 4096
+    x = torch.randn(2, 96, D, device="cuda").bfloat16().requires_grad_(True)
+    r = torch.randn(2, 96, D, device="cuda").to(res_dtype or torch.bfloat16).requires_grad_(True)
+    w = (1 + 0.1 * torch.randn(D, device="cuda")).bfloat16().requires_grad_(True)
+    out, rn = ops.add_rmsnorm(x, r, w, 1e-5, res_dtype)
+    g1, g2 = torch.randn_like(out), torch.randn_like(rn)
+    torch.autograd.backward([out, rn], [g1, g2])
+    xr, rr, wr = [t.detach().float().requires_grad_(True) for t in (x, r, w)]
+    s = xr + rr
+    o2 = oracle.rmsnorm(s, wr, 1e-5)
+    torch.autograd.backward([o2, s], [g1.float(), g2.float()])
+    _close(out, o2, atol=2e-2)
+    _close(rn, s, atol=3e-2)
+    _close(x.grad, xr.grad, atol=5e-2)
+    _close(r.grad, rr.grad, atol=5e-2)
+    _close(w.grad, wr.grad, atol=0.5, rtol=3e-2)
+
+
+def test_gelu_and_ce():
+    from state_space_models_neuron_b200 import ops
+    x = torch.randn(64, 2048, device="cuda").bfloat16().requires_grad_(True)
+    y = ops.gelu(x)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    xr = x.detach().float().requires_grad_(True)
+    yr = torch.nn.functional.gelu(xr)
+    yr.backward(gy.float())
+    _close(y, yr, atol=2e-2)
+    _close(x.grad, xr.grad, atol=2e-2)
+    from state_space_models_neuron_b200.parallel.cross_entropy import parallel_cross_entropy
+    V = 6286
+    base = torch.randn(200, 6288, device="cuda").bfloat16()
+    lg = base[:, :V].detach().requires_grad_(True)
+    lb = torch.randint(0, V, (200,), device="cuda")
+    lb[5] = -100
+    loss = parallel_cross_entropy(lg, lb)
+    loss.sum().backward()
+    lr_ = lg.detach().float().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(lr_, lb, reduction="none", ignore_index=-100)
+    ref.sum().backward()
+    _close(loss, ref, atol=2e-2)
+    _close(lg.grad, lr_.grad, atol=2e-3)
+
+
+def test_adamw_and_sumsq():
+    from state_space_models_neuron_b200.ops import cuda_ops
+    n = 100000
+    master = torch.randn(n, device="cuda")
+    m, v = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    g = torch.randn(n, device="cuda")
+    out = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    ref_p = master.clone().requires_grad_(True)
+    opt = torch.optim.AdamW([ref_p], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    clip = torch.full((1,), 0.5, device="cuda")
+    for step in (1, 2, 3):
+        ref_p.grad = g * 0.5
+        opt.step()
+        cuda_ops.adamw_step(master, m, v, g, out, clip, 1e-2, 0.9, 0.95, 1e-8, 0.1, step)
+    assert torch.allclose(master, ref_p.detach(), atol=1e-5, rtol=1e-4)
+    assert torch.allclose(out.float(), master, atol=1e-2, rtol=1e-2)
+    tot = torch.zeros(1, device="cuda")
+    cuda_ops.sumsq_accumulate(g, tot)
+    assert abs(tot.item() - g.pow(2).sum().item()) / g.pow(2).sum().item() < 1e-4
+
+
+def _scan_case(B, L, H, P, G, seed=0):
+    N = 128
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    x = torch.randn(B, L, H, P, device="cuda", generator=g).bfloat16()
+    dt_raw = (torch.rand(B, L, H, device="cuda", generator=g) * 4 - 4).bfloat16()
+    A = -(torch.rand(H, device="cuda", generator=g) * 15 + 1)
+    Bm = (torch.randn(B, L, G, N, device="cuda", generator=g) * 0.5).bfloat16()
+    Cm = (torch.randn(B, L, G, N, device="cuda", generator=g) * 0.5).bfloat16()
+    D = torch.randn(H, device="cuda", generator=g)
+    dt_bias = torch.randn(H, device="cuda", generator=g) * 0.5
+    return x, dt_raw, A, Bm, Cm, D, dt_bias
+
+
+@pytest.mark.parametrize("B,L,H,P,G", [(1, 128, 2, 64, 1), (2, 384, 4, 64, 2), (1, 256, 2, 128, 1), (1, 512, 16, 64, 8)])
+def test_ssd_scan_fwd_bwd(B, L, H, P, G):
+    from state_space_models_neuron_b200 import ops
+    from state_space_models_neuron_b200.ops import oracle
+    ins = _scan_case(B, L, H, P, G)
+    leaf = [t.detach().clone().requires_grad_(True) for t in ins]
+    y, fin = ops.ssd_chunk_scan(*leaf, chunk_size=128, return_final_state=True)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    ref = [t.detach().float().requires_grad_(True) for t in ins]
+    x, dt_raw, A, Bm, Cm, D, dt_bias = ref
+    dt = oracle.softplus(dt_raw + dt_bias)
+    yr, sr = oracle.ssd_chunked(x, dt, A, Bm, Cm, D, 128)
+    yr.backward(gy.float())
+    _close(y, yr, atol=3e-2, rtol=3e-2)
+    _close(fin, sr, atol=3e-2, rtol=3e-2)
+    names = ["dx", "ddt", "dA", "dB", "dC", "dD", "dbias"]
+    for n, a, b in zip(names, leaf, ref):
+        scale = b.grad.abs().max().item()
+        _close(a.grad, b.grad, atol=2e-2 * max(scale, 1.0), rtol=5e-2, frac=0.995)
+
+
+@pytest.mark.parametrize("recompute", [False, True])
+def test_mixer_core_fwd_bwd(recompute):
+    from state_space_models_neuron_b200 import ops
+    B, L, d_inner, G, N, P = 2, 256, 512, 2, 128, 64
+    H, C = d_inner // P, d_inner + 2 * G * N
+    g = torch.Generator(device="cuda").manual_seed(5)
+    zx = (torch.randn(B, L, d_inner + C + H, device="cuda", generator=g)).bfloat16()
+    params = dict(
+        conv_w=(torch.randn(C, 1, 4, device="cuda", generator=g) * 0.4).bfloat16(),
+        conv_b=(torch.randn(C, device="cuda", generator=g) * 0.2).bfloat16(),
+        dt_bias=(torch.randn(H, device="cuda", generator=g) * 0.5 - 2).bfloat16(),
+        A_log=torch.log(torch.rand(H, device="cuda", generator=g) * 15 + 1).bfloat16(),
+        D=torch.ones(H, device="cuda").bfloat16(),
+        norm_w=(1 + 0.1 * torch.randn(d_inner, device="cuda", generator=g)).bfloat16())
+    kw = dict(d_inner=d_inner, n_groups=G, d_state=N, head_dim=P, eps=1e-5, norm_group_size=d_inner // G)
+    a = [zx.clone().requires_grad_(True)] + [v.clone().requires_grad_(True) for v in params.values()]
+    out = ops.mamba2_mixer_core(*a, recompute=recompute, **kw)
+    go = torch.randn_like(out)
+    out.backward(go)
+    b = [t.detach().float().cpu().requires_grad_(True) for t in a]
+    ref = ops.mamba2_mixer_core(*b, **kw)
+    ref.backward(go.float().cpu())
+    _close(out.cpu(), ref, atol=3e-2, rtol=3e-2)
+    for n, x, y in zip(["zxBCdt"] + list(params), a, b):
+        scale = max(y.grad.abs().max().item(), 1.0)
+        _close(x.grad.cpu(), y.grad, atol=3e-2 * scale, rtol=5e-2, frac=0.99)
+    o2, (cs, ss) = ops.mamba2_mixer_core(*[t.detach() for t in a], return_final_states=True, **kw)
+    r2, (cs_r, ss_r) = ops.mamba2_mixer_core(*[t.detach() for t in b], return_final_states=True, **kw)
+    _close(ss.cpu(), ss_r, atol=3e-2, rtol=3e-2)
+    _close(cs.cpu(), cs_r, atol=1e-2)
+
+
+def test_decode_step_matches_oracle():
+    from state_space_models_neuron_b200 import ops
+    B, d_inner, G, N, P = 3, 512, 2, 128, 64
+    H, C = d_inner // P, d_inner + 2 * G * N
+    g = torch.Generator(device="cuda").manual_seed(9)
+    p = dict(conv_w=(torch.randn(C, 1, 4, device="cuda", generator=g) * 0.4).bfloat16(),
+             conv_b=(torch.randn(C, device="cuda", generator=g) * 0.2).bfloat16(),
+             dt_bias=(torch.randn(H, device="cuda", generator=g) * 0.5 - 2).bfloat16(),
+             A_log=torch.log(torch.rand(H, device="cuda", generator=g) * 15 + 1).bfloat16(),
+             D=torch.ones(H, device="cuda").bfloat16(),
+             norm_w=(1 + 0.1 * torch.randn(d_inner, device="cuda", generator=g)).bfloat16())
+    kw = dict(d_inner=d_inner, n_groups=G, d_state=N, head_dim=P, eps=1e-5, norm_group_size=d_inner // G)
+    cs = torch.zeros(B, C, 4, device="cuda", dtype=torch.bfloat16)
+    ss = torch.zeros(B, H, P, N, device="cuda")
+    cs_r, ss_r = cs.float().cpu(), ss.cpu()
+    pr = {k: v.float().cpu() for k, v in p.items()}
+    for step in range(6):
+        zx = torch.randn(B, d_inner + C + H, device="cuda", generator=g).bfloat16()
+        out = ops.ssm_decode_step(zx, cs, ss, *p.values(), **kw)
+        ref = ops.ssm_decode_step(zx.float().cpu(), cs_r, ss_r, *pr.values(), **kw)
+        _close(out.cpu(), ref, atol=3e-2, rtol=3e-2)
+    _close(ss.cpu(), ss_r, atol=2e-2, rtol=2e-2)
+    _close(cs.cpu(), cs_r, atol=1e-2, rtol=1e-2)
