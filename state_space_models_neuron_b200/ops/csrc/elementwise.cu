@@ -508,31 +508,58 @@ ce_backward_kernel(const T* __restrict__ logits, long long ld, const long long* 
 // =====================================================================================
 // AdamW on a flat fp32 master shard + low-precision copy; sum of squares
 // =====================================================================================
+// 4 elements per thread per iteration, 16-byte loads/stores; n4 = n / 4 (segments are multiples of 128 elements)
+template <typename GT> struct Vec4;
+template <> struct Vec4<float> {
+  static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+};
+template <> struct Vec4<__nv_bfloat16> {
+  static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    return make_float4(bf16_lo(u.x), bf16_hi(u.x), bf16_lo(u.y), bf16_hi(u.y));
+  }
+};
+
 template <typename GT>
-__global__ void adamw_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
-                             const GT* __restrict__ g, __nv_bfloat16* __restrict__ out16, float* __restrict__ out32,
-                             long long n, const float* __restrict__ clip, float lr, float b1, float b2, float eps,
-                             float wd, float bc1, float bc2) {
+__global__ void __launch_bounds__(256)
+adamw_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
+             const GT* __restrict__ g, __nv_bfloat16* __restrict__ out16, float* __restrict__ out32,
+             long long n4, const float* __restrict__ clip, float lr, float b1, float b2, float eps,
+             float wd, float bc1, float bc2) {
   const float c = clip ? *clip : 1.f;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-    const float gi = to_f<GT>(g[i]) * c;
-    const float mi = b1 * m[i] + (1.f - b1) * gi;
-    const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
-    float wv = master[i] * (1.f - lr * wd);
-    wv -= lr * (mi / bc1) / (sqrtf(vi / bc2) + eps);
-    m[i] = mi; v[i] = vi; master[i] = wv;
-    if (out16) out16[i] = __float2bfloat16(wv);
-    if (out32) out32[i] = wv;
+  const float decay = 1.f - lr * wd, ib1 = 1.f / bc1, ib2 = 1.f / bc2;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    const float4 gi = Vec4<GT>::load(g + i * 4);
+    float4 mi = *reinterpret_cast<const float4*>(m + i * 4);
+    float4 vi = *reinterpret_cast<const float4*>(v + i * 4);
+    float4 wv = *reinterpret_cast<const float4*>(master + i * 4);
+    #define SSM_ADAM(f)                                             \
+      { const float gg = gi.f * c;                                  \
+        mi.f = b1 * mi.f + (1.f - b1) * gg;                         \
+        vi.f = b2 * vi.f + (1.f - b2) * gg * gg;                    \
+        wv.f = wv.f * decay - lr * (mi.f * ib1) / (sqrtf(vi.f * ib2) + eps); }
+    SSM_ADAM(x) SSM_ADAM(y) SSM_ADAM(z) SSM_ADAM(w)
+    #undef SSM_ADAM
+    *reinterpret_cast<float4*>(m + i * 4) = mi;
+    *reinterpret_cast<float4*>(v + i * 4) = vi;
+    *reinterpret_cast<float4*>(master + i * 4) = wv;
+    if (out16) {
+      uint2 o;
+      o.x = pack_bf16(wv.x, wv.y); o.y = pack_bf16(wv.z, wv.w);
+      *reinterpret_cast<uint2*>(out16 + i * 4) = o;
+    }
+    if (out32) *reinterpret_cast<float4*>(out32 + i * 4) = wv;
   }
 }
 
 template <typename GT>
-__global__ void sumsq_kernel(const GT* __restrict__ g, long long n, float* __restrict__ total) {
+__global__ void __launch_bounds__(256)
+sumsq_kernel(const GT* __restrict__ g, long long n4, float* __restrict__ total) {
   __shared__ float red[33];
   float s = 0.f;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-    const float x = to_f<GT>(g[i]);
-    s += x * x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    const float4 x = Vec4<GT>::load(g + i * 4);
+    s += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
   }
   s = block_sum(s, red);
   if (threadIdx.x == 0) atomicAdd(total, s);
@@ -662,6 +689,11 @@ extern "C" int ssm_adamw(void* master, void* m, void* v, const void* g, int g_fp
                          long long n, const void* clip, float lr, float b1, float b2, float eps, float wd, int step,
                          cudaStream_t st) {
   const float bc1 = 1.f - powf(b1, (float)step), bc2 = 1.f - powf(b2, (float)step);
+  if (n % 4 || (reinterpret_cast<uintptr_t>(master) | reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v) |
+                reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(out32)) & 15 ||
+      (reinterpret_cast<uintptr_t>(out16) & 7))
+    return -SSM_ERR_BAD_ARG;
+  n /= 4;
   const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
   auto M = reinterpret_cast<float*>(master); auto mm = reinterpret_cast<float*>(m); auto vv = reinterpret_cast<float*>(v);
   auto cl = reinterpret_cast<const float*>(clip);
@@ -670,6 +702,8 @@ extern "C" int ssm_adamw(void* master, void* m, void* v, const void* g, int g_fp
   return (int)cudaGetLastError();
 }
 extern "C" int ssm_sumsq(const void* g, int g_fp32, long long n, void* total, cudaStream_t st) {
+  if (n % 4 || (reinterpret_cast<uintptr_t>(g) & 15)) return -SSM_ERR_BAD_ARG;
+  n /= 4;
   const int blocks = (int)((n + 255) / 256 < 148 * 4 ? (n + 255) / 256 : 148 * 4);
   if (g_fp32) sumsq_kernel<float><<<blocks, 256, 0, st>>>(reinterpret_cast<const float*>(g), n, reinterpret_cast<float*>(total));
   else sumsq_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(BF(g), n, reinterpret_cast<float*>(total));

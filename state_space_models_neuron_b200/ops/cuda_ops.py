@@ -27,8 +27,19 @@ def _lib():
     return native.lib()
 
 
+class _P:
+    """Pointer argument that keeps its tensor alive until the launch call has returned: a temporary
+    (`x.float()`, `.contiguous()`) must not be freed, and its block handed to the next temporary in the
+    same argument list, before the kernel is enqueued."""
+    __slots__ = ("t", "_as_parameter_")
+
+    def __init__(self, t):
+        self.t = t
+        self._as_parameter_ = _c.c_void_p(0 if t is None else t.data_ptr())
+
+
 def _p(t: Optional[torch.Tensor]):
-    return _c.c_void_p(0 if t is None else t.data_ptr())
+    return _P(t)
 
 
 def _st():
@@ -141,7 +152,9 @@ class _Linear(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             mg = getattr(w, "main_grad", None)
             if mg is not None and mg.dtype == torch.float32:
-                gemm(dy2, x2, a_mn=True, b_mn=True, out=mg, accumulate=True)   # main_grad += dY^T X
+                stale = getattr(w, "grad_stale", False)                        # first contribution: plain store
+                gemm(dy2, x2, a_mn=True, b_mn=True, out=mg, accumulate=not stale)   # main_grad (+)= dY^T X
+                w.grad_stale = False
             else:
                 dw = gemm(dy2, x2, a_mn=True, b_mn=True)
                 if not dw.is_contiguous():
@@ -497,9 +510,9 @@ class _MixerCore(torch.autograd.Function):
         out = _gated_fwd(y, z2, norm_w, eps, gs)
         ctx.dims = (B, L, W, C, d_inner, G, N, P, H, Hv, eps, gs, recompute)
         if recompute:
-            ctx.save_for_backward(zxBCdt, w2, conv_b, dt_bias, A_log, D, norm_w)
+            ctx.save_for_backward(zxBCdt, w2, conv_b, dt_bias, A_log, D, norm_w, A, Df, bf)
         else:
-            ctx.save_for_backward(zxBCdt, w2, conv_b, dt_bias, A_log, D, norm_w, conv_out, y, dt, l, s_in)
+            ctx.save_for_backward(zxBCdt, w2, conv_b, dt_bias, A_log, D, norm_w, A, Df, bf, conv_out, y, dt, l, s_in)
         ctx.conv_w_shape = conv_w.shape
         out = out.view(B, L, d_inner)
         if want_final:
@@ -512,16 +525,14 @@ class _MixerCore(torch.autograd.Function):
     def backward(ctx, dout, *unused):
         B, L, W, C, d_inner, G, N, P, H, Hv, eps, gs, recompute = ctx.dims
         saved = ctx.saved_tensors
-        zxBCdt, w2, conv_b, dt_bias, A_log, D, norm_w = saved[:7]
+        zxBCdt, w2, conv_b, dt_bias, A_log, D, norm_w, A, Df, bf = saved[:10]
         flat = zxBCdt.view(B * L, W)
         z2, xBC, dt_raw2 = flat[:, :d_inner], zxBCdt[..., d_inner:d_inner + C], flat[:, d_inner + C:]
-        A = -torch.exp(A_log.float())
-        Df, bf = D.float(), dt_bias.float()
         if recompute:
             conv_out = _conv_fwd(xBC, w2, conv_b, None).view(B * L, C)
             y, dt, l, s_in, _ = _ssd_forward(conv_out, dt_raw2, W, A, Df, bf, B, L, d_inner, G, H, Hv)
         else:
-            conv_out, y, dt, l, s_in = saved[7:]
+            conv_out, y, dt, l, s_in = saved[10:]
         d_zx = torch.empty_like(zxBCdt)
         dflat = d_zx.view(B * L, W)
         dout2 = dout.reshape(B * L, d_inner)

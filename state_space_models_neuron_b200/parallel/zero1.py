@@ -107,14 +107,28 @@ class Zero1Optimizer(torch.optim.Optimizer):
     @staticmethod
     def _accumulate_hook(p: torch.nn.Parameter) -> None:
         if p.grad is not None:
-            p.main_grad.add_(p.grad.to(p.main_grad.dtype))
+            if getattr(p, "grad_stale", False):
+                p.main_grad.copy_(p.grad)
+                p.grad_stale = False
+            else:
+                p.main_grad.add_(p.grad.to(p.main_grad.dtype))
             p.grad = None
 
     # ------------------------------------------------------------------------------------
     def zero_grad(self, set_to_none: bool = True) -> None:
-        self.flat_grads.zero_()
+        """Lazy: gradients are not cleared here; every parameter is marked stale and the first
+        contribution of the next micro-step overwrites `main_grad` instead of adding to it (the wgrad GEMM
+        then stores instead of read-modify-write).  Parameters that receive no gradient are zeroed in
+        `step()`.  This saves one full pass over the fp32 gradient buffer per step."""
         for p, *_ in self.layout:
             p.grad = None
+            p.grad_stale = True
+
+    def _finish_lazy_zero(self) -> None:
+        for p, *_ in self.layout:
+            if getattr(p, "grad_stale", False):
+                p.main_grad.zero_()
+                p.grad_stale = False
 
     def _allreduce_sequence_parallel_grads(self) -> None:
         """Sum over the TP group the grads of TP-replicated parameters that only saw a slice of
@@ -167,6 +181,7 @@ class Zero1Optimizer(torch.optim.Optimizer):
 
     @torch.no_grad()
     def step(self, closure=None):
+        self._finish_lazy_zero()
         self._allreduce_sequence_parallel_grads()
         g = self._reduce_gradients()
         self.step_count += 1
