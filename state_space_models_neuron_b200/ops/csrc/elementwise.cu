@@ -709,3 +709,65 @@ extern "C" int ssm_sumsq(const void* g, int g_fp32, long long n, void* total, cu
   else sumsq_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(BF(g), n, reinterpret_cast<float*>(total));
   return (int)cudaGetLastError();
 }
+
+// =====================================================================================
+// allocation-free variant of add_rmsnorm_bwd (declared in ssm_noalloc.h)
+// =====================================================================================
+#include "ssm_noalloc.h"
+#include <mutex>
+
+// Partial weight-gradient sums, [SSM_NOALLOC_SLICES][D] packed with the call's D.  In host code this name is
+// only a handle for the runtime's symbol table, never an address to pass to a kernel.
+static __device__ __align__(256) float g_noalloc_scratch[SSM_NOALLOC_SLICES * SSM_NOALLOC_MAX_D];
+
+namespace ssm {
+// dw[c] = sum_s part[s][c]; device code may name the array directly.
+__global__ void __launch_bounds__(256) noalloc_colsum_kernel(float* __restrict__ dw, int slices, int D) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= D) return;
+  float s = 0.f;
+  for (int r = 0; r < slices; ++r) s += g_noalloc_scratch[(long long)r * D + c];
+  dw[c] = s;
+}
+}  // namespace ssm
+
+static float* noalloc_scratch_for_current_device(int* err) {
+  constexpr int kMaxDevices = 64;
+  static float* ptrs[kMaxDevices] = {nullptr};
+  static std::mutex mu;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) { *err = e != cudaSuccess ? (int)e : -SSM_NOALLOC_ERR_BAD_ARG; return nullptr; }
+  std::lock_guard<std::mutex> lock(mu);
+  if (ptrs[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);   // device address of the array on the current device
+    if (e != cudaSuccess) { *err = (int)e; return nullptr; }
+    ptrs[dev] = static_cast<float*>(p);
+  }
+  *err = 0;
+  return ptrs[dev];
+}
+
+extern "C" int ssm_add_rmsnorm_bwd_noalloc(const void* res, const void* w, const void* dout, const void* dres_out,
+                                           void* dsum, void* dw, long long rows, int D, float eps, int res_fp32,
+                                           cudaStream_t st) {
+  if (D > SSM_NOALLOC_MAX_D) return -SSM_NOALLOC_ERR_TOO_LARGE;
+  const int t = norm_threads(D);
+  if (D <= 0 || D % 8 || t < 0 || rows < 1 || !res || !w || !dout || !dsum || !dw) return -SSM_NOALLOC_ERR_BAD_ARG;
+  int err = 0;
+  float* scratch = noalloc_scratch_for_current_device(&err);
+  if (scratch == nullptr) return err;
+  const int slices = rows < SSM_NOALLOC_SLICES ? (int)rows : SSM_NOALLOC_SLICES;
+  if (res_fp32)
+    add_rmsnorm_bwd_kernel<float><<<slices, t, 0, st>>>(reinterpret_cast<const float*>(res), BF(w), BF(dout),
+                                                        reinterpret_cast<const float*>(dres_out),
+                                                        reinterpret_cast<float*>(dsum), scratch, rows, D, eps);
+  else
+    add_rmsnorm_bwd_kernel<__nv_bfloat16><<<slices, t, 0, st>>>(BF(res), BF(w), BF(dout), BF(dres_out), BFM(dsum),
+                                                                scratch, rows, D, eps);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  noalloc_colsum_kernel<<<(D + 255) / 256, 256, 0, st>>>(reinterpret_cast<float*>(dw), slices, D);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,72 @@
+"""The allocation-free entry point, called through its exported C symbol, must agree with the regular
+add_rmsnorm backward on two consecutive calls (the second with other sizes, so contents left in the library's
+internal array by the first call would show up as an error).  Collected last on purpose."""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _close(a, b, atol=1e-3, rtol=3e-2):
+    a, b = a.float(), b.float()
+    assert ((a - b).abs() <= atol + rtol * b.abs()).all(), f"max err {(a - b).abs().max().item():.4e}"
+
+
+def _reference(res, w, dout, dres, eps):
+    """existing entry point: partial sums in a caller-allocated buffer, reduced by the caller"""
+    from state_space_models_neuron_b200.ops import native
+    lib = native.lib()
+    rows, D = res.shape
+    slices = min(rows, 296)
+    part = torch.empty(slices, D, dtype=torch.float32, device="cuda")
+    dsum = torch.empty_like(res)
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    fn = lib.ssm_add_rmsnorm_bwd
+    fn.restype = ctypes.c_int
+    code = fn(ctypes.c_void_p(res.data_ptr()), ctypes.c_void_p(w.data_ptr()), ctypes.c_void_p(dout.data_ptr()),
+              ctypes.c_void_p(dres.data_ptr()), ctypes.c_void_p(dsum.data_ptr()), ctypes.c_void_p(part.data_ptr()),
+              slices, ctypes.c_longlong(rows), D, ctypes.c_float(eps), int(res.dtype == torch.float32), st)
+    assert code == 0
+    return dsum, part.sum(0)
+
+
+def _noalloc(res, w, dout, dres, eps):
+    from state_space_models_neuron_b200.ops import native
+    lib = native.lib()
+    rows, D = res.shape
+    dsum = torch.empty_like(res)
+    dw = torch.full((D,), float("nan"), dtype=torch.float32, device="cuda")
+    fn = lib.ssm_add_rmsnorm_bwd_noalloc
+    fn.restype = ctypes.c_int
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    code = fn(ctypes.c_void_p(res.data_ptr()), ctypes.c_void_p(w.data_ptr()), ctypes.c_void_p(dout.data_ptr()),
+              ctypes.c_void_p(dres.data_ptr()), ctypes.c_void_p(dsum.data_ptr()), ctypes.c_void_p(dw.data_ptr()),
+              ctypes.c_longlong(rows), D, ctypes.c_float(eps), int(res.dtype == torch.float32), st)
+    return code, dsum, dw
+
+
+def test_no_alloc_entry_point_matches_regular_one_twice():
+    torch.cuda.set_device(0)
+    g = torch.Generator(device="cuda").manual_seed(11)
+    for rows, D, dtype in [(1000, 4096, torch.bfloat16), (37, 1024, torch.float32)]:
+        res = torch.randn(rows, D, device="cuda", generator=g).to(dtype)
+        dres = torch.randn(rows, D, device="cuda", generator=g).to(dtype)
+        dout = torch.randn(rows, D, device="cuda", generator=g).bfloat16()
+        w = (1 + 0.1 * torch.randn(D, device="cuda", generator=g)).bfloat16()
+        ref_dsum, ref_dw = _reference(res, w, dout, dres, 1e-5)
+        code, dsum, dw = _noalloc(res, w, dout, dres, 1e-5)
+        torch.cuda.synchronize()
+        assert code == 0
+        _close(dsum, ref_dsum)
+        _close(dw, ref_dw, atol=1e-3 * max(1.0, ref_dw.abs().max().item()))
+
+
+def test_no_alloc_entry_point_rejects_oversize():
+    torch.cuda.set_device(0)
+    D = 8192 + 8
+    res = torch.zeros(2, D, device="cuda", dtype=torch.bfloat16)
+    w = torch.ones(D, device="cuda", dtype=torch.bfloat16)
+    code, _, _ = _noalloc(res, w, res, res, 1e-5)
+    assert code == -4
