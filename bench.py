@@ -210,6 +210,9 @@ def main():
                              "far above the 126 MB L2"},
             "clocks": clocks, "gpu_launches": launches, "loss": last_loss,
         }
+        if tp > 1:
+            from state_space_models_neuron_b200.parallel import fused_ops
+            out["fused_kernel_launches"] = dict(fused_ops.CALLS)
         if e2e is not None:
             out["e2e"] = e2e
         print(json.dumps(out), flush=True)

@@ -10,6 +10,7 @@
 // This is the GEMM behind every Linear layer (the reference leaves those to the XLA compiler:
 // mamba2/mamba2_mixer.py:228,233; mamba2/modeling_mamba2.py:498).
 #include "common.cuh"
+#include <string.h>
 
 namespace ssm {
 
@@ -29,7 +30,61 @@ struct GemmParams {
   long long ldc32;
   int* status;
   int tiles_m, tiles_n;
+  int gemm_ctas;         // CTAs that run GEMM tiles (the grid may hold extra communication CTAs)
 };
+
+constexpr int MAX_RANKS = 8;
+struct PeerPtrs { void* p[MAX_RANKS]; };
+
+// Fusion of the GEMM with the tensor-parallel collectives over peer memory.
+//  * all-gather side (ag): the A operand is a gather buffer [nranks * rows_per_shard, K] in local memory that
+//    every rank fills by pushing its shard into all ranks' buffers.  The last `comm_ctas` CTAs of this grid do
+//    this rank's push (P2P stores) and publish flag[me] = seq on every rank; the TMA producer of the GEMM CTAs
+//    waits (bounded) for flag[shard] before the first load of a shard's rows and visits the local shard first.
+//  * reduce-scatter side (rs, epilogue mode 3): output rows belong to owner = row / rows_per_owner; each tile is
+//    TMA-stored into the owner's landing slot for this rank (one tensor map per owner, peer memory), remote
+//    owners first; when all of this rank's tiles for an owner have landed, flag[me] = seq is published there.
+struct GemmComm {
+  int nranks, me, seq;
+  // all-gather side
+  int ag, rows_per_shard, comm_ctas, ag_flag_base, ag_cols;
+  const int* ag_flags;                 // local flag array
+  const __nv_bfloat16* ag_src; long long ag_src_ld;
+  PeerPtrs ag_dst; long long ag_dst_ld;
+  PeerPtrs flag_ptrs;                  // every rank's flag array
+  int* ag_counter;
+  // reduce-scatter side
+  int rs, rows_per_owner, rs_flag_base;
+  int* rs_counters;                    // local [nranks]
+};
+struct RsMaps { CUtensorMap m[MAX_RANKS]; };
+
+__device__ __forceinline__ void st_release_sys_s32(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys_s32(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ bool wait_flag(const int* flag, int seq, int* status) {
+  if (ld_acquire_sys_s32(flag) >= seq) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (uint32_t i = 1;; ++i) {
+    if (ld_acquire_sys_s32(flag) >= seq) return true;
+    if ((i & 63u) == 0u) {
+      if (status != nullptr && *((volatile int*)status) != 0) return false;
+      if (global_timer_ns() - t0 > SSM_WAIT_NS) break;
+    }
+  }
+  if (status != nullptr) atomicCAS(status, 0, SSM_ERR_TIMEOUT_FLAG);
+  return false;
+}
+// m-tile visiting order: rotate so that `first_block` (a shard / owner index) comes first
+__device__ __forceinline__ int rotate_m(int tm, int tiles_m, int tiles_per_block, int first_block) {
+  int v = tm + first_block * tiles_per_block;
+  return v >= tiles_m ? v - tiles_m : v;
+}
 
 template <int BN, int STAGES>
 struct GemmSmem {
@@ -48,7 +103,8 @@ __device__ __forceinline__ float gelu_f(float x) {
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                  const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
+                  const __grid_constant__ CUtensorMap tmap_c, const GemmParams p, const GemmComm cm,
+                  const __grid_constant__ RsMaps rsm) {
   using L = GemmSmem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -61,6 +117,38 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int kblocks = (p.K + GEMM_BK - 1) / GEMM_BK;
+  const int nctas = p.gemm_ctas;
+
+  if ((int)blockIdx.x >= nctas) {
+    // ------------------------------------------------------------------ communication CTA (all-gather push)
+    const int ci = blockIdx.x - nctas;
+    const int vec_per_row = cm.ag_cols / 8;
+    const long long total = (long long)cm.rows_per_shard * vec_per_row;
+    const long long row_off = (long long)cm.me * cm.rows_per_shard;
+    for (long long i = (long long)ci * blockDim.x + threadIdx.x; i < total; i += (long long)cm.comm_ctas * blockDim.x) {
+      const long long r = i / vec_per_row;
+      const int c = (int)(i % vec_per_row) * 8;
+      const uint4 v = *reinterpret_cast<const uint4*>(cm.ag_src + r * cm.ag_src_ld + c);
+      #pragma unroll
+      for (int k = 0; k < MAX_RANKS; ++k) {
+        const int t = (cm.me + k) % MAX_RANKS;
+        if (t < cm.nranks)
+          *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(cm.ag_dst.p[t]) + (row_off + r) * cm.ag_dst_ld + c) = v;
+      }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const int done = atomicAdd(cm.ag_counter, 1) + 1;
+      if (done == cm.comm_ctas) {
+        __threadfence_system();
+        for (int t = 0; t < cm.nranks; ++t)
+          st_release_sys_s32(reinterpret_cast<int*>(cm.flag_ptrs.p[t]) + cm.ag_flag_base + cm.me, cm.seq);
+        *cm.ag_counter = 0;
+      }
+    }
+    return;
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -69,6 +157,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
     if (p.mode == 0) tma_prefetch_desc(&tmap_c);
+    if (p.mode == 3) for (int t = 0; t < cm.nranks; ++t) tma_prefetch_desc(&rsm.m[t]);
   }
   if (warp == 1) { tmem_alloc(tmem_slot, 2 * BN); tmem_relinquish(); }
   tc_fence_before_sync();
@@ -84,9 +173,21 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       #pragma unroll
       for (int s = 0; s < STAGES; ++s) armed[s] = -1;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % p.tiles_m) * GEMM_BM;
+      uint32_t shard_seen = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += nctas) {
+        int tm = tile % p.tiles_m;
+        if (cm.ag) tm = rotate_m(tm, p.tiles_m, cm.rows_per_shard / GEMM_BM, cm.me);
+        if (cm.rs) tm = rotate_m(tm, p.tiles_m, cm.rows_per_owner / GEMM_BM, (cm.me + 1) % cm.nranks);
+        const int m0 = tm * GEMM_BM;
         const int n0 = (tile / p.tiles_m) * BN;
+        if (cm.ag) {
+          const int shard = m0 / cm.rows_per_shard;
+          if (!(shard_seen & (1u << shard))) {
+            if (!wait_flag(cm.ag_flags + cm.ag_flag_base + shard, cm.seq, p.status)) { ok = false; break; }
+            fence_proxy_async_all();      // rows were written by generic-proxy stores (local or peer SMs)
+            shard_seen |= 1u << shard;
+          }
+        }
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status)) { ok = false; break; }
           uint8_t* sa = smem + stage * L::STAGE_BYTES;
@@ -128,7 +229,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       int stage = 0; uint32_t phase = 0;
       int acc = 0; uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += nctas) {
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, p.status)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -159,9 +260,20 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     int acc = 0; uint32_t acc_phase = 0;
     bool ok = true;
     int stores_issued = 0;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      const int m0 = (tile % p.tiles_m) * GEMM_BM;
+    int rs_count[MAX_RANKS];
+    #pragma unroll
+    for (int t = 0; t < MAX_RANKS; ++t) rs_count[t] = 0;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += nctas) {
+      int tm = tile % p.tiles_m;
+      if (cm.ag) tm = rotate_m(tm, p.tiles_m, cm.rows_per_shard / GEMM_BM, cm.me);
+      if (cm.rs) tm = rotate_m(tm, p.tiles_m, cm.rows_per_owner / GEMM_BM, (cm.me + 1) % cm.nranks);
+      const int m0 = tm * GEMM_BM;
       const int n0 = (tile / p.tiles_m) * BN;
+      const int owner = cm.rs ? m0 / cm.rows_per_owner : 0;
+      if (cm.rs && ok) {
+        #pragma unroll
+        for (int t = 0; t < MAX_RANKS; ++t) if (t == owner) rs_count[t] += 1;
+      }
       if (!mbar_wait(&tfull_bar[acc], acc_phase, p.status)) { ok = false; }
       {
         // the four epilogue warps must agree on the outcome before they meet at named barriers
@@ -186,7 +298,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           tmem_ld32(tmem_addr(tmem_base, q * 32, acc * BN + j * 64), v[0]);
           tmem_ld32(tmem_addr(tmem_base, q * 32, acc * BN + j * 64 + 32), v[1]);
           tmem_ld_wait();
-          if (p.mode == 0) {
+          if (p.mode == 0 || p.mode == 3) {
             uint8_t* buf = epi_buf + (stores_issued & 1) * EPI_BUF_BYTES;
             if (epi_tid == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
             asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -211,7 +323,11 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             }
             fence_proxy_async_smem();
             asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (epi_tid == 0) { tma_store_2d(&tmap_c, buf, nb, m0); tma_store_commit(); }
+            if (epi_tid == 0) {
+              if (p.mode == 0) tma_store_2d(&tmap_c, buf, nb, m0);
+              else tma_store_2d(&rsm.m[owner], buf, nb, m0 - owner * cm.rows_per_owner);
+              tma_store_commit();
+            }
             ++stores_issued;
           } else {
             const int r = m0 + row;
@@ -245,7 +361,26 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
-    if (epi_tid == 0) tma_store_wait_all();
+    if (epi_tid == 0) {
+      tma_store_wait_all();
+      if (cm.rs && ok) {
+        // all tiles of this CTA have landed: publish per owner once every CTA has reported its share
+        fence_proxy_async_all();
+        __threadfence_system();
+        const int per_owner = (cm.rows_per_owner / GEMM_BM) * p.tiles_n;
+        #pragma unroll
+        for (int t = 0; t < MAX_RANKS; ++t) {
+          if (t < cm.nranks && rs_count[t] > 0) {
+            const int done = atomicAdd(cm.rs_counters + t, rs_count[t]) + rs_count[t];
+            if (done == per_owner) {
+              cm.rs_counters[t] = 0;
+              __threadfence_system();
+              st_release_sys_s32(reinterpret_cast<int*>(cm.flag_ptrs.p[t]) + cm.rs_flag_base + cm.me, cm.seq);
+            }
+          }
+        }
+      }
+    }
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -257,7 +392,7 @@ static int g_num_sms = 0;
 
 template <int BN, int STAGES>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, GemmParams p,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, const GemmComm* comm = nullptr, const RsMaps* maps = nullptr) {
   using L = GemmSmem<BN, STAGES>;
   static bool configured = false;
   auto kern = gemm_bf16_tcgen05<BN, STAGES>;
@@ -269,8 +404,13 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
   p.tiles_m = (p.M + GEMM_BM - 1) / GEMM_BM;
   p.tiles_n = (p.N + BN - 1) / BN;
   const int tiles = p.tiles_m * p.tiles_n;
-  const int grid = tiles < g_num_sms ? tiles : g_num_sms;
-  kern<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(ta, tb, tc, p);
+  static GemmComm no_comm;       // zero-initialised: no fusion
+  static RsMaps no_maps;
+  GemmComm cm = comm ? *comm : no_comm;
+  int extra = (comm && cm.ag) ? cm.comm_ctas : 0;
+  const int avail = g_num_sms - extra;
+  p.gemm_ctas = tiles < avail ? tiles : avail;
+  kern<<<p.gemm_ctas + extra, GEMM_THREADS, L::TOTAL, stream>>>(ta, tb, tc, p, cm, maps ? *maps : no_maps);
   return (int)cudaGetLastError();
 }
 
@@ -313,6 +453,80 @@ extern "C" int ssm_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   p.M = M; p.N = N; p.K = K; p.a_mn = a_mn; p.b_mn = b_mn; p.mode = mode; p.act = act;
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.c32 = mode == 0 ? nullptr : reinterpret_cast<float*>(C);
-  p.ldc32 = ldc; p.status = status; p.tiles_m = 0; p.tiles_n = 0;
+  p.ldc32 = ldc; p.status = status; p.tiles_m = 0; p.tiles_n = 0; p.gemm_ctas = 0;
   return wide ? launch_gemm<256, 4>(ta, tb, tc, p, stream) : launch_gemm<128, 6>(ta, tb, tc, p, stream);
+}
+
+// GEMM fused with a tensor-parallel collective over peer memory (see GemmComm).
+//   ag = 1: A must be this rank's gather buffer [nranks * rows_per_shard, K] (= ag_dst_ptrs[me], row stride
+//           ag_dst_ld); ag_src is the local shard [rows_per_shard, K]; flag_ptrs[t] is rank t's flag array.
+//   rs = 1: mode is forced to 3; land_ptrs[o] is the base of the [rows_per_owner, N] slot this rank owns inside
+//           rank o's landing zone (row stride land_ld); C is ignored.
+// rows_per_shard / rows_per_owner must be multiples of 128 and M = nranks * rows.
+extern "C" int ssm_gemm_bf16_fused(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                                   long long ldb, long long ldc, int a_mn, int b_mn, int mode, const void* bias,
+                                   int act, int* status, cudaStream_t stream, int nranks, int me, int seq,
+                                   const void* const* flag_ptrs, int ag, int rows_per_shard, int comm_ctas,
+                                   int ag_flag_base, const void* ag_src, long long ag_src_ld,
+                                   const void* const* ag_dst_ptrs, long long ag_dst_ld, int* ag_counter, int rs,
+                                   int rows_per_owner, int rs_flag_base, const void* const* land_ptrs,
+                                   long long land_ld, int* rs_counters) {
+  using namespace ssm;
+  if (M <= 0 || N <= 0 || K <= 0 || nranks < 1 || nranks > MAX_RANKS || me < 0 || me >= nranks) return -SSM_ERR_BAD_ARG;
+  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
+    return -SSM_ERR_BAD_ARG;
+  if (ag && (a_mn || rows_per_shard % GEMM_BM || (long long)rows_per_shard * nranks != M || K % 8 || comm_ctas < 1 ||
+             ag_src_ld % 8 || ag_dst_ld % 8))
+    return -SSM_ERR_BAD_ARG;
+  if (rs && (rows_per_owner % GEMM_BM || (long long)rows_per_owner * nranks != M || land_ld % 8)) return -SSM_ERR_BAD_ARG;
+  if (rs) mode = 3;
+  if (mode == 0 && ((ldc % 8) || (reinterpret_cast<uintptr_t>(C) & 15))) return -SSM_ERR_BAD_ARG;
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const bool wide = N > 128;
+  const int BN = wide ? 256 : 128;
+  CUtensorMap ta, tb, tc;
+  int r;
+  if (!a_mn) r = make_tmap_2d_bf16(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, 64, 128);
+  else       r = make_tmap_2d_bf16(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, 64, 64);
+  if (r) return -100 - r;
+  if (!b_mn) r = make_tmap_2d_bf16(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, 64, BN);
+  else       r = make_tmap_2d_bf16(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, 64);
+  if (r) return -200 - r;
+  if (mode == 0) {
+    r = make_tmap_2d_bf16(&tc, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc * 2, 64, 128);
+    if (r) return -300 - r;
+  } else {
+    tc = ta;
+  }
+  RsMaps maps;
+  GemmComm cm;
+  memset(&cm, 0, sizeof(cm));
+  memset(&maps, 0, sizeof(maps));
+  cm.nranks = nranks; cm.me = me; cm.seq = seq;
+  for (int t = 0; t < MAX_RANKS; ++t) cm.flag_ptrs.p[t] = t < nranks ? const_cast<void*>(flag_ptrs[t]) : nullptr;
+  if (ag) {
+    cm.ag = 1; cm.rows_per_shard = rows_per_shard; cm.comm_ctas = comm_ctas; cm.ag_flag_base = ag_flag_base;
+    cm.ag_cols = K; cm.ag_flags = reinterpret_cast<const int*>(flag_ptrs[me]);
+    cm.ag_src = reinterpret_cast<const __nv_bfloat16*>(ag_src); cm.ag_src_ld = ag_src_ld;
+    for (int t = 0; t < MAX_RANKS; ++t) cm.ag_dst.p[t] = t < nranks ? const_cast<void*>(ag_dst_ptrs[t]) : nullptr;
+    cm.ag_dst_ld = ag_dst_ld; cm.ag_counter = ag_counter;
+  }
+  if (rs) {
+    cm.rs = 1; cm.rows_per_owner = rows_per_owner; cm.rs_flag_base = rs_flag_base; cm.rs_counters = rs_counters;
+    for (int t = 0; t < nranks; ++t) {
+      r = make_tmap_2d_bf16(&maps.m[t], land_ptrs[t], (uint64_t)N, (uint64_t)rows_per_owner, (uint64_t)land_ld * 2, 64, 128);
+      if (r) return -400 - r;
+    }
+  }
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.a_mn = a_mn; p.b_mn = b_mn; p.mode = mode; p.act = act;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.c32 = (mode == 1 || mode == 2) ? reinterpret_cast<float*>(C) : nullptr;
+  p.ldc32 = ldc; p.status = status; p.tiles_m = 0; p.tiles_n = 0; p.gemm_ctas = 0;
+  return wide ? launch_gemm<256, 4>(ta, tb, tc, p, stream, &cm, &maps)
+              : launch_gemm<128, 6>(ta, tb, tc, p, stream, &cm, &maps);
 }

@@ -12,7 +12,12 @@ def register(impl) -> None:
 
 
 def enabled_for(x) -> bool:
-    return bool(_ENABLED[0] and _IMPL[0] is not None and x.is_cuda and _IMPL[0].ready_for(x))
+    if not (_ENABLED[0] and x.is_cuda):
+        return False
+    if _IMPL[0] is None:
+        from . import fused_ops
+        fused_ops.install()
+    return bool(_IMPL[0].ready_for(x))
 
 
 def all_gather_linear(x, weight, bias=None):

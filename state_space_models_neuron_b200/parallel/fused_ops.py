@@ -1,0 +1,196 @@
+"""Column-/row-parallel linear layers whose sequence-parallel collective runs inside the GEMM kernel.
+
+    all_gather_linear      y = all_gather_seq(x_shard) W^T     one kernel: P2P push of the shard into every
+                           rank's gather buffer by dedicated CTAs + tcgen05 GEMM whose TMA producer waits per shard
+                           backward: dX = reduce_scatter_seq(dY W) as GEMM -> peer landing zones -> reduce;
+                                     dW += dY^T x_gathered
+    linear_reduce_scatter  y_shard = reduce_scatter_seq(x W^T)  GEMM whose epilogue TMA-stores every tile into the
+                           owning rank's landing zone + a reduce kernel that waits for the T sources
+                           backward: dX = all_gather_seq(dY_shard) W (same fused kernel), dW += dY_full^T x
+
+These replace the pairs (all-gather, GEMM) and (GEMM, reduce-scatter) that the reference leaves to
+neuronx-distributed's ColumnParallelLinear / RowParallelLinear with sequence parallelism
+(mamba2/mamba2_mixer.py:156-158,186-188,228,233).  The library-collective versions in `mappings.py` remain
+the measured baseline and the path for shapes the fused kernels do not take (batch > 1, shard rows not a
+multiple of 128).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import state as ps
+from . import symm
+from ..ops import cuda_ops
+from ..ops.cuda_ops import _P, _ceil8, _ll, _run, _st, status_tensor
+
+COMM_CTAS = 16
+CALLS = {"ag_gemm": 0, "gemm_rs": 0}     # how many fused kernels this process has launched
+_c = ctypes
+
+
+def _ws_for(rows_total: int, cols: int, device):
+    return symm.get_workspace(max(rows_total, 1), max(cols, 1), device)
+
+
+def ready_for(x: torch.Tensor) -> bool:
+    tp = ps.get_tensor_model_parallel_size()
+    if tp < 2 or tp > symm.MAX_RANKS or not x.is_cuda or x.dtype != torch.bfloat16 or x.dim() != 3:
+        return False
+    return x.shape[0] == 1
+
+
+def _fused_gemm(a, b, out, M, N, K, lda, ldb, ldc, a_mn, b_mn, mode, bias, ws, seq, ag=None, rs=None):
+    null = symm._ptr_array([])
+    ag = ag or dict(on=0, rows=0, base=0, src=None, src_ld=0, dst=null, dst_ld=0, counter=0)
+    rs = rs or dict(on=0, rows=0, base=0, land=null, ld=0, counters=0)
+    _run("ssm_gemm_bf16_fused", _P(a), _P(b), _P(out), M, N, K, _ll(lda), _ll(ldb), _ll(ldc), int(a_mn), int(b_mn), mode,
+         _P(bias), 0, _P(status_tensor(ws.device)), _st(), ws.nranks, ws.me, seq, ws.flag_ptr_array,
+         ag["on"], ag["rows"], COMM_CTAS, ag["base"], _P(ag["src"]), _ll(ag["src_ld"]), ag["dst"], _ll(ag["dst_ld"]),
+         _c.c_void_p(ag["counter"]), rs["on"], rs["rows"], rs["base"], rs["land"], _ll(rs["ld"]),
+         _c.c_void_p(rs["counters"]))
+
+
+def _ag_gemm(x_shard2, w, b_mn, bias, ws):
+    """gathered [T*Ls, K] (view of the workspace) and y = gathered @ (w^T or w)."""
+    Ls, K = x_shard2.shape
+    T = ws.nranks
+    M = T * Ls
+    N = w.shape[1] if b_mn else w.shape[0]
+    CALLS["ag_gemm"] += 1
+    seq = ws.next_seq()
+    par = seq & 1
+    off = ws.gather_offset(par)
+    gathered = ws.local_view(off, M, K)
+    y = torch.empty(M, _ceil8(N), dtype=torch.bfloat16, device=x_shard2.device)[:, :N]
+    if x_shard2.stride(1) != 1 or x_shard2.stride(0) % 8:
+        x_shard2 = x_shard2.contiguous()
+    _fused_gemm(gathered, w, y, M, N, K, K, w.stride(0), y.stride(0), False, b_mn, 0, bias, ws, seq,
+                ag=dict(on=1, rows=Ls, base=ws.flag_base(symm.KIND_AG, par), src=x_shard2, src_ld=x_shard2.stride(0),
+                        dst=ws.peer_ptrs(off), dst_ld=K, counter=ws.counter_ptr(0)))
+    return gathered, y
+
+
+def _gemm_rs(a2, w, b_mn, ws):
+    """reduce_scatter over rows of (a2 @ w^T) (or a2 @ w when b_mn): returns this rank's [Ls, N] block."""
+    M, K = a2.shape
+    T = ws.nranks
+    Ls = M // T
+    N = w.shape[1] if b_mn else w.shape[0]
+    CALLS["gemm_rs"] += 1
+    seq = ws.next_seq()
+    par = seq & 1
+    off = ws.land_offset(par)
+    slot_bytes = Ls * N * 2
+    land = symm._ptr_array([p + off + ws.me * slot_bytes for p in ws.base_ptrs])
+    if a2.stride(1) != 1 or a2.stride(0) % 8:
+        a2 = a2.contiguous()
+    _fused_gemm(a2, w, None, M, N, K, a2.stride(0), w.stride(0), 0, False, b_mn, 3, None, ws, seq,
+                rs=dict(on=1, rows=Ls, base=ws.flag_base(symm.KIND_RS, par), land=land, ld=N,
+                        counters=ws.counter_ptr(8)))
+    out = torch.empty(Ls, N, dtype=torch.bfloat16, device=a2.device)
+    local_land = ws.local_view(off, T * Ls, N)
+    _run("ssm_reduce_partials", _P(local_land), _ll(N), _ll(Ls * N), _P(out), _ll(N), Ls, N, T,
+         _c.c_void_p(ws.base_ptrs[ws.me]), ws.flag_base(symm.KIND_RS, par), seq, _P(status_tensor(ws.device)),
+         min(148, max(1, Ls * N // 8 // 256)), _st())
+    return out
+
+
+def _shape_ok(Ls, K, N, ws):
+    return Ls % 128 == 0 and K % 8 == 0 and N % 8 == 0 and ws is not None
+
+
+class _AllGatherLinear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias, ws):
+        Ls, K = x.shape[1], x.shape[2]
+        gathered, y = _ag_gemm(x.reshape(Ls, K), w, False, bias, ws)
+        xg = gathered.clone()                      # kept for dW; the workspace buffer is reused two calls later
+        ctx.save_for_backward(xg, w)
+        ctx.ws, ctx.has_bias = ws, bias is not None
+        return y.reshape(1, y.shape[0], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        xg, w = ctx.saved_tensors
+        ws = ctx.ws
+        N = w.shape[0]
+        dy2 = dy.reshape(-1, N)
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = _gemm_rs(dy2, w, True, ws)         # reduce_scatter(dY W)
+            dx = dx.reshape(1, dx.shape[0], dx.shape[1])
+        if ctx.needs_input_grad[1]:
+            mg = getattr(w, "main_grad", None)
+            if mg is not None and mg.dtype == torch.float32:
+                stale = getattr(w, "grad_stale", False)
+                cuda_ops.gemm(dy2, xg, a_mn=True, b_mn=True, out=mg, accumulate=not stale)
+                w.grad_stale = False
+            else:
+                dw = cuda_ops.gemm(dy2, xg, a_mn=True, b_mn=True).contiguous()
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.float().sum(0).to(dy.dtype)
+        return dx, dw, db, None
+
+
+class _LinearReduceScatter(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, ws):
+        L, K = x.shape[1], x.shape[2]
+        x2 = x.reshape(L, K)
+        y = _gemm_rs(x2, w, False, ws)
+        ctx.save_for_backward(x2, w)
+        ctx.ws = ws
+        return y.reshape(1, y.shape[0], y.shape[1])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        ws = ctx.ws
+        Ls, N = dy.shape[1], dy.shape[2]
+        dyg, dx = _ag_gemm(dy.reshape(Ls, N), w, True, None, ws)      # all_gather(dY) W
+        dw = None
+        if ctx.needs_input_grad[1]:
+            mg = getattr(w, "main_grad", None)
+            if mg is not None and mg.dtype == torch.float32:
+                stale = getattr(w, "grad_stale", False)
+                cuda_ops.gemm(dyg, x2, a_mn=True, b_mn=True, out=mg, accumulate=not stale)
+                w.grad_stale = False
+            else:
+                dw = cuda_ops.gemm(dyg, x2, a_mn=True, b_mn=True).contiguous()
+        return dx.reshape(1, dx.shape[0], dx.shape[1]), dw, None
+
+
+class _Impl:
+    @staticmethod
+    def ready_for(x):
+        return ready_for(x)
+
+    @staticmethod
+    def all_gather_linear(x, w, bias=None):
+        T = ps.get_tensor_model_parallel_size()
+        Ls, K = x.shape[1], x.shape[2]
+        ws = _ws_for(T * Ls, K, x.device)
+        if not _shape_ok(Ls, K, w.shape[0], ws) or not ws.fits(T * Ls, K):
+            from . import mappings as mp
+            from .. import ops
+            return ops.linear(mp.gather_from_sequence_parallel_region(x, True), w, bias)
+        return _AllGatherLinear.apply(x, w, bias, ws)
+
+    @staticmethod
+    def linear_reduce_scatter(x, w):
+        T = ps.get_tensor_model_parallel_size()
+        L, K = x.shape[1], x.shape[2]
+        N = w.shape[0]
+        ws = _ws_for(L, N, x.device)
+        if L % T or not _shape_ok(L // T, K, N, ws) or not ws.fits(L, N):
+            from . import mappings as mp
+            from .. import ops
+            return mp.reduce_scatter_to_sequence_parallel_region(ops.linear(x, w, None))
+        return _LinearReduceScatter.apply(x, w, ws)
+
+
+def install() -> None:
+    from . import fused
+    fused.register(_Impl)

@@ -1,0 +1,81 @@
+"""Run under torchrun on N GPUs: a small bf16 model at TP=N (+SP, +ZeRO-1) must reproduce the loss curve of the
+same model at TP=1 (built on every rank from the same seeds).  Exit code 0 on success."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from state_space_models_neuron_b200 import parallel as nxd  # noqa: E402
+from state_space_models_neuron_b200.models import (Mamba2Config, Mamba2ForCausalLM, Mamba2HybridConfig,  # noqa: E402
+                                                   Mamba2HybridForCausalLM)
+from state_space_models_neuron_b200.ops import cuda_ops  # noqa: E402
+from state_space_models_neuron_b200.parallel import state as ps  # noqa: E402
+
+
+def build(tp, sp, hybrid, fused):
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel(tp, backend="nccl")
+    kw = dict(num_heads=16, head_dim=64, vocab_size=2048, hidden_size=512, state_size=128, num_hidden_layers=2,
+              n_groups=8, tie_word_embeddings=True, initializer_range=0.02, sequence_parallel_enabled=sp,
+              dtype=torch.bfloat16)
+    if hybrid:
+        mc = Mamba2HybridConfig(**{**kw, "num_hidden_layers": 4}, attn_num_heads=8, attn_head_dim=128,
+                                attn_key_value_heads=8, mlp_hidden_size=1024, hybrid_attention_ratio=0.25,
+                                hybrid_mlp_ratio=0.25, residual_in_fp32=False)
+        cls = Mamba2HybridForCausalLM
+    else:
+        mc, cls = Mamba2Config(**kw), Mamba2ForCausalLM
+    cfg = nxd.parallel_config(tp, {"zero_one_enabled": True}, sequence_parallel=sp, init_seed=3, fused_comm=fused)
+    model = nxd.initialize_parallel_model(cfg, lambda: cls(mc, device="cuda").to(torch.bfloat16))
+    opt = nxd.initialize_parallel_optimizer(cfg, nxd.AdamW_FP32OptimParams,
+                                            [{"params": list(model.parameters()), "weight_decay": 0.1}], lr=1e-3)
+    return model, opt
+
+
+def run(model, opt, ids, steps):
+    losses = []
+    for _ in range(steps):
+        opt.zero_grad()
+        loss = model(input_ids=ids, labels=ids, return_logits=False).loss
+        loss.backward()
+        opt.step()
+        losses.append(loss.item())
+    return losses
+
+
+def main():
+    hybrid = "--hybrid" in sys.argv
+    fused = "--fused" in sys.argv
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    world = dist.get_world_size()
+    g = torch.Generator().manual_seed(0)
+    shape = (1, 1024) if fused else (2, 512)      # the fused kernels take batch 1 (sequence-sharded rows)
+    ids = torch.randint(0, 2048, shape, generator=g).cuda()
+    m1, o1 = build(1, False, hybrid, False)
+    ref = run(m1, o1, ids, 3)
+    del m1, o1
+    mt, ot = build(world, True, hybrid, fused)
+    got = run(mt, ot, ids, 3)
+    torch.cuda.synchronize()
+    cuda_ops.check_status()
+    ok = all(abs(a - b) < 0.05 for a, b in zip(ref, got))
+    if fused:
+        from state_space_models_neuron_b200.parallel import fused_ops
+        ok = ok and fused_ops.CALLS["ag_gemm"] > 0 and fused_ops.CALLS["gemm_rs"] > 0
+        if dist.get_rank() == 0:
+            print("fused kernel launches", fused_ops.CALLS)
+    if dist.get_rank() == 0:
+        print("TP=1 losses", ref)
+        print(f"TP={world} losses", got, "fused" if fused else "nccl")
+        print("OK" if ok else "MISMATCH")
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.exit(0 if ok else 1)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,26 @@
+"""Multi-GPU equivalence (needs >= 2 GPUs): TP=N+SP+ZeRO-1 in bf16 follows the TP=1 loss curve."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _torchrun(n, *extra, port=29611):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "gpu_tp_check.py"), *extra]
+    return subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+
+
+@pytest.mark.parametrize("extra", [(), ("--fused",)])
+def test_tp_matches_single_gpu(extra):
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    r = _torchrun(min(n, 8) if n in (2, 4, 8) else 2, *extra, port=29611 + len(extra))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
