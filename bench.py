@@ -91,6 +91,8 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="override layer count (profiling only)")
     ap.add_argument("--fused_comm", default="on", choices=["on", "off"])
     ap.add_argument("--no_e2e", action="store_true")
+    ap.add_argument("--graph", default="on", choices=["on", "off"],
+                    help="replay the whole training step as one CUDA graph (off = eager launches)")
     ap.add_argument("--profile_mode", action="store_true",
                     help="allow fewer than 3 warm-up steps (for profiler captures; not a benchmark value)")
     args = ap.parse_args()
@@ -120,6 +122,9 @@ def main():
     if args.layers:
         m["num_hidden_layers"] = args.layers
     fused = args.fused_comm == "on" and args.impl == "ours"
+    if args.impl == "baseline":
+        from baseline import nccl_cublas
+        nccl_cublas.enable()
     cfg = nxd.parallel_config(
         tensor_parallel_size=tp, optimizer_config={"zero_one_enabled": True, "grad_clipping": True, "max_grad_norm": 1.0},
         sequence_parallel=tp > 1, fused_comm=fused, init_seed=0)
@@ -140,12 +145,21 @@ def main():
     host = [torch.randint(0, V, (B, L), generator=g).pin_memory() for _ in range(n_batches)]
     dev = [h.cuda(non_blocking=True) for h in host]
 
-    def step(ids):
+    def eager_step(ids):
         loss = model(input_ids=ids, labels=ids, return_logits=False).loss
         loss.backward()
         opt.step()
         opt.zero_grad()
         return loss
+
+    step, gstep, graph_note = eager_step, None, "off"
+    if args.graph == "on" and args.impl == "ours":
+        from state_space_models_neuron_b200.parallel.graph import GraphedTrainStep
+        gstep = GraphedTrainStep(model, opt, {"input_ids": dev[0], "labels": dev[0]})
+        graph_note = "whole step (fwd+bwd+optimizer+collectives) captured once, replayed per step"
+
+        def step(ids):
+            return gstep({"input_ids": ids, "labels": ids})
 
     def barrier():
         if world > 1:
@@ -162,12 +176,16 @@ def main():
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
+    h0 = time.perf_counter()
     for i in range(args.steps):
         loss = step(dev[args.warmup + i])
+    host_issue_ms = (time.perf_counter() - h0) * 1e3 / args.steps     # host time to enqueue one step (no sync)
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1)
     launches = cuda_ops.launch_count() - launches0
+    if gstep is not None:
+        launches = gstep.native_launches_per_step * args.steps
     clocks = sampler.stop()
     last_loss = float(loss.detach())
     cuda_ops.check_status()
@@ -205,10 +223,10 @@ def main():
             "impl": args.impl if args.impl != "ours" else "ours",
             "config": {"model": m["name"], "layers": m["num_hidden_layers"], "global_batch": B * dp, "seq_len": L,
                        "parallelism": f"tp{tp}" + ("+sp" if tp > 1 else "") + "+zero1(dp%d)" % dp,
-                       "fused_comm": fused,
+                       "fused_comm": fused, "cuda_graph": graph_note,
                        "l2": "no explicit flush: each step streams >100 GB of weights, gradients and optimizer state, "
                              "far above the 126 MB L2"},
-            "clocks": clocks, "gpu_launches": launches, "loss": last_loss,
+            "clocks": clocks, "gpu_launches": launches, "loss": last_loss, "host_issue_ms_per_step": host_issue_ms,
         }
         if tp > 1:
             from state_space_models_neuron_b200.parallel import fused_ops

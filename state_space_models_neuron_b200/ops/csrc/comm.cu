@@ -51,8 +51,9 @@ __device__ __forceinline__ bool wait_flag_ge(const int* flag, int seq, int* stat
 // ---------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 push_shard_kernel(const __nv_bfloat16* __restrict__ src, long long src_ld, PeerPtrs dst, long long dst_ld,
-                  long long row_off, int rows, int cols, int nranks, int me, PeerPtrs flags, int flag_base, int seq,
-                  int* counter) {
+                  long long row_off, int rows, int cols, int nranks, int me, PeerPtrs flags, int flag_base, int seq_off,
+                  const int* seq_base, int* counter) {
+  const int seq = seq_off + (seq_base ? *seq_base : 0);
   const int vec_per_row = cols / 8;
   const long long total = (long long)rows * vec_per_row;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -85,7 +86,8 @@ push_shard_kernel(const __nv_bfloat16* __restrict__ src, long long src_ld, PeerP
 __global__ void __launch_bounds__(256)
 reduce_partials_kernel(const __nv_bfloat16* __restrict__ land, long long ld, long long slot_stride,
                        __nv_bfloat16* __restrict__ out, long long out_ld, int rows, int cols, int nranks,
-                       const int* flags, int flag_base, int seq, int* status) {
+                       const int* flags, int flag_base, int seq_off, const int* seq_base, int* status) {
+  const int seq = seq_off + (seq_base ? *seq_base : 0);
   __shared__ int s_ok;
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
@@ -119,7 +121,8 @@ reduce_partials_kernel(const __nv_bfloat16* __restrict__ land, long long ld, lon
 // ---------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 small_allreduce_kernel(float* __restrict__ data, int n, int n_max, PeerPtrs slots, PeerPtrs flags, int flag_base,
-                       int nranks, int me, int seq, int op, int* status) {
+                       int nranks, int me, int seq_off, const int* seq_base, int op, int* status) {
+  const int seq = seq_off + (seq_base ? *seq_base : 0);
   __shared__ int s_ok;
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     const float v = data[i];
@@ -148,6 +151,10 @@ small_allreduce_kernel(float* __restrict__ data, int n, int n_max, PeerPtrs slot
   }
 }
 
+// *base += stride  (one thread); launched once per training step so that sequence numbers grow across replays of
+// a captured CUDA graph although every kernel node keeps its fixed offset
+__global__ void advance_counter_kernel(int* base, int stride) { *base += stride; }
+
 }  // namespace ssm
 
 using namespace ssm;
@@ -162,29 +169,34 @@ extern "C" int ssm_comm_max_ranks() { return MAX_RANKS; }
 
 extern "C" int ssm_push_shard(const void* src, long long src_ld, const void* const* dst_ptrs, long long dst_ld,
                               long long row_off, int rows, int cols, int nranks, int me, const void* const* flag_ptrs,
-                              int flag_base, int seq, int* counter, int blocks, cudaStream_t st) {
+                              int flag_base, int seq, const int* seq_base, int* counter, int blocks, cudaStream_t st) {
   if (cols % 8 || src_ld % 8 || dst_ld % 8 || nranks > MAX_RANKS || nranks < 1) return -SSM_ERR_BAD_ARG;
   push_shard_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(src), src_ld,
                                             to_peers(dst_ptrs, nranks), dst_ld, row_off, rows, cols, nranks, me,
-                                            to_peers(flag_ptrs, nranks), flag_base, seq, counter);
+                                            to_peers(flag_ptrs, nranks), flag_base, seq, seq_base, counter);
   return (int)cudaGetLastError();
 }
 
 extern "C" int ssm_reduce_partials(const void* land, long long ld, long long slot_stride, void* out, long long out_ld,
                                    int rows, int cols, int nranks, const void* flags, int flag_base, int seq,
-                                   int* status, int blocks, cudaStream_t st) {
+                                   const int* seq_base, int* status, int blocks, cudaStream_t st) {
   if (cols % 8 || ld % 8 || out_ld % 8 || slot_stride % 8 || nranks > MAX_RANKS) return -SSM_ERR_BAD_ARG;
   reduce_partials_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(land), ld, slot_stride,
                                                  reinterpret_cast<__nv_bfloat16*>(out), out_ld, rows, cols, nranks,
-                                                 reinterpret_cast<const int*>(flags), flag_base, seq, status);
+                                                 reinterpret_cast<const int*>(flags), flag_base, seq, seq_base, status);
   return (int)cudaGetLastError();
 }
 
 extern "C" int ssm_small_allreduce(void* data, int n, int n_max, const void* const* slot_ptrs,
-                                   const void* const* flag_ptrs, int flag_base, int nranks, int me, int seq, int op,
-                                   int* status, cudaStream_t st) {
+                                   const void* const* flag_ptrs, int flag_base, int nranks, int me, int seq,
+                                   const int* seq_base, int op, int* status, cudaStream_t st) {
   if (n > n_max || nranks > MAX_RANKS) return -SSM_ERR_BAD_ARG;
   small_allreduce_kernel<<<1, 256, 0, st>>>(reinterpret_cast<float*>(data), n, n_max, to_peers(slot_ptrs, nranks),
-                                            to_peers(flag_ptrs, nranks), flag_base, nranks, me, seq, op, status);
+                                            to_peers(flag_ptrs, nranks), flag_base, nranks, me, seq, seq_base, op, status);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ssm_advance_counter(int* base, int stride, cudaStream_t st) {
+  advance_counter_kernel<<<1, 1, 0, st>>>(base, stride);
   return (int)cudaGetLastError();
 }

@@ -525,8 +525,14 @@ __global__ void __launch_bounds__(256)
 adamw_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
              const GT* __restrict__ g, __nv_bfloat16* __restrict__ out16, float* __restrict__ out32,
              long long n4, const float* __restrict__ clip, float lr, float b1, float b2, float eps,
-             float wd, float bc1, float bc2) {
+             float wd, float bc1, float bc2, const float* __restrict__ lr_dev, const int* __restrict__ step_dev) {
   const float c = clip ? *clip : 1.f;
+  if (lr_dev != nullptr) lr = *lr_dev;                   // device-resident hyper-parameters: a captured graph
+  if (step_dev != nullptr) {                             // replays with the current learning rate and step
+    const float st = (float)(*step_dev);
+    bc1 = 1.f - powf(b1, st);
+    bc2 = 1.f - powf(b2, st);
+  }
   const float decay = 1.f - lr * wd, ib1 = 1.f / bc1, ib2 = 1.f / bc2;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
     const float4 gi = Vec4<GT>::load(g + i * 4);
@@ -563,6 +569,62 @@ sumsq_kernel(const GT* __restrict__ g, long long n4, float* __restrict__ total) 
   }
   s = block_sum(s, red);
   if (threadIdx.x == 0) atomicAdd(total, s);
+}
+
+// =====================================================================================
+// finalisation of small parameter gradients: column sums of per-CTA partial buffers written straight into the
+// fp32 main-gradient buffers (store or accumulate per parameter), so the mixer backward issues one launch
+// instead of ~20 reduction / cast / copy kernels
+// =====================================================================================
+struct SmallGradArgs {
+  const float* conv_part; int T1, C;          // [T1][C][5]  (dw0..dw3, db)
+  const float* gated_part; int S, d_in;       // [S][d_in]
+  const float* hpart; int T2, Hv, H;          // [T2][Hv][3] (dA, dD, d dt_bias)
+  const float* A;                             // [H]  (dA_log = dA * A)
+  float *g_conv_w, *g_conv_b, *g_norm_w, *g_A_log, *g_D, *g_dt_bias;
+  int acc_mask;                               // bit i set: add into parameter i's buffer, else overwrite
+};
+
+__device__ __forceinline__ void put(float* dst, float v, bool acc) { *dst = acc ? *dst + v : v; }
+
+__global__ void __launch_bounds__(256) mixer_small_grads_kernel(const SmallGradArgs a) {
+  const long long n_conv = (long long)a.C * 5, n_gated = a.d_in, n_h = (long long)a.H * 3;
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n_conv) {
+    float s = 0.f;
+    for (int t = 0; t < a.T1; ++t) s += a.conv_part[(long long)t * n_conv + i];
+    const int c = (int)(i / 5), k = (int)(i % 5);
+    if (k < 4) put(a.g_conv_w + c * 4 + k, s, a.acc_mask & 1);
+    else if (a.g_conv_b) put(a.g_conv_b + c, s, a.acc_mask & 2);
+    return;
+  }
+  i -= n_conv;
+  if (i < n_gated) {
+    float s = 0.f;
+    for (int t = 0; t < a.S; ++t) s += a.gated_part[(long long)t * n_gated + i];
+    put(a.g_norm_w + i, s, a.acc_mask & 4);
+    return;
+  }
+  i -= n_gated;
+  if (i < n_h) {
+    const int h = (int)(i / 3), which = (int)(i % 3);
+    const int psplit = a.Hv / a.H;
+    float s = 0.f;
+    for (int t = 0; t < a.T2; ++t)
+      for (int ps = 0; ps < psplit; ++ps) s += a.hpart[((long long)t * a.Hv + h * psplit + ps) * 3 + which];
+    if (which == 0) put(a.g_A_log + h, s * a.A[h], a.acc_mask & 8);
+    else if (which == 1) put(a.g_D + h, s, a.acc_mask & 16);
+    else put(a.g_dt_bias + h, s, a.acc_mask & 32);
+  }
+}
+
+// dst[c] (+)= sum_s part[s][c]
+__global__ void __launch_bounds__(256) colsum_kernel(const float* __restrict__ part, int S, int n, float* dst, int acc) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= n) return;
+  float s = 0.f;
+  for (int t = 0; t < S; ++t) s += part[(long long)t * n + c];
+  dst[c] = acc ? dst[c] + s : s;
 }
 
 }  // namespace ssm
@@ -687,7 +749,9 @@ extern "C" int ssm_ce_backward(const void* logits, long long ld, int is_fp32, co
 
 extern "C" int ssm_adamw(void* master, void* m, void* v, const void* g, int g_fp32, void* out16, void* out32,
                          long long n, const void* clip, float lr, float b1, float b2, float eps, float wd, int step,
-                         cudaStream_t st) {
+                         const void* lr_dev, const void* step_dev, cudaStream_t st) {
+  auto lrd = reinterpret_cast<const float*>(lr_dev);
+  auto std_ = reinterpret_cast<const int*>(step_dev);
   const float bc1 = 1.f - powf(b1, (float)step), bc2 = 1.f - powf(b2, (float)step);
   if (n % 4 || (reinterpret_cast<uintptr_t>(master) | reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v) |
                 reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(out32)) & 15 ||
@@ -697,8 +761,8 @@ extern "C" int ssm_adamw(void* master, void* m, void* v, const void* g, int g_fp
   const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
   auto M = reinterpret_cast<float*>(master); auto mm = reinterpret_cast<float*>(m); auto vv = reinterpret_cast<float*>(v);
   auto cl = reinterpret_cast<const float*>(clip);
-  if (g_fp32) adamw_kernel<float><<<blocks, 256, 0, st>>>(M, mm, vv, reinterpret_cast<const float*>(g), BFM(out16), reinterpret_cast<float*>(out32), n, cl, lr, b1, b2, eps, wd, bc1, bc2);
-  else adamw_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(M, mm, vv, BF(g), BFM(out16), reinterpret_cast<float*>(out32), n, cl, lr, b1, b2, eps, wd, bc1, bc2);
+  if (g_fp32) adamw_kernel<float><<<blocks, 256, 0, st>>>(M, mm, vv, reinterpret_cast<const float*>(g), BFM(out16), reinterpret_cast<float*>(out32), n, cl, lr, b1, b2, eps, wd, bc1, bc2, lrd, std_);
+  else adamw_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(M, mm, vv, BF(g), BFM(out16), reinterpret_cast<float*>(out32), n, cl, lr, b1, b2, eps, wd, bc1, bc2, lrd, std_);
   return (int)cudaGetLastError();
 }
 extern "C" int ssm_sumsq(const void* g, int g_fp32, long long n, void* total, cudaStream_t st) {
@@ -769,5 +833,28 @@ extern "C" int ssm_add_rmsnorm_bwd_noalloc(const void* res, const void* w, const
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   noalloc_colsum_kernel<<<(D + 255) / 256, 256, 0, st>>>(reinterpret_cast<float*>(dw), slices, D);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ssm_mixer_small_grads(const void* conv_part, int T1, int C, const void* gated_part, int S, int d_in,
+                                     const void* hpart, int T2, int Hv, int H, const void* A, void* g_conv_w,
+                                     void* g_conv_b, void* g_norm_w, void* g_A_log, void* g_D, void* g_dt_bias,
+                                     int acc_mask, cudaStream_t st) {
+  SmallGradArgs a;
+  a.conv_part = reinterpret_cast<const float*>(conv_part); a.T1 = T1; a.C = C;
+  a.gated_part = reinterpret_cast<const float*>(gated_part); a.S = S; a.d_in = d_in;
+  a.hpart = reinterpret_cast<const float*>(hpart); a.T2 = T2; a.Hv = Hv; a.H = H;
+  a.A = reinterpret_cast<const float*>(A);
+  a.g_conv_w = reinterpret_cast<float*>(g_conv_w); a.g_conv_b = reinterpret_cast<float*>(g_conv_b);
+  a.g_norm_w = reinterpret_cast<float*>(g_norm_w); a.g_A_log = reinterpret_cast<float*>(g_A_log);
+  a.g_D = reinterpret_cast<float*>(g_D); a.g_dt_bias = reinterpret_cast<float*>(g_dt_bias);
+  a.acc_mask = acc_mask;
+  const long long n = (long long)C * 5 + d_in + (long long)H * 3;
+  mixer_small_grads_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(a);
+  return (int)cudaGetLastError();
+}
+extern "C" int ssm_colsum(const void* part, int S, int n, void* dst, int acc, cudaStream_t st) {
+  colsum_kernel<<<(n + 255) / 256, 256, 0, st>>>(reinterpret_cast<const float*>(part), S, n,
+                                                 reinterpret_cast<float*>(dst), acc);
   return (int)cudaGetLastError();
 }

@@ -45,7 +45,8 @@ struct PeerPtrs { void* p[MAX_RANKS]; };
 //    TMA-stored into the owner's landing slot for this rank (one tensor map per owner, peer memory), remote
 //    owners first; when all of this rank's tiles for an owner have landed, flag[me] = seq is published there.
 struct GemmComm {
-  int nranks, me, seq;
+  int nranks, me, seq;          // sequence number of this call = *seq_base + seq (seq_base may be null)
+  const int* seq_base;          // device counter advanced once per training step (keeps CUDA-graph replays unique)
   // all-gather side
   int ag, rows_per_shard, comm_ctas, ag_flag_base, ag_cols;
   const int* ag_flags;                 // local flag array
@@ -118,6 +119,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int kblocks = (p.K + GEMM_BK - 1) / GEMM_BK;
   const int nctas = p.gemm_ctas;
+  const int seqv = cm.seq + (cm.seq_base != nullptr ? *cm.seq_base : 0);
 
   if ((int)blockIdx.x >= nctas) {
     // ------------------------------------------------------------------ communication CTA (all-gather push)
@@ -143,7 +145,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       if (done == cm.comm_ctas) {
         __threadfence_system();
         for (int t = 0; t < cm.nranks; ++t)
-          st_release_sys_s32(reinterpret_cast<int*>(cm.flag_ptrs.p[t]) + cm.ag_flag_base + cm.me, cm.seq);
+          st_release_sys_s32(reinterpret_cast<int*>(cm.flag_ptrs.p[t]) + cm.ag_flag_base + cm.me, seqv);
         *cm.ag_counter = 0;
       }
     }
@@ -156,7 +158,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
-    if (p.mode == 0) tma_prefetch_desc(&tmap_c);
+    if (p.mode != 3) tma_prefetch_desc(&tmap_c);
     if (p.mode == 3) for (int t = 0; t < cm.nranks; ++t) tma_prefetch_desc(&rsm.m[t]);
   }
   if (warp == 1) { tmem_alloc(tmem_slot, 2 * BN); tmem_relinquish(); }
@@ -183,7 +185,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         if (cm.ag) {
           const int shard = m0 / cm.rows_per_shard;
           if (!(shard_seen & (1u << shard))) {
-            if (!wait_flag(cm.ag_flags + cm.ag_flag_base + shard, cm.seq, p.status)) { ok = false; break; }
+            if (!wait_flag(cm.ag_flags + cm.ag_flag_base + shard, seqv, p.status)) { ok = false; break; }
             fence_proxy_async_all();      // rows were written by generic-proxy stores (local or peer SMs)
             shard_seen |= 1u << shard;
           }
@@ -330,28 +332,30 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             }
             ++stores_issued;
           } else {
-            const int r = m0 + row;
-            if (r < p.M) {
-              float* dst = p.c32 + (long long)r * p.ldc32 + nb;
+            // fp32 output: 32 columns (128 bytes) per staging block, TMA store or TMA reduce-add (grad accumulation)
+            #pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              if (nb + h * 32 >= p.N) break;
+              uint8_t* buf = epi_buf + (stores_issued & 1) * EPI_BUF_BYTES;
+              if (epi_tid == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+              asm volatile("bar.sync 1, 128;" ::: "memory");
               #pragma unroll
-              for (int h = 0; h < 2; ++h) {
-                #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                  const int col = nb + h * 32 + c * 4;
-                  float4 o = make_float4(__uint_as_float(v[h][c * 4]), __uint_as_float(v[h][c * 4 + 1]),
-                                         __uint_as_float(v[h][c * 4 + 2]), __uint_as_float(v[h][c * 4 + 3]));
-                  float* d4 = dst + h * 32 + c * 4;
-                  if (col + 3 < p.N && ((reinterpret_cast<uintptr_t>(d4) & 15) == 0)) {
-                    if (p.mode == 1) *reinterpret_cast<float4*>(d4) = o;
-                    else asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(d4), "f"(o.x), "f"(o.y),
-                                      "f"(o.z), "f"(o.w) : "memory");
-                  } else {
-                    const float e4[4] = {o.x, o.y, o.z, o.w};
-                    for (int e = 0; e < 4; ++e)
-                      if (col + e < p.N) { if (p.mode == 1) d4[e] = e4[e]; else atomicAdd(d4 + e, e4[e]); }
-                  }
+              for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<uint4*>(buf + sw128_offset(row, c)) =
+                    make_uint4(v[h][c * 4], v[h][c * 4 + 1], v[h][c * 4 + 2], v[h][c * 4 + 3]);
+              fence_proxy_async_smem();
+              asm volatile("bar.sync 1, 128;" ::: "memory");
+              if (epi_tid == 0) {
+                if (p.mode == 1) {
+                  tma_store_2d(&tmap_c, buf, nb + h * 32, m0);
+                } else {
+                  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                               ::"l"(reinterpret_cast<uint64_t>(&tmap_c)), "r"(smem_u32(buf)), "r"(nb + h * 32), "r"(m0)
+                               : "memory");
                 }
+                tma_store_commit();
               }
+              ++stores_issued;
             }
           }
         }
@@ -375,7 +379,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             if (done == per_owner) {
               cm.rs_counters[t] = 0;
               __threadfence_system();
-              st_release_sys_s32(reinterpret_cast<int*>(cm.flag_ptrs.p[t]) + cm.rs_flag_base + cm.me, cm.seq);
+              st_release_sys_s32(reinterpret_cast<int*>(cm.flag_ptrs.p[t]) + cm.rs_flag_base + cm.me, seqv);
             }
           }
         }
@@ -447,7 +451,9 @@ extern "C" int ssm_gemm_bf16(const void* A, const void* B, void* C, int M, int N
     r = make_tmap_2d_bf16(&tc, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc * 2, 64, 128);
     if (r) return -300 - r;
   } else {
-    tc = ta;
+    if ((ldc % 4) || (reinterpret_cast<uintptr_t>(C) & 15)) return -SSM_ERR_BAD_ARG;
+    r = make_tmap_2d(&tc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc * 4, 32, 128);
+    if (r) return -300 - r;
   }
   GemmParams p;
   p.M = M; p.N = N; p.K = K; p.a_mn = a_mn; p.b_mn = b_mn; p.mode = mode; p.act = act;
@@ -466,7 +472,7 @@ extern "C" int ssm_gemm_bf16(const void* A, const void* B, void* C, int M, int N
 extern "C" int ssm_gemm_bf16_fused(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
                                    long long ldb, long long ldc, int a_mn, int b_mn, int mode, const void* bias,
                                    int act, int* status, cudaStream_t stream, int nranks, int me, int seq,
-                                   const void* const* flag_ptrs, int ag, int rows_per_shard, int comm_ctas,
+                                   const int* seq_base, const void* const* flag_ptrs, int ag, int rows_per_shard, int comm_ctas,
                                    int ag_flag_base, const void* ag_src, long long ag_src_ld,
                                    const void* const* ag_dst_ptrs, long long ag_dst_ld, int* ag_counter, int rs,
                                    int rows_per_owner, int rs_flag_base, const void* const* land_ptrs,
@@ -499,6 +505,10 @@ extern "C" int ssm_gemm_bf16_fused(const void* A, const void* B, void* C, int M,
   if (mode == 0) {
     r = make_tmap_2d_bf16(&tc, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc * 2, 64, 128);
     if (r) return -300 - r;
+  } else if (mode == 1 || mode == 2) {
+    if ((ldc % 4) || (reinterpret_cast<uintptr_t>(C) & 15)) return -SSM_ERR_BAD_ARG;
+    r = make_tmap_2d(&tc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc * 4, 32, 128);
+    if (r) return -300 - r;
   } else {
     tc = ta;
   }
@@ -506,7 +516,7 @@ extern "C" int ssm_gemm_bf16_fused(const void* A, const void* B, void* C, int M,
   GemmComm cm;
   memset(&cm, 0, sizeof(cm));
   memset(&maps, 0, sizeof(maps));
-  cm.nranks = nranks; cm.me = me; cm.seq = seq;
+  cm.nranks = nranks; cm.me = me; cm.seq = seq; cm.seq_base = seq_base;
   for (int t = 0; t < MAX_RANKS; ++t) cm.flag_ptrs.p[t] = t < nranks ? const_cast<void*>(flag_ptrs[t]) : nullptr;
   if (ag) {
     cm.ag = 1; cm.rows_per_shard = rows_per_shard; cm.comm_ctas = comm_ctas; cm.ag_flag_base = ag_flag_base;

@@ -182,8 +182,9 @@ def _conv_fwd(xBC, w2, bias, init, out=None):
     return out
 
 
-def _conv_bwd(xBC, w2, bias, dy16, dy32, c_split, dx_out):
-    """dx_out [B,L,C] view (row stride may exceed C); returns (dw [C,K], db [C]) fp32."""
+def _conv_bwd(xBC, w2, bias, dy16, dy32, c_split, dx_out, raw=False):
+    """dx_out [B,L,C] view (row stride may exceed C); returns (dw [C,K], db [C]) fp32, or the per-tile partial
+    buffer [tiles, C, 5] when `raw`."""
     B, L, C = xBC.shape
     tile = _lib().ssm_conv_tok_tile()
     ntile = (L + tile - 1) // tile
@@ -191,6 +192,8 @@ def _conv_bwd(xBC, w2, bias, dy16, dy32, c_split, dx_out):
     _run("ssm_conv1d_silu_bwd", _p(xBC), _ll(xBC.stride(1)), _p(w2), _p(bias), _p(dy16),
          _ll(dy16.stride(1) if dy16 is not None else 0), _p(dy32), _ll(dy32.stride(1) if dy32 is not None else 0),
          int(c_split), _p(dx_out), _ll(dx_out.stride(1)), _p(part), B, L, C, _st())
+    if raw:
+        return part
     s = part.sum(0)
     return s[:, :4], s[:, 4]
 
@@ -239,14 +242,14 @@ def _gated_fwd(y2, z2, w, eps, gs, out=None):
     return out
 
 
-def _gated_bwd(y2, z2, w, dout2, eps, gs, dy_out, dz_out):
+def _gated_bwd(y2, z2, w, dout2, eps, gs, dy_out, dz_out, raw=False):
     rows, d = y2.shape
     slices = int(min(rows, _ROW_SLICES))
     part = torch.empty(slices, d, dtype=torch.float32, device=y2.device)
     _run("ssm_gated_rmsnorm_bwd", _p(y2), _ll(y2.stride(0)), _p(z2), _ll(z2.stride(0) if z2 is not None else 0), _p(w),
          _p(dout2), _ll(dout2.stride(0)), _p(dy_out), _ll(dy_out.stride(0)), _p(dz_out),
          _ll(dz_out.stride(0) if dz_out is not None else 0), _p(part), slices, _ll(rows), d, gs, _c.c_float(eps), _st())
-    return part.sum(0)
+    return part if raw else part.sum(0)
 
 
 def _rows(t):
@@ -315,6 +318,11 @@ class _AddRMSNorm(torch.autograd.Function):
              _c.c_float(ctx.eps), int(res_out.dtype == torch.float32), _st())
         dsum = dsum.reshape(ctx.shape)
         dx = dsum if dsum.dtype == ctx.x_dtype else dsum.to(ctx.x_dtype)
+        mg = getattr(w, "main_grad", None)
+        if mg is not None and mg.dtype == torch.float32 and w.is_leaf:
+            _run("ssm_colsum", _p(part), slices, D, _p(mg), int(not getattr(w, "grad_stale", False)), _st())
+            w.grad_stale = False
+            return dx, (dsum if ctx.has_res else None), None, None, None
         return dx, (dsum if ctx.has_res else None), part.sum(0).to(w.dtype), None, None
 
 
@@ -383,14 +391,15 @@ def ce_backward(logits, labels, row_max, row_sum, grad_rows, vocab_start, ignore
 # ======================================================================================
 # optimizer
 # ======================================================================================
-def adamw_step(master, m, v, g, out, clip, lr, b1, b2, eps, wd, step):
+def adamw_step(master, m, v, g, out, clip, lr, b1, b2, eps, wd, step, lr_dev=None, step_dev=None):
+    """lr_dev (fp32 [1]) / step_dev (int32 [1]): device-resident values that override `lr` / `step`."""
     if master.dtype != torch.float32:
         raise TypeError("the fused AdamW keeps fp32 state")
     out16 = out if out.dtype == torch.bfloat16 else None
     out32 = out if out.dtype == torch.float32 else None
     _run("ssm_adamw", _p(master), _p(m), _p(v), _p(g), int(g.dtype == torch.float32), _p(out16), _p(out32),
          _ll(master.numel()), _p(clip), _c.c_float(lr), _c.c_float(b1), _c.c_float(b2), _c.c_float(eps),
-         _c.c_float(wd), int(step), _st())
+         _c.c_float(wd), int(step), _p(lr_dev), _p(step_dev), _st())
 
 
 def sumsq_accumulate(g, total):
@@ -449,7 +458,7 @@ def _pick_hpc(hv_per_group, nc, G, B, target=296):
 
 
 def _ssd_backward(conv_out, dy2, y2, dt, l, s_in, dt_raw2, dt_raw_stride, A, D, dt_bias, ddt_out, ddt_stride,
-                  B, L, d_inner, G, H, Hv):
+                  B, L, d_inner, G, H, Hv, raw=False):
     """Returns dx [B*L, d_inner] bf16, dBC fp32 [B*L, 2*G*128], dA, dD, d_dt_bias (fp32 [H]);
     d(dt_raw) goes to ddt_out (bf16, row stride ddt_stride, column h)."""
     dev = conv_out.device
@@ -471,10 +480,12 @@ def _ssd_backward(conv_out, dy2, y2, dt, l, s_in, dt_raw2, dt_raw_stride, A, D, 
          _p(s_in), _p(ds_out), _p(dx), _ll(d_inner), _p(dBC), _p(hpart), _p(ddt_out), _ll(ddt_stride), _p(ddt32),
          _p(dt_raw2), _ll(dt_raw_stride), _p(dt_bias), _p(A), _p(dt), _p(l), _p(D), B, L, H, Hv, G, d_inner, hpc,
          _p(st), _st())
-    hp = hpart.sum(0).reshape(H, psplit, 3).sum(1)
     if ddt32 is not None:
         summed = ddt32.reshape(B, H, psplit, L).sum(2).transpose(1, 2)           # [B, L, H]
         ddt_out.as_strided((B, L, H), (L * ddt_stride, ddt_stride, 1)).copy_(summed)
+    if raw:
+        return dx, dBC, hpart
+    hp = hpart.sum(0).reshape(H, psplit, 3).sum(1)
     return dx, dBC, hp[:, 0], hp[:, 1], hp[:, 2]
 
 
@@ -493,19 +504,24 @@ class _MixerCore(torch.autograd.Function):
                 want_final):
         _require_bf16(zxBCdt, conv_w, conv_b, norm_w)
         H, psplit, Hv = _ssd_dims(d_inner, P, G, N)
-        if not zxBCdt.is_contiguous():
-            zxBCdt = zxBCdt.contiguous()
         B, L, W = zxBCdt.shape
         C = d_inner + 2 * G * N
-        if W != d_inner + C + H or L % _CT or W % 8 or d_inner % 8:
+        if W != d_inner + C + H or L % _CT or d_inner % 8 or (G * N) % 8:
             raise ValueError("bad zxBCdt shape for the mixer core")
-        flat = zxBCdt.view(B * L, W)
+        # rows may carry padding (row stride ld >= W, multiple of 8): that is how the GEMM epilogue writes them
+        if (zxBCdt.stride(2) != 1 or zxBCdt.stride(1) % 8 or zxBCdt.stride(0) != L * zxBCdt.stride(1)
+                or zxBCdt.data_ptr() % 16):
+            buf = torch.empty(B * L, _ceil8(W), dtype=zxBCdt.dtype, device=zxBCdt.device)[:, :W]
+            buf.copy_(zxBCdt.reshape(B * L, W))
+            zxBCdt = buf.as_strided((B, L, W), (L * buf.stride(0), buf.stride(0), 1))
+        ld = zxBCdt.stride(1)
+        flat = zxBCdt.as_strided((B * L, W), (ld, 1))
         z2, xBC, dt_raw2 = flat[:, :d_inner], zxBCdt[..., d_inner:d_inner + C], flat[:, d_inner + C:]
         w2 = conv_w.reshape(C, -1).contiguous()
         conv_out = _conv_fwd(xBC, w2, conv_b, None).view(B * L, C)
         A = -torch.exp(A_log.float())
         Df, bf = D.float(), dt_bias.float()
-        y, dt, l, s_in, final = _ssd_forward(conv_out, dt_raw2, W, A, Df, bf, B, L, d_inner, G, H, Hv,
+        y, dt, l, s_in, final = _ssd_forward(conv_out, dt_raw2, ld, A, Df, bf, B, L, d_inner, G, H, Hv,
                                              want_final=want_final)
         out = _gated_fwd(y, z2, norm_w, eps, gs)
         ctx.dims = (B, L, W, C, d_inner, G, N, P, H, Hv, eps, gs, recompute)
@@ -514,6 +530,7 @@ class _MixerCore(torch.autograd.Function):
         else:
             ctx.save_for_backward(zxBCdt, w2, conv_b, dt_bias, A_log, D, norm_w, A, Df, bf, conv_out, y, dt, l, s_in)
         ctx.conv_w_shape = conv_w.shape
+        ctx.conv_w_param = conv_w if conv_w.is_leaf else None
         out = out.view(B, L, d_inner)
         if want_final:
             conv_state, ssm_state = _final_states(final, xBC, H, psplit, w2.shape[1])
@@ -526,22 +543,44 @@ class _MixerCore(torch.autograd.Function):
         B, L, W, C, d_inner, G, N, P, H, Hv, eps, gs, recompute = ctx.dims
         saved = ctx.saved_tensors
         zxBCdt, w2, conv_b, dt_bias, A_log, D, norm_w, A, Df, bf = saved[:10]
-        flat = zxBCdt.view(B * L, W)
+        ld = zxBCdt.stride(1)
+        flat = zxBCdt.as_strided((B * L, W), (ld, 1))
         z2, xBC, dt_raw2 = flat[:, :d_inner], zxBCdt[..., d_inner:d_inner + C], flat[:, d_inner + C:]
         if recompute:
             conv_out = _conv_fwd(xBC, w2, conv_b, None).view(B * L, C)
-            y, dt, l, s_in, _ = _ssd_forward(conv_out, dt_raw2, W, A, Df, bf, B, L, d_inner, G, H, Hv)
+            y, dt, l, s_in, _ = _ssd_forward(conv_out, dt_raw2, ld, A, Df, bf, B, L, d_inner, G, H, Hv)
         else:
             conv_out, y, dt, l, s_in = saved[10:]
-        d_zx = torch.empty_like(zxBCdt)
-        dflat = d_zx.view(B * L, W)
+        dflat = torch.empty(B * L, ld, dtype=zxBCdt.dtype, device=zxBCdt.device)[:, :W]
+        d_zx = dflat.as_strided((B, L, W), (L * ld, ld, 1))
         dout2 = dout.reshape(B * L, d_inner)
         if not dout2.is_contiguous():
             dout2 = dout2.contiguous()
         dy = torch.empty(B * L, d_inner, dtype=torch.bfloat16, device=dout.device)
+        small = [ctx.conv_w_param, conv_b, norm_w, A_log, D, dt_bias]
+        direct = all(p is None or (getattr(p, "main_grad", None) is not None and p.main_grad.dtype == torch.float32
+                                   and p.main_grad.is_contiguous()) for p in small) and ctx.conv_w_param is not None
+        if direct:
+            # partial sums go straight into the fp32 main-gradient buffers with one finalisation kernel
+            gpart = _gated_bwd(y, z2, norm_w, dout2, eps, gs, dy, dflat[:, :d_inner], raw=True)
+            dx, dBC, hpart = _ssd_backward(conv_out, dy, y, dt, l, s_in, dt_raw2, ld, A, Df, bf,
+                                           dflat[:, d_inner + C:], ld, B, L, d_inner, G, H, Hv, raw=True)
+            cpart = _conv_bwd(xBC, w2, conv_b, dx.view(B, L, d_inner), dBC.view(B, L, 2 * G * N), d_inner,
+                              d_zx[..., d_inner:d_inner + C], raw=True)
+            mask = 0
+            for bit, p in enumerate(small):
+                if p is not None:
+                    if not getattr(p, "grad_stale", False):
+                        mask |= 1 << bit
+                    p.grad_stale = False
+            mg = [None if p is None else p.main_grad for p in small]
+            _run("ssm_mixer_small_grads", _p(cpart), cpart.shape[0], C, _p(gpart), gpart.shape[0], d_inner, _p(hpart),
+                 hpart.shape[0], Hv, H, _p(A), _p(mg[0]), _p(mg[1]), _p(mg[2]), _p(mg[3]), _p(mg[4]), _p(mg[5]),
+                 mask, _st())
+            return (d_zx,) + (None,) * 14
         dnorm_w = _gated_bwd(y, z2, norm_w, dout2, eps, gs, dy, dflat[:, :d_inner])
-        dx, dBC, dA, dD, dbias = _ssd_backward(conv_out, dy, y, dt, l, s_in, dt_raw2, W, A, Df, bf,
-                                               dflat[:, d_inner + C:], W, B, L, d_inner, G, H, Hv)
+        dx, dBC, dA, dD, dbias = _ssd_backward(conv_out, dy, y, dt, l, s_in, dt_raw2, ld, A, Df, bf,
+                                               dflat[:, d_inner + C:], ld, B, L, d_inner, G, H, Hv)
         dw, db = _conv_bwd(xBC, w2, conv_b, dx.view(B, L, d_inner), dBC.view(B, L, 2 * G * N), d_inner,
                            d_zx[..., d_inner:d_inner + C])
         dA_log = (dA * A).to(A_log.dtype)

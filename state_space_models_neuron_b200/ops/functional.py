@@ -15,15 +15,23 @@ import torch.nn.functional as F
 from . import oracle
 
 
+# Measurement switch used only by `baseline/nccl_cublas.py`: run the PyTorch/cuBLAS restatement on GPU tensors.
+_BASELINE = [False]
+
+
 def _cuda():
     from . import cuda_ops
     return cuda_ops
 
 
+def _native(t) -> bool:
+    return t.is_cuda and not _BASELINE[0]
+
+
 # ---- GEMM ---------------------------------------------------------------------------------
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y = x @ weight^T (+ bias); weight is [out, in]."""
-    if x.is_cuda:
+    if _native(x):
         return _cuda().linear(x, weight, bias)
     return F.linear(x, weight, bias)
 
@@ -31,27 +39,27 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
 # ---- conv ---------------------------------------------------------------------------------
 def causal_conv1d_silu(x, weight, bias, initial_state=None):
     """Depthwise causal conv (taps = weight.shape[-1]) + SiLU on channels-last x [B,L,C]."""
-    if x.is_cuda:
+    if _native(x):
         return _cuda().causal_conv1d_silu(x, weight, bias, initial_state)
     return oracle.causal_conv1d_silu(x, weight, bias, initial_state)
 
 
 # ---- norms --------------------------------------------------------------------------------
 def gated_rmsnorm(y, z, weight, eps: float, group_size: Optional[int] = None):
-    if y.is_cuda:
+    if _native(y):
         return _cuda().gated_rmsnorm(y, z, weight, eps, group_size)
     return oracle.gated_rmsnorm(y, z, weight, eps, group_size)
 
 
 def rmsnorm(x, weight, eps: float):
-    if x.is_cuda:
+    if _native(x):
         return _cuda().rmsnorm(x, weight, eps)
     return oracle.rmsnorm(x, weight, eps)
 
 
 def add_rmsnorm(x, residual, weight, eps: float, residual_dtype=None):
     """(residual + x) -> (normed in x.dtype, new residual).  residual may be None."""
-    if x.is_cuda:
+    if _native(x):
         return _cuda().add_rmsnorm(x, residual, weight, eps, residual_dtype)
     rd = residual_dtype or x.dtype
     r = x.to(rd) if residual is None else residual.to(rd) + x.to(rd)
@@ -66,7 +74,7 @@ def ssd_chunk_scan(x, dt_raw, A, Bm, Cm, D, dt_bias, chunk_size: int = 128,
     x [B,L,H,P]; dt_raw [B,L,H]; A,D,dt_bias [H]; Bm,Cm [B,L,G,N].  Returns y (x's dtype) and, if
     asked, the final state [B,H,P,N] in fp32.
     """
-    if x.is_cuda:
+    if _native(x):
         return _cuda().ssd_chunk_scan(x, dt_raw, A, Bm, Cm, D, dt_bias, chunk_size,
                                       initial_state, return_final_state)
     dt = oracle.softplus(dt_raw.float() + dt_bias.float())
@@ -88,7 +96,7 @@ def mamba2_mixer_core(zxBCdt, conv_w, conv_b, dt_bias, A_log, D, norm_w, *, d_in
     keep the intermediates of the forward pass, or rebuild them from zxBCdt in backward.
     Returns out [B,L,d_inner] and optionally (conv_state [B,C,K], ssm_state [B,H,P,N]).
     """
-    if zxBCdt.is_cuda:
+    if _native(zxBCdt):
         return _cuda().mamba2_mixer_core(zxBCdt, conv_w, conv_b, dt_bias, A_log, D, norm_w, d_inner,
                                          n_groups, d_state, head_dim, eps, norm_group_size, chunk_size,
                                          recompute, return_final_states)
@@ -126,7 +134,7 @@ def ssm_decode_step(zxBCdt, conv_state, ssm_state, conv_w, conv_b, dt_bias, A_lo
     (mamba2/mamba2_kernel_inference.py:26-104), softplus in torch (mamba2/mamba2_mixer.py:267) and the
     torch gated norm (mamba2/mamba2_mixer.py:279).
     """
-    if zxBCdt.is_cuda:
+    if _native(zxBCdt):
         return _cuda().ssm_decode_step(zxBCdt, conv_state, ssm_state, conv_w, conv_b, dt_bias, A_log, D,
                                        norm_w, d_inner, n_groups, d_state, head_dim, eps, norm_group_size)
     conv_dim = d_inner + 2 * n_groups * d_state
@@ -142,27 +150,27 @@ def ssm_decode_step(zxBCdt, conv_state, ssm_state, conv_w, conv_b, dt_bias, A_lo
 # ---- attention ----------------------------------------------------------------------------
 def attention(q, k, v, causal: bool = True):
     """GQA flash attention; q [B,L,Hq,Dh], k/v [B,L,Hkv,Dh]."""
-    if q.is_cuda:
+    if _native(q):
         return _cuda().attention(q, k, v, causal)
     return oracle.attention(q, k, v, causal)
 
 
 def gelu(x):
-    if x.is_cuda:
+    if _native(x):
         return _cuda().gelu(x)
     return F.gelu(x)
 
 
 # ---- cross entropy ------------------------------------------------------------------------
 def ce_partials(logits, labels, vocab_start: int):
-    if logits.is_cuda:
+    if _native(logits):
         return _cuda().ce_partials(logits, labels, vocab_start)
     return oracle.ce_partials(logits, labels, vocab_start)
 
 
 def ce_backward(logits, labels, row_max, row_sum, grad_rows, vocab_start: int, ignore_index: int):
     """d loss / d logits for the local vocab shard: (softmax - onehot) * grad_rows."""
-    if logits.is_cuda:
+    if _native(logits):
         return _cuda().ce_backward(logits, labels, row_max, row_sum, grad_rows, vocab_start, ignore_index)
     lf = logits.float()
     p = torch.exp(lf - row_max[:, None]) / row_sum[:, None]

@@ -46,7 +46,7 @@ def _fused_gemm(a, b, out, M, N, K, lda, ldb, ldc, a_mn, b_mn, mode, bias, ws, s
     ag = ag or dict(on=0, rows=0, base=0, src=None, src_ld=0, dst=null, dst_ld=0, counter=0)
     rs = rs or dict(on=0, rows=0, base=0, land=null, ld=0, counters=0)
     _run("ssm_gemm_bf16_fused", _P(a), _P(b), _P(out), M, N, K, _ll(lda), _ll(ldb), _ll(ldc), int(a_mn), int(b_mn), mode,
-         _P(bias), 0, _P(status_tensor(ws.device)), _st(), ws.nranks, ws.me, seq, ws.flag_ptr_array,
+         _P(bias), 0, _P(status_tensor(ws.device)), _st(), ws.nranks, ws.me, seq, _P(ws.seq_base), ws.flag_ptr_array,
          ag["on"], ag["rows"], COMM_CTAS, ag["base"], _P(ag["src"]), _ll(ag["src_ld"]), ag["dst"], _ll(ag["dst_ld"]),
          _c.c_void_p(ag["counter"]), rs["on"], rs["rows"], rs["base"], rs["land"], _ll(rs["ld"]),
          _c.c_void_p(rs["counters"]))
@@ -92,7 +92,8 @@ def _gemm_rs(a2, w, b_mn, ws):
     out = torch.empty(Ls, N, dtype=torch.bfloat16, device=a2.device)
     local_land = ws.local_view(off, T * Ls, N)
     _run("ssm_reduce_partials", _P(local_land), _ll(N), _ll(Ls * N), _P(out), _ll(N), Ls, N, T,
-         _c.c_void_p(ws.base_ptrs[ws.me]), ws.flag_base(symm.KIND_RS, par), seq, _P(status_tensor(ws.device)),
+         _c.c_void_p(ws.base_ptrs[ws.me]), ws.flag_base(symm.KIND_RS, par), seq, _P(ws.seq_base),
+         _P(status_tensor(ws.device)),
          min(148, max(1, Ls * N // 8 // 256)), _st())
     return out
 

@@ -54,6 +54,9 @@ class SymmWorkspace:
         torch.cuda.synchronize(self.device)
         dist.barrier(group=group)
         self.counters = torch.zeros(64, dtype=torch.int32, device=self.device)   # local, not shared
+        # sequence number of a fused call = seq_base (device, advanced once per training step) + its position in
+        # the step (host); the device part keeps the numbers growing when a captured CUDA graph is replayed
+        self.seq_base = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.flag_ptr_array = _ptr_array(self.base_ptrs)
         self._keep = []
 
@@ -80,9 +83,21 @@ class SymmWorkspace:
     def fits(self, rows: int, cols: int) -> bool:
         return rows * cols <= self.rows_total * self.cols
 
+    STEP_STRIDE = 1 << 16    # even and larger than the number of fused calls in one training step
+
     def next_seq(self) -> int:
+        """Position of the next fused call inside the current step (parity selects the double buffers)."""
         self.seq += 1
+        if self.seq >= self.STEP_STRIDE:
+            raise RuntimeError("too many fused collective calls without advance_step()")
         return self.seq
+
+    def advance_step(self) -> None:
+        """Start a new step: bump the device-side base (a kernel on the current stream, so it is captured into
+        CUDA graphs) and restart the host-side position."""
+        from ..ops.cuda_ops import _P, _run, _st
+        _run("ssm_advance_counter", _P(self.seq_base), self.STEP_STRIDE, _st())
+        self.seq = 0
 
     def counter_ptr(self, index: int) -> int:
         return self.counters.data_ptr() + 4 * index
@@ -103,6 +118,11 @@ def get_workspace(rows_total: int, cols: int, device) -> Optional[SymmWorkspace]
     _WS = SymmWorkspace(ps.get_tensor_model_parallel_group(), ps.get_tensor_model_parallel_size(),
                         ps.get_tensor_model_parallel_rank(), rows_total, cols, device)
     return _WS
+
+
+def advance_step() -> None:
+    if _WS is not None:
+        _WS.advance_step()
 
 
 def reset_workspace() -> None:

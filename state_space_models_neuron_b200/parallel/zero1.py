@@ -103,6 +103,12 @@ class Zero1Optimizer(torch.optim.Optimizer):
                 segs.append([lo - s, hi - s, gi, rep])
         self.segments = [tuple(x) for x in segs]
         self._norm_buf = torch.zeros(1, dtype=torch.float32, device=self.device)
+        # device-resident step counter and per-group learning rates (read by the fused AdamW kernel, so a captured
+        # CUDA graph of the step keeps working when the scheduler changes the rate)
+        self._dev_step = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._dev_lr = torch.zeros(max(1, len(self.param_groups)), dtype=torch.float32, device=self.device)
+        self._host_lr = torch.zeros(max(1, len(self.param_groups)), dtype=torch.float32,
+                                    pin_memory=self.device.type == "cuda")
 
     @staticmethod
     def _accumulate_hook(p: torch.nn.Parameter) -> None:
@@ -168,7 +174,8 @@ class Zero1Optimizer(torch.optim.Optimizer):
             if rep and self.tp_rank != 0:
                 continue
             seg = g[lo:hi]
-            if seg.is_cuda:
+            from ..ops.functional import _native
+            if _native(seg):
                 from ..ops import cuda_ops
                 cuda_ops.sumsq_accumulate(seg, total)
             else:
@@ -180,11 +187,21 @@ class Zero1Optimizer(torch.optim.Optimizer):
         return total
 
     @torch.no_grad()
+    def upload_learning_rates(self) -> None:
+        """Copy the groups' current learning rates to the device (outside any graph capture)."""
+        for i, grp in enumerate(self.param_groups):
+            self._host_lr[i] = float(grp["lr"])
+        self._dev_lr.copy_(self._host_lr, non_blocking=True)
+
     def step(self, closure=None):
+        capturing = self.device.type == "cuda" and torch.cuda.is_current_stream_capturing()
+        if not capturing:
+            self.upload_learning_rates()
         self._finish_lazy_zero()
         self._allreduce_sequence_parallel_grads()
         g = self._reduce_gradients()
         self.step_count += 1
+        self._dev_step.add_(1)
         clip = torch.ones(1, dtype=torch.float32, device=self.device)
         if self.max_grad_norm is not None:
             norm = torch.sqrt(self._grad_norm_sq(g))
@@ -196,10 +213,14 @@ class Zero1Optimizer(torch.optim.Optimizer):
             grp = self.param_groups[gi]
             b1, b2 = grp["betas"]
             self._adamw(self.master[lo:hi], self.exp_avg[lo:hi], self.exp_avg_sq[lo:hi], g[lo:hi], out[lo:hi],
-                        clip, grp["lr"], b1, b2, grp["eps"], grp["weight_decay"], self.step_count)
+                        clip, grp["lr"], b1, b2, grp["eps"], grp["weight_decay"], self.step_count,
+                        self._dev_lr[gi:gi + 1], self._dev_step)
         if self.shard:
             dist.all_gather_into_tensor(self.flat_params, out.contiguous(), group=self.dp_group) \
                 if dist.get_backend(self.dp_group) != "gloo" else self._gloo_all_gather(out)
+        if self.tp_size > 1 and self.device.type == "cuda":
+            from . import symm
+            symm.advance_step()
         return None
 
     def _gloo_all_gather(self, out: torch.Tensor) -> None:
@@ -208,10 +229,11 @@ class Zero1Optimizer(torch.optim.Optimizer):
         self.flat_params.copy_(torch.cat(parts))
 
     @staticmethod
-    def _adamw(master, m, v, g, out, clip, lr, b1, b2, eps, wd, step) -> None:
-        if master.is_cuda:
+    def _adamw(master, m, v, g, out, clip, lr, b1, b2, eps, wd, step, lr_dev=None, step_dev=None) -> None:
+        from ..ops.functional import _native
+        if _native(master):
             from ..ops import cuda_ops
-            cuda_ops.adamw_step(master, m, v, g, out, clip, lr, b1, b2, eps, wd, step)
+            cuda_ops.adamw_step(master, m, v, g, out, clip, lr, b1, b2, eps, wd, step, lr_dev, step_dev)
             return
         gf = g.float() * clip
         mf, vf, w = m.float(), v.float(), master.float()
@@ -237,6 +259,7 @@ class Zero1Optimizer(torch.optim.Optimizer):
         if sd["total"] != self.total or sd["shard_size"] != self.shard_size or sd["shard_start"] != self.shard_start:
             raise ValueError("optimizer checkpoint was written with a different parallel layout")
         self.step_count = int(sd["step"])
+        self._dev_step.fill_(self.step_count)
         self.master.copy_(sd["master"])
         self.exp_avg.copy_(sd["exp_avg"])
         self.exp_avg_sq.copy_(sd["exp_avg_sq"])

@@ -268,3 +268,36 @@ def test_decode_step_matches_oracle():
         _close(out.cpu(), ref, atol=3e-2, rtol=3e-2)
     _close(ss.cpu(), ss_r, atol=2e-2, rtol=2e-2)
     _close(cs.cpu(), cs_r, atol=1e-2, rtol=1e-2)
+
+
+def test_mixer_core_direct_main_grad_path():
+    """With fp32 `main_grad` buffers on the parameters the backward writes the small gradients itself
+    (store on a stale buffer, accumulate afterwards) and must match the autograd-returned gradients."""
+    from state_space_models_neuron_b200 import ops
+    B, L, d_inner, G, N, P = 1, 256, 512, 2, 128, 64
+    H, C = d_inner // P, d_inner + 2 * G * N
+    g = torch.Generator(device="cuda").manual_seed(6)
+    zx = torch.randn(B, L, d_inner + C + H, device="cuda", generator=g).bfloat16()
+    mk = lambda t: torch.nn.Parameter(t)
+    def params():
+        g2 = torch.Generator(device="cuda").manual_seed(7)
+        return [mk((torch.randn(C, 1, 4, device="cuda", generator=g2) * 0.4).bfloat16()),
+                mk((torch.randn(C, device="cuda", generator=g2) * 0.2).bfloat16()),
+                mk((torch.randn(H, device="cuda", generator=g2) * 0.5 - 2).bfloat16()),
+                mk(torch.log(torch.rand(H, device="cuda", generator=g2) * 15 + 1).bfloat16()),
+                mk(torch.ones(H, device="cuda").bfloat16()),
+                mk((1 + 0.1 * torch.randn(d_inner, device="cuda", generator=g2)).bfloat16())]
+    kw = dict(d_inner=d_inner, n_groups=G, d_state=N, head_dim=P, eps=1e-5, norm_group_size=d_inner // G)
+    pa, pb = params(), params()
+    go = torch.randn(B, L, d_inner, device="cuda", generator=g).bfloat16()
+    ops.mamba2_mixer_core(zx, *pa, **kw).backward(go)
+    for p in pb:
+        p.main_grad = torch.full(p.shape, 7.0, device="cuda")      # stale contents must be overwritten
+        p.grad_stale = True
+    ops.mamba2_mixer_core(zx, *pb, **kw).backward(go)
+    for a, b in zip(pa, pb):
+        assert b.grad is None
+        _close(b.main_grad, a.grad, atol=2e-2 * max(1.0, a.grad.float().abs().max().item()), rtol=2e-2)
+    ops.mamba2_mixer_core(zx, *pb, **kw).backward(go)               # second micro-step accumulates
+    for a, b in zip(pa, pb):
+        _close(b.main_grad, 2 * a.grad.float(), atol=4e-2 * max(1.0, a.grad.float().abs().max().item()), rtol=2e-2)
