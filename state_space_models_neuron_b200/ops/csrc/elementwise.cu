@@ -151,6 +151,7 @@ conv1d_silu_bwd_kernel(const __nv_bfloat16* __restrict__ x, long long xs, const 
     }
   }
   // walk t over [t0, t0 + CONV_TOK + 3): dpre[t] is produced at step t, dx[t-3] is emitted at step t
+  #pragma unroll 5
   for (int i = 0; i < CONV_TOK + 3; ++i) {
     const int t = t0 + i;
     float cur[8], g[8], d[8];
@@ -194,9 +195,11 @@ conv1d_silu_bwd_kernel(const __nv_bfloat16* __restrict__ x, long long xs, const 
 // gated group RMSNorm:  out = w * h * rsqrt(mean_g(h^2) + eps),  h = y * silu(z)
 // one block per (row, group); thread handles vectors v = tid, tid + blockDim, ... of 8 elements
 // =====================================================================================
-constexpr int NORM_MAXV = 4;
+// MAXV = 16-byte vectors per thread.  Rows up to 8192 elements run with one vector per thread and up to 1024
+// threads (few registers, full occupancy); longer rows use four vectors per thread.
 
-__global__ void __launch_bounds__(256)
+template <int NORM_MAXV>
+__global__ void __launch_bounds__(NORM_MAXV == 1 ? 1024 : 256)
 gated_rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ y, long long ys, const __nv_bfloat16* __restrict__ z,
                          long long zs, const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out,
                          long long os, int gs, float eps) {
@@ -240,7 +243,8 @@ gated_rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ y, long long ys, cons
 
 // grid (row_slices, groups); each block walks rows r = blockIdx.x, blockIdx.x + gridDim.x, ...
 // dwpart [gridDim.x, d] fp32 partial sums of dout * h * rstd.
-__global__ void __launch_bounds__(256)
+template <int NORM_MAXV>
+__global__ void __launch_bounds__(NORM_MAXV == 1 ? 1024 : 256)
 gated_rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ y, long long ys, const __nv_bfloat16* __restrict__ z,
                          long long zs, const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ dout,
                          long long dos, __nv_bfloat16* __restrict__ dy, long long dys, __nv_bfloat16* __restrict__ dz,
@@ -331,8 +335,8 @@ __device__ __forceinline__ void store8r(RT* p, const float (&f)[8]);
 template <> __device__ __forceinline__ void store8r<__nv_bfloat16>(__nv_bfloat16* p, const float (&f)[8]) { store8(p, f); }
 template <> __device__ __forceinline__ void store8r<float>(float* p, const float (&f)[8]) { store8f(p, f); }
 
-template <typename RT>
-__global__ void __launch_bounds__(256)
+template <typename RT, int NORM_MAXV>
+__global__ void __launch_bounds__(NORM_MAXV == 1 ? 1024 : 256)
 add_rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const RT* __restrict__ res, const __nv_bfloat16* __restrict__ w,
                        __nv_bfloat16* __restrict__ out, RT* __restrict__ res_out, int D, float eps) {
   __shared__ float red[33];
@@ -372,8 +376,8 @@ add_rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const RT* __restrict
 }
 
 // d_sum = d_res_out + rmsnorm_bwd(d_out);  dwpart [gridDim.x, D].  res = the summed residual r' saved by fwd.
-template <typename RT>
-__global__ void __launch_bounds__(256)
+template <typename RT, int NORM_MAXV>
+__global__ void __launch_bounds__(NORM_MAXV == 1 ? 1024 : 256)
 add_rmsnorm_bwd_kernel(const RT* __restrict__ res, const __nv_bfloat16* __restrict__ w,
                        const __nv_bfloat16* __restrict__ dout, const RT* __restrict__ dres_out,
                        RT* __restrict__ dsum, float* __restrict__ dwpart, long long rows, int D, float eps) {
@@ -631,6 +635,11 @@ __global__ void __launch_bounds__(256) colsum_kernel(const float* __restrict__ p
 
 // ------------------------------------------------------------------------------------ C API
 using namespace ssm;
+#define LAUNCH_MV(kern, T, grid, t, st, ...)                                     \
+  do {                                                                          \
+    if (mv == 1) kern<T, 1><<<grid, t, 0, st>>>(__VA_ARGS__);                   \
+    else kern<T, 4><<<grid, t, 0, st>>>(__VA_ARGS__);                           \
+  } while (0)
 #define BF(p) reinterpret_cast<const __nv_bfloat16*>(p)
 #define BFM(p) reinterpret_cast<__nv_bfloat16*>(p)
 
@@ -655,22 +664,25 @@ extern "C" int ssm_conv1d_silu_bwd(const void* x, long long xs, const void* w, c
 }
 extern "C" int ssm_conv_tok_tile() { return CONV_TOK; }
 
-static int norm_threads(int n) {
-  int v = n / 8;
-  int t = 32;
-  while (t < 256 && t * NORM_MAXV < v) t <<= 1;
-  if (t * NORM_MAXV < v) return -1;
-  // prefer one vector per thread when the row is short
-  while (t < 256 && t < v) t <<= 1;
+// threads per block and vectors per thread for a row (or group) of n elements; -1 if unsupported
+static int norm_threads(int n, int* maxv = nullptr) {
+  const int v = n / 8;
+  int mv, t = 32;
+  if (v <= 1024) { mv = 1; while (t < v) t <<= 1; }
+  else if (v <= 4096) { mv = 4; t = 256; while (t * 4 < v) t <<= 1; if (t > 256) return -1; }
+  else return -1;
+  if (maxv) *maxv = mv;
   return t;
 }
 
 extern "C" int ssm_gated_rmsnorm_fwd(const void* y, long long ys, const void* z, long long zs, const void* w,
                                      void* out, long long os, long long rows, int d, int gs, float eps, cudaStream_t st) {
-  const int t = norm_threads(gs);
+  int mv = 1;
+  const int t = norm_threads(gs, &mv);
   if (gs % 8 || d % gs || t < 0 || ys % 8 || zs % 8 || os % 8) return -SSM_ERR_BAD_ARG;
   dim3 grid((unsigned)rows, d / gs);
-  gated_rmsnorm_fwd_kernel<<<grid, t, 0, st>>>(BF(y), ys, BF(z), zs, BF(w), BFM(out), os, gs, eps);
+  if (mv == 1) gated_rmsnorm_fwd_kernel<1><<<grid, t, 0, st>>>(BF(y), ys, BF(z), zs, BF(w), BFM(out), os, gs, eps);
+  else gated_rmsnorm_fwd_kernel<4><<<grid, t, 0, st>>>(BF(y), ys, BF(z), zs, BF(w), BFM(out), os, gs, eps);
   return (int)cudaGetLastError();
 }
 // dwpart must hold row_slices * d floats.
@@ -678,37 +690,44 @@ extern "C" int ssm_gated_rmsnorm_bwd(const void* y, long long ys, const void* z,
                                      const void* dout, long long dos, void* dy, long long dys, void* dz, long long dzs,
                                      void* dwpart, int row_slices, long long rows, int d, int gs, float eps,
                                      cudaStream_t st) {
-  const int t = norm_threads(gs);
+  int mv = 1;
+  const int t = norm_threads(gs, &mv);
   if (gs % 8 || d % gs || t < 0 || ys % 8 || zs % 8 || dos % 8 || dys % 8 || dzs % 8) return -SSM_ERR_BAD_ARG;
   dim3 grid(row_slices, d / gs);
-  gated_rmsnorm_bwd_kernel<<<grid, t, 0, st>>>(BF(y), ys, BF(z), zs, BF(w), BF(dout), dos, BFM(dy), dys, BFM(dz), dzs,
-                                               reinterpret_cast<float*>(dwpart), rows, d, gs, eps);
+  if (mv == 1)
+    gated_rmsnorm_bwd_kernel<1><<<grid, t, 0, st>>>(BF(y), ys, BF(z), zs, BF(w), BF(dout), dos, BFM(dy), dys, BFM(dz), dzs,
+                                                    reinterpret_cast<float*>(dwpart), rows, d, gs, eps);
+  else
+    gated_rmsnorm_bwd_kernel<4><<<grid, t, 0, st>>>(BF(y), ys, BF(z), zs, BF(w), BF(dout), dos, BFM(dy), dys, BFM(dz), dzs,
+                                                    reinterpret_cast<float*>(dwpart), rows, d, gs, eps);
   return (int)cudaGetLastError();
 }
 
 extern "C" int ssm_add_rmsnorm_fwd(const void* x, const void* res, const void* w, void* out, void* res_out,
                                    long long rows, int D, float eps, int res_fp32, cudaStream_t st) {
-  const int t = norm_threads(D);
+  int mv = 1;
+  const int t = norm_threads(D, &mv);
   if (D % 8 || t < 0) return -SSM_ERR_BAD_ARG;
   if (res_fp32)
-    add_rmsnorm_fwd_kernel<float><<<(unsigned)rows, t, 0, st>>>(BF(x), reinterpret_cast<const float*>(res), BF(w), BFM(out),
+    LAUNCH_MV(add_rmsnorm_fwd_kernel, float, (unsigned)rows, t, st, BF(x), reinterpret_cast<const float*>(res), BF(w), BFM(out),
                                                                 reinterpret_cast<float*>(res_out), D, eps);
   else
-    add_rmsnorm_fwd_kernel<__nv_bfloat16><<<(unsigned)rows, t, 0, st>>>(BF(x), BF(res), BF(w), BFM(out), BFM(res_out), D, eps);
+    LAUNCH_MV(add_rmsnorm_fwd_kernel, __nv_bfloat16, (unsigned)rows, t, st, BF(x), BF(res), BF(w), BFM(out), BFM(res_out), D, eps);
   return (int)cudaGetLastError();
 }
 extern "C" int ssm_add_rmsnorm_bwd(const void* res, const void* w, const void* dout, const void* dres_out, void* dsum,
                                    void* dwpart, int row_slices, long long rows, int D, float eps, int res_fp32,
                                    cudaStream_t st) {
-  const int t = norm_threads(D);
+  int mv = 1;
+  const int t = norm_threads(D, &mv);
   if (D % 8 || t < 0) return -SSM_ERR_BAD_ARG;
   if (res_fp32)
-    add_rmsnorm_bwd_kernel<float><<<row_slices, t, 0, st>>>(reinterpret_cast<const float*>(res), BF(w), BF(dout),
+    LAUNCH_MV(add_rmsnorm_bwd_kernel, float, row_slices, t, st, reinterpret_cast<const float*>(res), BF(w), BF(dout),
                                                             reinterpret_cast<const float*>(dres_out),
                                                             reinterpret_cast<float*>(dsum),
                                                             reinterpret_cast<float*>(dwpart), rows, D, eps);
   else
-    add_rmsnorm_bwd_kernel<__nv_bfloat16><<<row_slices, t, 0, st>>>(BF(res), BF(w), BF(dout), BF(dres_out), BFM(dsum),
+    LAUNCH_MV(add_rmsnorm_bwd_kernel, __nv_bfloat16, row_slices, t, st, BF(res), BF(w), BF(dout), BF(dres_out), BFM(dsum),
                                                                     reinterpret_cast<float*>(dwpart), rows, D, eps);
   return (int)cudaGetLastError();
 }
@@ -817,18 +836,19 @@ extern "C" int ssm_add_rmsnorm_bwd_noalloc(const void* res, const void* w, const
                                            void* dsum, void* dw, long long rows, int D, float eps, int res_fp32,
                                            cudaStream_t st) {
   if (D > SSM_NOALLOC_MAX_D) return -SSM_NOALLOC_ERR_TOO_LARGE;
-  const int t = norm_threads(D);
+  int mv = 1;
+  const int t = norm_threads(D, &mv);
   if (D <= 0 || D % 8 || t < 0 || rows < 1 || !res || !w || !dout || !dsum || !dw) return -SSM_NOALLOC_ERR_BAD_ARG;
   int err = 0;
   float* scratch = noalloc_scratch_for_current_device(&err);
   if (scratch == nullptr) return err;
   const int slices = rows < SSM_NOALLOC_SLICES ? (int)rows : SSM_NOALLOC_SLICES;
   if (res_fp32)
-    add_rmsnorm_bwd_kernel<float><<<slices, t, 0, st>>>(reinterpret_cast<const float*>(res), BF(w), BF(dout),
+    LAUNCH_MV(add_rmsnorm_bwd_kernel, float, slices, t, st, reinterpret_cast<const float*>(res), BF(w), BF(dout),
                                                         reinterpret_cast<const float*>(dres_out),
                                                         reinterpret_cast<float*>(dsum), scratch, rows, D, eps);
   else
-    add_rmsnorm_bwd_kernel<__nv_bfloat16><<<slices, t, 0, st>>>(BF(res), BF(w), BF(dout), BF(dres_out), BFM(dsum),
+    LAUNCH_MV(add_rmsnorm_bwd_kernel, __nv_bfloat16, slices, t, st, BF(res), BF(w), BF(dout), BF(dres_out), BFM(dsum),
                                                                 scratch, rows, D, eps);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;

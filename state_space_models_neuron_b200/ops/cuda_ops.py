@@ -116,7 +116,15 @@ def gemm(a: torch.Tensor, b: torch.Tensor, a_mn: bool = False, b_mn: bool = Fals
         if out_dtype == torch.bfloat16:
             out = torch.empty(M, _ceil8(N), dtype=torch.bfloat16, device=a.device)[:, :N]
         else:
-            out = torch.empty(M, N, dtype=torch.float32, device=a.device)
+            out = torch.empty(M, (N + 3) // 4 * 4, dtype=torch.float32, device=a.device)[:, :N]
+    if out.dtype == torch.float32 and (out.stride(0) % 4 or out.data_ptr() % 16) and out.stride(1) == 1:
+        # TMA needs 16-byte aligned rows: go through a padded temporary
+        tmp = gemm(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
+        if accumulate:
+            out.add_(tmp)
+        else:
+            out.copy_(tmp)
+        return out
     if out.dtype == torch.bfloat16:
         mode = 0
         if out.stride(1) != 1 or out.stride(0) % 8 or out.data_ptr() % 16:
@@ -681,3 +689,46 @@ def ssm_decode_step(zxBCdt, conv_state, ssm_state, conv_w, conv_b, dt_bias, A_lo
          _p(A), _p(D.float()), _p(ssm_state), _p(y), B, C, H, head_dim, d_state, n_groups, d_inner, _st())
     gs = d_inner if norm_group_size is None else norm_group_size
     return _gated_fwd(y, zxBCdt[:, :d_inner], norm_w, eps, gs)
+
+
+# ======================================================================================
+# attention
+# ======================================================================================
+class _Attention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v):
+        B, L, Hq, D = q.shape
+        Hkv = k.shape[2]
+        q2, k2, v2 = q.reshape(B * L, Hq * D), k.reshape(B * L, Hkv * D), v.reshape(B * L, Hkv * D)
+        q2, k2, v2 = [t if t.is_contiguous() else t.contiguous() for t in (q2, k2, v2)]
+        out = torch.empty_like(q2)
+        lse = torch.empty(B, Hq, L, dtype=torch.float32, device=q.device)
+        scale = 1.0 / (D ** 0.5)
+        _run("ssm_attn_fwd", _p(q2), _p(k2), _p(v2), _p(out), _p(lse), B, L, Hq, Hkv, D, _c.c_float(scale),
+             _p(status_tensor(q.device)), _st())
+        ctx.save_for_backward(q2, k2, v2, out, lse)
+        ctx.dims = (B, L, Hq, Hkv, D, scale)
+        return out.view(B, L, Hq, D)
+
+    @staticmethod
+    def backward(ctx, dout):
+        q2, k2, v2, out, lse = ctx.saved_tensors
+        B, L, Hq, Hkv, D, scale = ctx.dims
+        do2 = dout.reshape(B * L, Hq * D)
+        if not do2.is_contiguous():
+            do2 = do2.contiguous()
+        delta = (do2.view(B, L, Hq, D).float() * out.view(B, L, Hq, D).float()).sum(-1).permute(0, 2, 1).contiguous()
+        dq32 = torch.zeros(B * L, Hq * D, dtype=torch.float32, device=dout.device)
+        dk, dv = torch.empty_like(k2), torch.empty_like(v2)
+        _run("ssm_attn_bwd", _p(q2), _p(k2), _p(v2), _p(do2), _p(lse), _p(delta), _p(dq32), _p(dk), _p(dv), B, L, Hq, Hkv,
+             D, _c.c_float(scale), _p(status_tensor(dout.device)), _st())
+        return (dq32.to(torch.bfloat16).view(B, L, Hq, D), dk.view(B, L, Hkv, D), dv.view(B, L, Hkv, D))
+
+
+def attention(q, k, v, causal=True):
+    _require_bf16(q, k, v)
+    if not causal:
+        raise NotImplementedError("the GPU attention kernel is causal")
+    if q.shape[-1] != 128 or q.shape[1] % 128 or q.shape[1] != k.shape[1]:
+        raise ValueError("the GPU attention kernel needs head_dim 128 and equal q/k lengths that are multiples of 128")
+    return _Attention.apply(q, k, v)

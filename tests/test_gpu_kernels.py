@@ -301,3 +301,23 @@ def test_mixer_core_direct_main_grad_path():
     ops.mamba2_mixer_core(zx, *pb, **kw).backward(go)               # second micro-step accumulates
     for a, b in zip(pa, pb):
         _close(b.main_grad, 2 * a.grad.float(), atol=4e-2 * max(1.0, a.grad.float().abs().max().item()), rtol=2e-2)
+
+
+@pytest.mark.parametrize("B,L,Hq,Hkv", [(1, 128, 1, 1), (2, 384, 4, 2), (1, 512, 4, 1)])
+def test_flash_attention_fwd_bwd(B, L, Hq, Hkv):
+    from state_space_models_neuron_b200 import ops
+    from state_space_models_neuron_b200.ops import oracle
+    g = torch.Generator(device="cuda").manual_seed(L + Hq)
+    q = torch.randn(B, L, Hq, 128, device="cuda", generator=g).bfloat16().requires_grad_(True)
+    k = torch.randn(B, L, Hkv, 128, device="cuda", generator=g).bfloat16().requires_grad_(True)
+    v = torch.randn(B, L, Hkv, 128, device="cuda", generator=g).bfloat16().requires_grad_(True)
+    o = ops.attention(q, k, v)
+    go = torch.randn_like(o)
+    o.backward(go)
+    qr, kr, vr = [t.detach().float().requires_grad_(True) for t in (q, k, v)]
+    orf = oracle.attention(qr, kr, vr)
+    orf.backward(go.float())
+    _close(o, orf, atol=2e-2, rtol=3e-2)
+    _close(q.grad, qr.grad, atol=3e-2, rtol=3e-2, frac=0.995)
+    _close(k.grad, kr.grad, atol=3e-2, rtol=3e-2, frac=0.995)
+    _close(v.grad, vr.grad, atol=3e-2, rtol=3e-2, frac=0.995)
