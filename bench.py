@@ -234,9 +234,17 @@ def main():
         if e2e is not None:
             out["e2e"] = e2e
         print(json.dumps(out), flush=True)
+    # Tear down without destroying NCCL communicators that a live CUDA graph still references (that can block
+    # forever): drop the graph, drain the device, meet the other ranks, then leave the process directly.
+    if gstep is not None:
+        gstep.graph.reset()
+        gstep = None
+    torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-        dist.destroy_process_group()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
 
 
 if __name__ == "__main__":

@@ -41,6 +41,8 @@ class GraphedTrainStep:
             self.static_loss = self._eager_step()
         self.native_launches_per_step = cuda_ops.launch_count() - before   # native kernel nodes in the graph
         self.replays = 0
+        self.optimizer.step_count -= 1     # capturing recorded a step without executing it
+        self.eager_steps = warmup          # optimizer steps really taken before the first replay
 
     def _eager_step(self):
         loss = self.loss_fn(self.model, self.static)

@@ -1,0 +1,178 @@
+"""Run one kernel of the framework on one shape: the small case used for `ncu` captures and the CUDA-event
+timing behind the roofline numbers in `profiles/`.
+
+    python -m state_space_models_neuron_b200.utils.kernel_bench gemm --m 2048 --n 18560 --k 4096 --iters 20
+    python -m state_space_models_neuron_b200.utils.kernel_bench ssd --seq 2048 --heads 128 --groups 8 --iters 10
+    python -m state_space_models_neuron_b200.utils.kernel_bench norm|conv|attn|adamw ...
+
+Prints one JSON line: time per launch (CUDA events, after warm-up, L2 flushed between launches by writing a
+256 MiB buffer), achieved TFLOP/s or GB/s and the fraction of the measured peak from MEASURED_PEAKS.json.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from ..ops import cuda_ops
+
+
+def _peaks():
+    here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    for base in (os.getcwd(), here):
+        p = os.path.join(base, "MEASURED_PEAKS.json")
+        if os.path.exists(p):
+            with open(p) as f:
+                d = json.load(f)
+            return d.get("bf16_tflops", 1590.0), d.get("hbm_gbs", 6650.0), "measured"
+    return 1590.0, 6650.0, "fallback"
+
+
+def time_kernel(fn, iters: int, warmup: int = 3, flush: bool = True) -> float:
+    scratch = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        if scratch is not None:
+            scratch.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        total += a.elapsed_time(b)
+    cuda_ops.check_status()
+    return total / iters
+
+
+def bench_gemm(a):
+    A = torch.randn(a.m, a.k, device="cuda").bfloat16()
+    B = torch.randn(a.n, a.k, device="cuda").bfloat16()
+    if a.layout == "tn":
+        fn = lambda: cuda_ops.gemm(A, B)
+    elif a.layout == "nn":
+        Bt = B.t().contiguous()
+        fn = lambda: cuda_ops.gemm(A, Bt, b_mn=True)
+    else:
+        At, Bt = A.t().contiguous(), B.t().contiguous()
+        out = torch.zeros(a.m, a.n, device="cuda")
+        fn = lambda: cuda_ops.gemm(At, Bt, a_mn=True, b_mn=True, out=out, accumulate=False)
+    ms = time_kernel(fn, a.iters)
+    return ms, 2.0 * a.m * a.n * a.k, None
+
+
+def bench_ssd(a):
+    from .. import ops
+    H, P, G, N, L, Bz = a.heads, 64, a.groups, 128, a.seq, a.batch
+    x = torch.randn(Bz, L, H, P, device="cuda").bfloat16().requires_grad_(True)
+    dt = (torch.rand(Bz, L, H, device="cuda") * 4 - 4).bfloat16().requires_grad_(True)
+    A = -(torch.rand(H, device="cuda") * 15 + 1)
+    Bm = (torch.randn(Bz, L, G, N, device="cuda") * 0.5).bfloat16().requires_grad_(True)
+    Cm = (torch.randn(Bz, L, G, N, device="cuda") * 0.5).bfloat16().requires_grad_(True)
+    D, bias = torch.ones(H, device="cuda"), torch.zeros(H, device="cuda")
+    if a.backward:
+        y = ops.ssd_chunk_scan(x, dt, A, Bm, Cm, D, bias)
+        gy = torch.randn_like(y)
+        fn = lambda: torch.autograd.grad(y, [x, dt, Bm, Cm], gy, retain_graph=True)
+    else:
+        fn = lambda: ops.ssd_chunk_scan(x.detach(), dt.detach(), A, Bm.detach(), Cm.detach(), D, bias)
+    ms = time_kernel(fn, a.iters)
+    byts = 2.0 * Bz * L * (2 * H * P + 2 * G * N + H) * (3 if a.backward else 1)
+    return ms, None, byts
+
+
+def bench_norm(a):
+    from .. import ops
+    rows, d = a.rows, a.cols
+    y = torch.randn(1, rows, d, device="cuda").bfloat16().requires_grad_(True)
+    z = torch.randn(1, rows, d, device="cuda").bfloat16().requires_grad_(True)
+    w = torch.ones(d, device="cuda").bfloat16().requires_grad_(True)
+    if a.backward:
+        out = ops.gated_rmsnorm(y, z, w, 1e-5, a.group)
+        go = torch.randn_like(out)
+        fn = lambda: torch.autograd.grad(out, [y, z, w], go, retain_graph=True)
+        byts = 2.0 * rows * d * 5
+    else:
+        fn = lambda: ops.gated_rmsnorm(y.detach(), z.detach(), w.detach(), 1e-5, a.group)
+        byts = 2.0 * rows * d * 3
+    return time_kernel(fn, a.iters), None, byts
+
+
+def bench_conv(a):
+    from .. import ops
+    x = torch.randn(a.batch, a.seq, a.cols, device="cuda").bfloat16().requires_grad_(True)
+    w = (torch.randn(a.cols, 1, 4, device="cuda") * 0.3).bfloat16().requires_grad_(True)
+    b = torch.zeros(a.cols, device="cuda").bfloat16().requires_grad_(True)
+    if a.backward:
+        out = ops.causal_conv1d_silu(x, w, b)
+        go = torch.randn_like(out)
+        fn = lambda: torch.autograd.grad(out, [x, w, b], go, retain_graph=True)
+        byts = 2.0 * a.batch * a.seq * a.cols * 3
+    else:
+        fn = lambda: ops.causal_conv1d_silu(x.detach(), w.detach(), b.detach())
+        byts = 2.0 * a.batch * a.seq * a.cols * 2
+    return time_kernel(fn, a.iters), None, byts
+
+
+def bench_attn(a):
+    from .. import ops
+    q = torch.randn(a.batch, a.seq, a.heads, 128, device="cuda").bfloat16().requires_grad_(True)
+    k = torch.randn(a.batch, a.seq, a.groups, 128, device="cuda").bfloat16().requires_grad_(True)
+    v = torch.randn(a.batch, a.seq, a.groups, 128, device="cuda").bfloat16().requires_grad_(True)
+    fl = 4.0 * a.batch * a.heads * a.seq * a.seq * 128 / 2
+    if a.backward:
+        o = ops.attention(q, k, v)
+        go = torch.randn_like(o)
+        fn = lambda: torch.autograd.grad(o, [q, k, v], go, retain_graph=True)
+        fl *= 2.5
+    else:
+        fn = lambda: ops.attention(q.detach(), k.detach(), v.detach())
+    return time_kernel(fn, a.iters), fl, None
+
+
+def bench_adamw(a):
+    n = a.n
+    master, m, v = [torch.zeros(n, device="cuda") for _ in range(3)]
+    g = torch.randn(n, device="cuda")
+    out = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    clip = torch.ones(1, device="cuda")
+    fn = lambda: cuda_ops.adamw_step(master, m, v, g, out, clip, 1e-3, 0.9, 0.95, 1e-8, 0.1, 1)
+    return time_kernel(fn, a.iters, flush=False), None, 30.0 * n
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["gemm", "ssd", "norm", "conv", "attn", "adamw"])
+    ap.add_argument("--m", type=int, default=2048)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--layout", default="tn", choices=["tn", "nn", "tt"])
+    ap.add_argument("--seq", type=int, default=2048)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--heads", type=int, default=128)
+    ap.add_argument("--groups", type=int, default=8)
+    ap.add_argument("--rows", type=int, default=2048)
+    ap.add_argument("--cols", type=int, default=8192)
+    ap.add_argument("--group", type=int, default=8192)
+    ap.add_argument("--backward", action="store_true")
+    ap.add_argument("--iters", type=int, default=10)
+    a = ap.parse_args(argv)
+    ms, flops, byts = {"gemm": bench_gemm, "ssd": bench_ssd, "norm": bench_norm, "conv": bench_conv,
+                       "attn": bench_attn, "adamw": bench_adamw}[a.kernel](a)
+    tf_peak, bw_peak, src = _peaks()
+    out = {"kernel": a.kernel, "args": {k: v for k, v in vars(a).items() if k != "kernel"}, "ms": ms}
+    if flops:
+        out["tflops"] = flops / ms / 1e9
+        out["frac_of_%s_bf16_peak" % src] = out["tflops"] / tf_peak
+    if byts:
+        out["gbs"] = byts / ms / 1e6
+        out["frac_of_%s_hbm_peak" % src] = out["gbs"] / bw_peak
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()

@@ -117,10 +117,39 @@ def run(args):
         from state_space_models_neuron_b200.utils.profiling import StepProfiler
         prof = StepProfiler(args.output_dir)
 
+    graphed = None
+    if args.cuda_graph:
+        if not use_cuda or args.grad_accum_usteps != 1:
+            raise SystemExit("--cuda_graph needs a CUDA device and --grad_accum_usteps 1")
     done = global_step >= args.max_steps
     while not done:
         for data in device_loader:
             training_step += 1
+            if args.cuda_graph:
+                if graphed is None:
+                    from state_space_models_neuron_b200.parallel.graph import GraphedTrainStep
+                    graphed = GraphedTrainStep(model, optimizer, data, warmup=2)
+                    global_step += graphed.eager_steps
+                    for _ in range(graphed.eager_steps):
+                        scheduler.step()
+                running_loss += graphed(data)
+                reduced = running_loss / dp_size
+                if dp_size > 1:
+                    dist.all_reduce(reduced, group=ps.get_data_parallel_group())
+                reduced = reduced.clone()
+                running_loss.zero_()
+                scheduler.step()
+                global_step += 1
+                if is_root and global_step % args.logging_interval == 0:
+                    step_time, tput, mfu = throughput.get_throughput()
+                    logger.log(global_step, reduced.item(), optimizer.param_groups[0]["lr"], step_time, tput, mfu,
+                               tokens_per_s=tput * args.seq_len)
+                if args.checkpoint_freq > 0 and global_step % args.checkpoint_freq == 0:
+                    save(global_step)
+                if global_step >= args.max_steps:
+                    done = True
+                    break
+                continue
             out = model(input_ids=data["input_ids"], labels=data["labels"], return_logits=False)
             loss = out.loss / args.grad_accum_usteps
             loss.backward()
@@ -205,6 +234,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--recompute_mixer", action="store_true", help="rebuild conv/scan intermediates in backward")
     p.add_argument("--resume", action="store_true", help="also restore optimizer, scheduler and step")
     p.add_argument("--profile", action="store_true")
+    p.add_argument("--cuda_graph", action="store_true",
+                   help="capture the whole optimizer step (fwd+bwd+collectives+AdamW) in one CUDA graph and replay it")
     p.add_argument("--device", default=None)
     return p
 
@@ -225,7 +256,8 @@ def main(argv=None):
     finally:
         if dist.is_initialized():
             dist.barrier()
-            dist.destroy_process_group()
+            if not args.cuda_graph:      # communicators referenced by a live graph are left to process exit
+                dist.destroy_process_group()
 
 
 if __name__ == "__main__":
