@@ -200,3 +200,151 @@ extern "C" int ssm_advance_counter(int* base, int stride, cudaStream_t st) {
   advance_counter_kernel<<<1, 1, 0, st>>>(base, stride);
   return (int)cudaGetLastError();
 }
+
+// =====================================================================================================
+// ZeRO-1 over peer memory: gradient reduce-scatter fused with scaling and the squared-norm partial, and the
+// sharded AdamW update fused with the all-gather of the updated low-precision parameters.
+// Every data-parallel rank keeps its flat fp32 gradient buffer and its flat bf16 parameter buffer in symmetric
+// memory.  Rank r owns elements [r*S, (r+1)*S).
+//   zero1_reduce   : publish "my gradients are final", wait for all ranks (bounded), then for the owned shard
+//                    g = (1/dp) * sum over ranks of their gradient (P2P loads), store g locally, add sum(g^2)
+//   zero1_adamw_push: AdamW on the owned fp32 master shard with the clip coefficient, store the new bf16 values
+//                    into every rank's parameter buffer (P2P stores), then publish "my shard has landed"
+//   zero1_wait     : wait until every rank's shard has landed (bounded) before later kernels read parameters
+// These replace reduce_scatter + scale + norm + AdamW + all_gather of the NxD ZeRO-1 wrapper the reference
+// enables with zero_one_enabled (train.py:73,129-138).
+// =====================================================================================================
+namespace ssm {
+
+__global__ void __launch_bounds__(256)
+zero1_reduce_kernel(PeerPtrs grads, float* __restrict__ shard_out, long long shard_start, long long n4, int nranks,
+                    int me, float scale, float* __restrict__ sumsq, PeerPtrs flags, int flag_base, int seq_off,
+                    const int* seq_base, int* status) {
+  const int seq = seq_off + (seq_base ? *seq_base : 0);
+  __shared__ int s_ok;
+  __shared__ float red[8];
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (blockIdx.x == 0 && threadIdx.x < nranks)      // this rank's backward is complete (stream order)
+    st_release_sys(reinterpret_cast<int*>(flags.p[threadIdx.x]) + flag_base + me, seq);
+  if (threadIdx.x < nranks) {
+    if (!wait_flag_ge(reinterpret_cast<const int*>(flags.p[me]) + flag_base + threadIdx.x, seq, status)) s_ok = 0;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  float local = 0.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    #pragma unroll
+    for (int k = 0; k < MAX_RANKS; ++k) {
+      const int r = (me + k) % MAX_RANKS;
+      if (r < nranks) {
+        const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[r]) + shard_start + i * 4);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+    }
+    acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+    *reinterpret_cast<float4*>(shard_out + i * 4) = acc;
+    local += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+  }
+  #pragma unroll
+  for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = local;
+  __syncthreads();
+  if (threadIdx.x == 0 && sumsq != nullptr) {
+    float t = 0.f;
+    for (int w = 0; w < 8; ++w) t += red[w];
+    atomicAdd(sumsq, t);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+zero1_adamw_push_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
+                        const float* __restrict__ g, PeerPtrs params, long long param_off, long long n4, int nranks,
+                        int me, const float* __restrict__ clip, float lr, float b1, float b2, float eps, float wd,
+                        const float* __restrict__ lr_dev, const int* __restrict__ step_dev, int step, PeerPtrs flags,
+                        int flag_base, int seq_off, const int* seq_base, int* counter, int publish) {
+  const int seq = seq_off + (seq_base ? *seq_base : 0);
+  const float c = clip ? *clip : 1.f;
+  if (lr_dev != nullptr) lr = *lr_dev;
+  const float st = step_dev != nullptr ? (float)(*step_dev) : (float)step;
+  const float ib1 = 1.f / (1.f - powf(b1, st)), ib2 = 1.f / (1.f - powf(b2, st));
+  const float decay = 1.f - lr * wd;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    const float4 gi = *reinterpret_cast<const float4*>(g + i * 4);
+    float4 mi = *reinterpret_cast<const float4*>(m + i * 4);
+    float4 vi = *reinterpret_cast<const float4*>(v + i * 4);
+    float4 wv = *reinterpret_cast<const float4*>(master + i * 4);
+    #define SSM_ADAM(f)                                             \
+      { const float gg = gi.f * c;                                  \
+        mi.f = b1 * mi.f + (1.f - b1) * gg;                         \
+        vi.f = b2 * vi.f + (1.f - b2) * gg * gg;                    \
+        wv.f = wv.f * decay - lr * (mi.f * ib1) / (sqrtf(vi.f * ib2) + eps); }
+    SSM_ADAM(x) SSM_ADAM(y) SSM_ADAM(z) SSM_ADAM(w)
+    #undef SSM_ADAM
+    *reinterpret_cast<float4*>(m + i * 4) = mi;
+    *reinterpret_cast<float4*>(v + i * 4) = vi;
+    *reinterpret_cast<float4*>(master + i * 4) = wv;
+    uint2 o;
+    o.x = pack_bf16(wv.x, wv.y); o.y = pack_bf16(wv.z, wv.w);
+    #pragma unroll
+    for (int k = 0; k < MAX_RANKS; ++k) {
+      const int r = (me + k) % MAX_RANKS;
+      if (r < nranks) *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(params.p[r]) + param_off + i * 4) = o;
+    }
+  }
+  if (!publish) return;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int done = atomicAdd(counter, 1) + 1;
+    if (done == (int)gridDim.x) {
+      __threadfence_system();
+      for (int t = 0; t < nranks; ++t) st_release_sys(reinterpret_cast<int*>(flags.p[t]) + flag_base + me, seq);
+      *counter = 0;
+    }
+  }
+}
+
+__global__ void zero1_wait_kernel(const int* flags, int flag_base, int nranks, int seq_off, const int* seq_base,
+                                  int* status) {
+  const int seq = seq_off + (seq_base ? *seq_base : 0);
+  if ((int)threadIdx.x < nranks) wait_flag_ge(flags + flag_base + threadIdx.x, seq, status);
+}
+
+}  // namespace ssm
+
+extern "C" int ssm_zero1_reduce(const void* const* grad_ptrs, void* shard_out, long long shard_start, long long n,
+                                int nranks, int me, float scale, void* sumsq, const void* const* flag_ptrs,
+                                int flag_base, int seq, const int* seq_base, int* status, cudaStream_t st) {
+  if (n % 4 || shard_start % 4 || nranks > MAX_RANKS) return -SSM_ERR_BAD_ARG;
+  const long long n4 = n / 4;
+  const int blocks = (int)((n4 + 255) / 256 < 148 * 8 ? (n4 + 255) / 256 : 148 * 8);
+  zero1_reduce_kernel<<<blocks, 256, 0, st>>>(to_peers(grad_ptrs, nranks), reinterpret_cast<float*>(shard_out),
+                                              shard_start, n4, nranks, me, scale, reinterpret_cast<float*>(sumsq),
+                                              to_peers(flag_ptrs, nranks), flag_base, seq, seq_base, status);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ssm_zero1_adamw_push(void* master, void* m, void* v, const void* g, const void* const* param_ptrs,
+                                    long long param_off, long long n, int nranks, int me, const void* clip, float lr,
+                                    float b1, float b2, float eps, float wd, const void* lr_dev, const void* step_dev,
+                                    int step, const void* const* flag_ptrs, int flag_base, int seq, const int* seq_base,
+                                    int* counter, int publish, cudaStream_t st) {
+  if (n % 4 || param_off % 4 || nranks > MAX_RANKS) return -SSM_ERR_BAD_ARG;
+  const long long n4 = n / 4;
+  const int blocks = (int)((n4 + 255) / 256 < 148 * 8 ? (n4 + 255) / 256 : 148 * 8);
+  zero1_adamw_push_kernel<<<blocks, 256, 0, st>>>(
+      reinterpret_cast<float*>(master), reinterpret_cast<float*>(m), reinterpret_cast<float*>(v),
+      reinterpret_cast<const float*>(g), to_peers(param_ptrs, nranks), param_off, n4, nranks, me,
+      reinterpret_cast<const float*>(clip), lr, b1, b2, eps, wd, reinterpret_cast<const float*>(lr_dev),
+      reinterpret_cast<const int*>(step_dev), step, to_peers(flag_ptrs, nranks), flag_base, seq, seq_base, counter,
+      publish);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ssm_zero1_wait(const void* flags, int flag_base, int nranks, int seq, const int* seq_base, int* status,
+                              cudaStream_t st) {
+  zero1_wait_kernel<<<1, 32, 0, st>>>(reinterpret_cast<const int*>(flags), flag_base, nranks, seq, seq_base, status);
+  return (int)cudaGetLastError();
+}

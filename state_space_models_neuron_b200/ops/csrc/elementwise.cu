@@ -114,29 +114,35 @@ conv1d_silu_fwd_kernel(const __nv_bfloat16* __restrict__ x, long long xs, const 
 // Backward.  dy for channels [0, c_split) comes from dy16 (bf16, row stride ds16); channels >= c_split from
 // dy32 (fp32, row stride ds32, indexed by channel - c_split).  dx is written with row stride dxs.
 // part [gridDim.z * gridDim.y, C, 5] receives per-tile partial sums (dw[0..3], db).
-__global__ void __launch_bounds__(128)
+// Each thread owns 4 channels and walks CONV_TOK (+3 halo) tokens; loads are issued four tokens at a time before
+// any arithmetic so that every thread keeps 8 requests in flight.
+constexpr int CONV_CPT = 4;
+
+__device__ __forceinline__ void unpack4(const uint2 u, float (&f)[4]) {
+  f[0] = bf16_lo(u.x); f[1] = bf16_hi(u.x); f[2] = bf16_lo(u.y); f[3] = bf16_hi(u.y);
+}
+
+__global__ void __launch_bounds__(128, 4)
 conv1d_silu_bwd_kernel(const __nv_bfloat16* __restrict__ x, long long xs, const __nv_bfloat16* __restrict__ w,
                        const __nv_bfloat16* __restrict__ bias, const __nv_bfloat16* __restrict__ dy16, long long ds16,
                        const float* __restrict__ dy32, long long ds32, int c_split,
                        __nv_bfloat16* __restrict__ dx, long long dxs, float* __restrict__ part, int L, int C) {
-  const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * CONV_CPT;
   if (c0 >= C) return;
   const int t0 = blockIdx.y * CONV_TOK;
   const int b = blockIdx.z;
-  float wt[CONV_K][8], bs[8];
+  float wt[CONV_K][CONV_CPT], bs[CONV_CPT];
   #pragma unroll
-  for (int e = 0; e < 8; ++e) {
+  for (int e = 0; e < CONV_CPT; ++e) {
     #pragma unroll
     for (int k = 0; k < CONV_K; ++k) wt[k][e] = __bfloat162float(w[(c0 + e) * CONV_K + k]);
     bs[e] = bias ? __bfloat162float(bias[c0 + e]) : 0.f;
   }
   const __nv_bfloat16* xb = x + (long long)b * L * xs + c0;
   const bool lo = c0 < c_split;
-  float xw[3][8];                 // sliding window x[t-3], x[t-2], x[t-1]
-  float dp[CONV_K][8];            // dpre[t-3 .. t]
-  float dw[CONV_K][8], db[8];
+  float xw[3][CONV_CPT], dp[CONV_K][CONV_CPT], dw[CONV_K][CONV_CPT], db[CONV_CPT];
   #pragma unroll
-  for (int e = 0; e < 8; ++e) {
+  for (int e = 0; e < CONV_CPT; ++e) {
     db[e] = 0.f;
     #pragma unroll
     for (int k = 0; k < CONV_K; ++k) { dw[k][e] = 0.f; dp[k][e] = 0.f; }
@@ -144,48 +150,69 @@ conv1d_silu_bwd_kernel(const __nv_bfloat16* __restrict__ x, long long xs, const 
   #pragma unroll
   for (int k = 0; k < 3; ++k) {
     const int t = t0 - 3 + k;
-    if (t >= 0) load8(xb + (long long)t * xs, xw[k]);
+    if (t >= 0) unpack4(*reinterpret_cast<const uint2*>(xb + (long long)t * xs), xw[k]);
     else {
       #pragma unroll
-      for (int e = 0; e < 8; ++e) xw[k][e] = 0.f;
+      for (int e = 0; e < CONV_CPT; ++e) xw[k][e] = 0.f;
     }
   }
-  // walk t over [t0, t0 + CONV_TOK + 3): dpre[t] is produced at step t, dx[t-3] is emitted at step t
-  #pragma unroll 5
-  for (int i = 0; i < CONV_TOK + 3; ++i) {
-    const int t = t0 + i;
-    float cur[8], g[8], d[8];
-    const bool valid = t < L;
-    if (valid) {
-      load8(xb + (long long)t * xs, cur);
-      if (lo) load8(dy16 + ((long long)b * L + t) * ds16 + c0, g);
-      else load8f(dy32 + ((long long)b * L + t) * ds32 + (c0 - c_split), g);
+  constexpr int NSTEP = CONV_TOK + 3;
+  constexpr int NB = (NSTEP + 3) / 4;
+  #pragma unroll 1
+  for (int ib = 0; ib < NB; ++ib) {
+    uint2 xr[4], g16[4];
+    float4 g32[4];
+    #pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int t = t0 + ib * 4 + k;
+      if (t < L && ib * 4 + k < NSTEP) {
+        xr[k] = *reinterpret_cast<const uint2*>(xb + (long long)t * xs);
+        if (lo) g16[k] = *reinterpret_cast<const uint2*>(dy16 + ((long long)b * L + t) * ds16 + c0);
+        else g32[k] = *reinterpret_cast<const float4*>(dy32 + ((long long)b * L + t) * ds32 + (c0 - c_split));
+      }
     }
     #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      float dpre = 0.f;
+    for (int k = 0; k < 4; ++k) {
+      const int i = ib * 4 + k;
+      const int t = t0 + i;
+      if (i >= NSTEP) break;
+      const bool valid = t < L;
+      float cur[CONV_CPT], g[CONV_CPT], d[CONV_CPT];
       if (valid) {
-        const float pre = bs[e] + wt[0][e] * xw[0][e] + wt[1][e] * xw[1][e] + wt[2][e] * xw[2][e] + wt[3][e] * cur[e];
-        const float s = sigmoid_f(pre);
-        dpre = g[e] * s * (1.f + pre * (1.f - s));
-        if (i < CONV_TOK) {
-          dw[0][e] += xw[0][e] * dpre; dw[1][e] += xw[1][e] * dpre; dw[2][e] += xw[2][e] * dpre;
-          dw[3][e] += cur[e] * dpre; db[e] += dpre;
-        }
-      } else {
-        cur[e] = 0.f;
+        unpack4(xr[k], cur);
+        if (lo) unpack4(g16[k], g);
+        else { g[0] = g32[k].x; g[1] = g32[k].y; g[2] = g32[k].z; g[3] = g32[k].w; }
       }
-      dp[0][e] = dp[1][e]; dp[1][e] = dp[2][e]; dp[2][e] = dp[3][e]; dp[3][e] = dpre;
-      // dx[t-3] = w3*dpre[t-3] + w2*dpre[t-2] + w1*dpre[t-1] + w0*dpre[t]
-      d[e] = wt[3][e] * dp[0][e] + wt[2][e] * dp[1][e] + wt[1][e] * dp[2][e] + wt[0][e] * dp[3][e];
-      xw[0][e] = xw[1][e]; xw[1][e] = xw[2][e]; xw[2][e] = cur[e];
+      #pragma unroll
+      for (int e = 0; e < CONV_CPT; ++e) {
+        float dpre = 0.f;
+        if (valid) {
+          const float pre = bs[e] + wt[0][e] * xw[0][e] + wt[1][e] * xw[1][e] + wt[2][e] * xw[2][e] + wt[3][e] * cur[e];
+          const float sg = sigmoid_f(pre);
+          dpre = g[e] * sg * (1.f + pre * (1.f - sg));
+          if (i < CONV_TOK) {
+            dw[0][e] += xw[0][e] * dpre; dw[1][e] += xw[1][e] * dpre; dw[2][e] += xw[2][e] * dpre;
+            dw[3][e] += cur[e] * dpre; db[e] += dpre;
+          }
+        } else {
+          cur[e] = 0.f;
+        }
+        dp[0][e] = dp[1][e]; dp[1][e] = dp[2][e]; dp[2][e] = dp[3][e]; dp[3][e] = dpre;
+        // dx[t-3] = w3*dpre[t-3] + w2*dpre[t-2] + w1*dpre[t-1] + w0*dpre[t]
+        d[e] = wt[3][e] * dp[0][e] + wt[2][e] * dp[1][e] + wt[1][e] * dp[2][e] + wt[0][e] * dp[3][e];
+        xw[0][e] = xw[1][e]; xw[1][e] = xw[2][e]; xw[2][e] = cur[e];
+      }
+      const int td = t - 3;
+      if (i >= 3 && td < L) {
+        uint2 o;
+        o.x = pack_bf16(d[0], d[1]); o.y = pack_bf16(d[2], d[3]);
+        *reinterpret_cast<uint2*>(dx + ((long long)b * L + td) * dxs + c0) = o;
+      }
     }
-    const int td = t - 3;
-    if (i >= 3 && td < L) store8(dx + ((long long)b * L + td) * dxs + c0, d);
   }
   float* pp = part + ((long long)(blockIdx.z * gridDim.y + blockIdx.y) * C + c0) * 5;
   #pragma unroll
-  for (int e = 0; e < 8; ++e) {
+  for (int e = 0; e < CONV_CPT; ++e) {
     pp[e * 5 + 0] = dw[0][e]; pp[e * 5 + 1] = dw[1][e]; pp[e * 5 + 2] = dw[2][e]; pp[e * 5 + 3] = dw[3][e];
     pp[e * 5 + 4] = db[e];
   }
@@ -655,8 +682,8 @@ extern "C" int ssm_conv1d_silu_fwd(const void* x, long long xs, const void* w, c
 extern "C" int ssm_conv1d_silu_bwd(const void* x, long long xs, const void* w, const void* bias, const void* dy16,
                                    long long ds16, const void* dy32, long long ds32, int c_split, void* dx,
                                    long long dxs, void* part, int B, int L, int C, cudaStream_t st) {
-  if (C % 8 || xs % 8 || dxs % 8 || c_split % 8) return -SSM_ERR_BAD_ARG;
-  dim3 grid((C / 8 + 127) / 128, (L + CONV_TOK - 1) / CONV_TOK, B);
+  if (C % 8 || xs % 8 || dxs % 8 || c_split % 8 || ds16 % 4 || ds32 % 4) return -SSM_ERR_BAD_ARG;
+  dim3 grid((C / CONV_CPT + 127) / 128, (L + CONV_TOK - 1) / CONV_TOK, B);
   conv1d_silu_bwd_kernel<<<grid, 128, 0, st>>>(BF(x), xs, BF(w), BF(bias), BF(dy16), ds16,
                                                reinterpret_cast<const float*>(dy32), ds32, c_split, BFM(dx), dxs,
                                                reinterpret_cast<float*>(part), L, C);

@@ -25,10 +25,13 @@ class _ParallelCrossEntropy(torch.autograd.Function):
         tp, grp = ps.get_tensor_model_parallel_size(), ps.get_tensor_model_parallel_group()
         m, s, tgt = ops.ce_partials(lg, lb, vocab_start)
         if tp > 1:
+            from . import fused
             gm = m.clone()
-            dist.all_reduce(gm, op=dist.ReduceOp.MAX, group=grp)
-            packed = torch.stack([s * torch.exp(m - gm), tgt], dim=0)
-            dist.all_reduce(packed, group=grp)
+            if not fused.small_allreduce(gm, "max"):
+                dist.all_reduce(gm, op=dist.ReduceOp.MAX, group=grp)
+            packed = torch.stack([s * torch.exp(m - gm), tgt], dim=0).contiguous()
+            if not fused.small_allreduce(packed.view(-1), "sum"):
+                dist.all_reduce(packed, group=grp)
             s, tgt, m = packed[0], packed[1], gm
         valid = lb != ignore_index
         loss = torch.where(valid, torch.log(s) + m - tgt, torch.zeros_like(s))

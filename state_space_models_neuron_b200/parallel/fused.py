@@ -1,6 +1,21 @@
 """Switchboard for the fused compute+collective kernels (filled in by parallel/fused_ops)."""
+import os
+
 _ENABLED = [True]
 _IMPL = [None]
+# the single-kernel small all-reduce replaces library all-reduces of tiny vectors; SSM_B200_SMALL_AR=0 turns it off
+_SMALL_AR = [os.environ.get("SSM_B200_SMALL_AR", "1") != "0"]
+
+
+_ZERO1 = [os.environ.get("SSM_B200_FUSED_ZERO1", "1") != "0"]
+
+
+def is_enabled() -> bool:
+    return bool(_ENABLED[0])
+
+
+def zero1_enabled() -> bool:
+    return bool(_ZERO1[0])
 
 
 def set_enabled(flag: bool) -> None:
@@ -26,3 +41,11 @@ def all_gather_linear(x, weight, bias=None):
 
 def linear_reduce_scatter(x, weight):
     return _IMPL[0].linear_reduce_scatter(x, weight)
+
+
+def small_allreduce(data, op: str = "sum") -> bool:
+    """Fused small all-reduce over the TP group; False means "not available, use the library collective"."""
+    if not (_ENABLED[0] and _SMALL_AR[0] and data.is_cuda) or _IMPL[0] is None:
+        return False
+    from . import fused_ops
+    return fused_ops.small_allreduce(data, op)

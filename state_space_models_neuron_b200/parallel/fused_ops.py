@@ -98,6 +98,26 @@ def _gemm_rs(a2, w, b_mn, ws):
     return out
 
 
+def small_allreduce(data: torch.Tensor, op: str = "sum") -> bool:
+    """In-place all-reduce (sum or max) of a small fp32 vector over the TP group through the symmetric workspace:
+    one single-CTA kernel in which every rank stores its vector into every rank's slot, publishes a flag, waits
+    (bounded) for the others and reduces locally.  Used for the cross-entropy statistics, sequence-parallel norm
+    gradients and the gradient norm instead of three library all-reduces (modeling_mamba2.py:505-510 of the
+    reference goes through parallel_cross_entropy).  Returns False (nothing done) when no workspace exists yet or
+    the vector does not fit, so the caller can use the library collective."""
+    ws = symm._WS
+    if (ws is None or ws.group is not ps.get_tensor_model_parallel_group() or not data.is_cuda
+            or data.dtype != torch.float32 or not data.is_contiguous() or data.numel() > symm.SMALL_N_MAX):
+        return False
+    CALLS["small_allreduce"] = CALLS.get("small_allreduce", 0) + 1
+    seq = ws.next_seq()
+    par = seq & 1
+    _run("ssm_small_allreduce", _P(data), data.numel(), symm.SMALL_N_MAX, ws.peer_ptrs(ws.slots_offset(par)),
+         ws.flag_ptr_array, ws.flag_base(symm.KIND_AR, par), ws.nranks, ws.me, seq, _P(ws.seq_base),
+         0 if op == "sum" else 1, _P(status_tensor(ws.device)), _st())
+    return True
+
+
 def _shape_ok(Ls, K, N, ws):
     return Ls % 128 == 0 and K % 8 == 0 and N % 8 == 0 and ws is not None
 

@@ -51,6 +51,14 @@ class Zero1Optimizer(torch.optim.Optimizer):
         self._build_flat_buffers()
 
     # ------------------------------------------------------------------------------------
+    def _want_fused_dp(self) -> bool:
+        """ZeRO-1 collectives inside our own kernels over peer memory (instead of NCCL reduce-scatter/all-gather):
+        CUDA, sharded, at most 8 DP ranks, bf16 parameters with fp32 gradients and master weights."""
+        from . import fused
+        return bool(self.shard and self.device.type == "cuda" and fused.is_enabled() and self.dp_size <= 8
+                    and self.param_dtype == torch.bfloat16 and self.grad_dtype == torch.float32
+                    and self.master_dtype == torch.float32 and fused.zero1_enabled())
+
     def _build_flat_buffers(self) -> None:
         entries = []  # (sort key, group index, param)
         seen = set()
@@ -75,8 +83,28 @@ class Zero1Optimizer(torch.optim.Optimizer):
             off += _ceil_to(p.numel(), _ALIGN)
         unit = _ALIGN * (self.dp_size if self.shard else 1)
         self.total = _ceil_to(off, unit)
-        self.flat_params = torch.zeros(self.total, dtype=self.param_dtype, device=self.device)
-        self.flat_grads = torch.zeros(self.total, dtype=self.grad_dtype, device=self.device)
+        self._fused_dp = self._want_fused_dp()
+        if self._fused_dp:
+            # flat buffers in symmetric memory of the DP group: peers read gradients and write parameters directly
+            import torch.distributed._symmetric_memory as symm_mem
+            self.flat_params = symm_mem.empty(self.total, dtype=self.param_dtype, device=self.device)
+            self.flat_grads = symm_mem.empty(self.total, dtype=self.grad_dtype, device=self.device)
+            self._zflags = symm_mem.empty(64, dtype=torch.int32, device=self.device)
+            self.flat_params.zero_(), self.flat_grads.zero_(), self._zflags.zero_()
+            hp = symm_mem.rendezvous(self.flat_params, self.dp_group)
+            hg = symm_mem.rendezvous(self.flat_grads, self.dp_group)
+            hf = symm_mem.rendezvous(self._zflags, self.dp_group)
+            self._peer_params = [int(x) for x in hp.buffer_ptrs]
+            self._peer_grads = [int(x) for x in hg.buffer_ptrs]
+            self._peer_flags = [int(x) for x in hf.buffer_ptrs]
+            self._symm_handles = (hp, hg, hf)
+            self._zseq_base = torch.zeros(1, dtype=torch.int32, device=self.device)
+            self._zcounter = torch.zeros(4, dtype=torch.int32, device=self.device)
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.dp_group)
+        else:
+            self.flat_params = torch.zeros(self.total, dtype=self.param_dtype, device=self.device)
+            self.flat_grads = torch.zeros(self.total, dtype=self.grad_dtype, device=self.device)
         for p, start, n, gi, rep in self.layout:
             self.flat_params[start:start + n].copy_(p.data.reshape(-1))
             p.data = self.flat_params[start:start + n].view(p.shape)
@@ -145,7 +173,12 @@ class Zero1Optimizer(torch.optim.Optimizer):
         if not tagged:
             return
         bucket = torch.cat([p.main_grad.reshape(-1) for p in tagged])
-        dist.all_reduce(bucket, group=self.tp_group)
+        from . import fused
+        done = bucket.dtype == torch.float32 and all(
+            fused.small_allreduce(bucket[i:i + 16384], "sum") for i in range(0, bucket.numel(), 16384)) \
+            if bucket.numel() <= 32 * 16384 else False
+        if not done:
+            dist.all_reduce(bucket, group=self.tp_group)
         off = 0
         for p in tagged:
             p.main_grad.copy_(bucket[off:off + p.numel()].view(p.shape))
@@ -179,11 +212,14 @@ class Zero1Optimizer(torch.optim.Optimizer):
                 from ..ops import cuda_ops
                 cuda_ops.sumsq_accumulate(seg, total)
             else:
-                total += seg.float().pow(2).sum()
+                for lo2 in range(0, seg.numel(), 1 << 26):
+                    total += seg[lo2:lo2 + (1 << 26)].float().pow(2).sum()
         if self.shard:
             dist.all_reduce(total, group=self.dp_group)
         if self.tp_size > 1:
-            dist.all_reduce(total, group=self.tp_group)
+            from . import fused
+            if not fused.small_allreduce(total, "sum"):
+                dist.all_reduce(total, group=self.tp_group)
         return total
 
     @torch.no_grad()
@@ -199,9 +235,11 @@ class Zero1Optimizer(torch.optim.Optimizer):
             self.upload_learning_rates()
         self._finish_lazy_zero()
         self._allreduce_sequence_parallel_grads()
-        g = self._reduce_gradients()
         self.step_count += 1
         self._dev_step.add_(1)
+        if self._fused_dp:
+            return self._fused_step()
+        g = self._reduce_gradients()
         clip = torch.ones(1, dtype=torch.float32, device=self.device)
         if self.max_grad_norm is not None:
             norm = torch.sqrt(self._grad_norm_sq(g))
@@ -223,6 +261,52 @@ class Zero1Optimizer(torch.optim.Optimizer):
             symm.advance_step()
         return None
 
+    def _fused_step(self):
+        """reduce-scatter(+1/dp, +norm partial) -> clip -> AdamW(+push of bf16 params to every rank) -> wait."""
+        import ctypes
+        from ..ops.cuda_ops import _P, _ll, _run, _st, status_tensor
+
+        def arr(ptrs):
+            a = (ctypes.c_void_p * 8)()
+            for i, p in enumerate(ptrs):
+                a[i] = p
+            return a
+        st = status_tensor(self.device)
+        g = self.shard_grad
+        total = self._norm_buf.zero_()
+        fused_norm = self.tp_size == 1 and self.max_grad_norm is not None
+        _run("ssm_zero1_reduce", arr(self._peer_grads), _P(g), _ll(self.shard_start), _ll(self.shard_size), self.dp_size,
+             self.dp_rank, ctypes.c_float(1.0 / self.dp_size), _P(total if fused_norm else None), arr(self._peer_flags),
+             0, 1, _P(self._zseq_base), _P(st), _st())
+        clip = torch.ones(1, dtype=torch.float32, device=self.device)
+        if self.max_grad_norm is not None:
+            if fused_norm:
+                dist.all_reduce(total, group=self.dp_group)
+            else:
+                total = self._grad_norm_sq(g)
+            norm = torch.sqrt(total)
+            self.last_grad_norm = norm
+            clip = torch.clamp(self.max_grad_norm / (norm + 1e-6), max=1.0)
+        else:
+            dist.barrier(group=self.dp_group)     # peers must finish reading gradients before the next backward
+        for k, (lo, hi, gi, rep) in enumerate(self.segments):
+            grp = self.param_groups[gi]
+            b1, b2 = grp["betas"]
+            last = k == len(self.segments) - 1
+            _run("ssm_zero1_adamw_push", _P(self.master[lo:hi]), _P(self.exp_avg[lo:hi]), _P(self.exp_avg_sq[lo:hi]),
+                 _P(g[lo:hi]), arr(self._peer_params), _ll(self.shard_start + lo), _ll(hi - lo), self.dp_size,
+                 self.dp_rank, _P(clip), ctypes.c_float(grp["lr"]), ctypes.c_float(b1), ctypes.c_float(b2),
+                 ctypes.c_float(grp["eps"]), ctypes.c_float(grp["weight_decay"]), _P(self._dev_lr[gi:gi + 1]),
+                 _P(self._dev_step), int(self.step_count), arr(self._peer_flags), 16, 2, _P(self._zseq_base),
+                 _P(self._zcounter), int(last), _st())
+        _run("ssm_zero1_wait", ctypes.c_void_p(self._peer_flags[self.dp_rank]), 16, self.dp_size, 2,
+             _P(self._zseq_base), _P(st), _st())
+        _run("ssm_advance_counter", _P(self._zseq_base), 4, _st())
+        if self.tp_size > 1:
+            from . import symm
+            symm.advance_step()
+        return None
+
     def _gloo_all_gather(self, out: torch.Tensor) -> None:
         parts = [torch.empty_like(out) for _ in range(self.dp_size)]
         dist.all_gather(parts, out.contiguous(), group=self.dp_group)
@@ -235,15 +319,18 @@ class Zero1Optimizer(torch.optim.Optimizer):
             from ..ops import cuda_ops
             cuda_ops.adamw_step(master, m, v, g, out, clip, lr, b1, b2, eps, wd, step, lr_dev, step_dev)
             return
-        gf = g.float() * clip
-        mf, vf, w = m.float(), v.float(), master.float()
-        mf.mul_(b1).add_(gf, alpha=1 - b1)
-        vf.mul_(b2).addcmul_(gf, gf, value=1 - b2)
         bc1, bc2 = 1 - b1 ** step, 1 - b2 ** step
-        w.mul_(1 - lr * wd)
-        w.addcdiv_(mf / bc1, (vf / bc2).sqrt_().add_(eps), value=-lr)
-        m.copy_(mf), v.copy_(vf), master.copy_(w)
-        out.copy_(w)
+        chunk = 1 << 26        # bounded temporaries: the flat buffers hold billions of elements
+        for lo in range(0, master.numel(), chunk):
+            sl = slice(lo, lo + chunk)
+            gf = g[sl].float() * clip
+            mf, vf, w = m[sl].float(), v[sl].float(), master[sl].float()
+            mf.mul_(b1).add_(gf, alpha=1 - b1)
+            vf.mul_(b2).addcmul_(gf, gf, value=1 - b2)
+            w.mul_(1 - lr * wd)
+            w.addcdiv_(mf / bc1, (vf / bc2).sqrt_().add_(eps), value=-lr)
+            m[sl].copy_(mf), v[sl].copy_(vf), master[sl].copy_(w)
+            out[sl].copy_(w)
 
     # ------------------------------------------------------------------------------------
     def state_dict(self) -> Dict:

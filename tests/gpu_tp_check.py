@@ -34,6 +34,25 @@ def build(tp, sp, hybrid, fused):
     return model, opt
 
 
+def build_solo(hybrid):
+    """TP=1, DP=1 on this rank alone (no collectives): the reference for the data-parallel check."""
+    from state_space_models_neuron_b200.parallel import state as st
+    st.destroy_model_parallel()
+    st._S = st._State(initialized=True)        # one-rank groups regardless of the launcher's world size
+    kw = dict(num_heads=16, head_dim=64, vocab_size=2048, hidden_size=512, state_size=128, num_hidden_layers=2,
+              n_groups=8, tie_word_embeddings=True, initializer_range=0.02, dtype=torch.bfloat16)
+    cfg = nxd.parallel_config(1, {"zero_one_enabled": False}, init_seed=3, fused_comm=False)
+    from state_space_models_neuron_b200.parallel.layers import set_init_seed
+    from state_space_models_neuron_b200.parallel import fused as fz
+    set_init_seed(3)
+    fz.set_enabled(False)
+    model = Mamba2ForCausalLM(Mamba2Config(**kw), device="cuda").to(torch.bfloat16)
+    model.lm_head.weight = model.backbone.embeddings.weight
+    opt = nxd.initialize_parallel_optimizer(cfg, nxd.AdamW_FP32OptimParams,
+                                            [{"params": list(model.parameters()), "weight_decay": 0.1}], lr=1e-3)
+    return model, opt
+
+
 def run(model, opt, ids, steps):
     losses = []
     for _ in range(steps):
@@ -48,22 +67,35 @@ def run(model, opt, ids, steps):
 def main():
     hybrid = "--hybrid" in sys.argv
     fused = "--fused" in sys.argv
+    dp_mode = "--dp" in sys.argv            # TP=1, DP=world: exercises the fused ZeRO-1 reduce/AdamW/push kernels
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     world = dist.get_world_size()
     g = torch.Generator().manual_seed(0)
-    shape = (1, 1024) if fused else (2, 512)      # the fused kernels take batch 1 (sequence-sharded rows)
+    shape = (1, 1024) if (fused and not dp_mode) else (world if dp_mode else 2, 512)
     ids = torch.randint(0, 2048, shape, generator=g).cuda()
-    m1, o1 = build(1, False, hybrid, False)
+    if dp_mode:
+        # single-rank reference: every rank runs the full batch in its own one-rank group
+        ps.destroy_model_parallel()
+    m1, o1 = build(1, False, hybrid, False) if not dp_mode else build_solo(hybrid)
     ref = run(m1, o1, ids, 3)
     del m1, o1
-    mt, ot = build(world, True, hybrid, fused)
-    got = run(mt, ot, ids, 3)
+    if dp_mode:
+        mt, ot = build(1, False, hybrid, fused)
+        mine = ids[ps.get_data_parallel_rank():ps.get_data_parallel_rank() + 1]
+        got = run(mt, ot, mine, 3)
+        t = torch.tensor(got, device="cuda")
+        dist.all_reduce(t)
+        got = (t / world).tolist()
+        assert getattr(ot, "_fused_dp", False) == fused, "fused ZeRO-1 path was not selected"
+    else:
+        mt, ot = build(world, True, hybrid, fused)
+        got = run(mt, ot, ids, 3)
     torch.cuda.synchronize()
     cuda_ops.check_status()
     ok = all(abs(a - b) < 0.05 for a, b in zip(ref, got))
-    if fused:
+    if fused and not dp_mode:
         from state_space_models_neuron_b200.parallel import fused_ops
         ok = ok and fused_ops.CALLS["ag_gemm"] > 0 and fused_ops.CALLS["gemm_rs"] > 0
         if dist.get_rank() == 0:

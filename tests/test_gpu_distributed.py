@@ -17,7 +17,7 @@ def _torchrun(n, *extra, port=29611):
     return subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
 
 
-@pytest.mark.parametrize("extra", [(), ("--fused",)])
+@pytest.mark.parametrize("extra", [(), ("--fused",), ("--fused", "--dp"), ("--fused", "--hybrid")])
 def test_tp_matches_single_gpu(extra):
     n = torch.cuda.device_count()
     if n < 2:
