@@ -79,9 +79,19 @@ def bench(args, device) -> dict:
     prompt = torch.randint(0, args.vocab_size, (args.batch, args.seq_len), generator=g).to(device)
     logits, cache = model.prefill(prompt)
     tok = logits[:, -1].argmax(-1, keepdim=True)
-    for _ in range(args.warmup):
-        tok = model.step(tok, cache).argmax(-1)
     cuda = device.type == "cuda"
+    graphed = None
+    if cuda and not args.no_graph:
+        from state_space_models_neuron_b200.parallel.graph import GraphedDecodeStep
+        graphed = GraphedDecodeStep(model, cache, args.batch)
+
+    def one_step(t):
+        if graphed is not None:
+            return graphed(t).clone()
+        return model.step(t, cache).argmax(-1)
+
+    for _ in range(args.warmup):
+        tok = one_step(tok)
     times = []
     if cuda:
         torch.cuda.synchronize()
@@ -91,7 +101,7 @@ def bench(args, device) -> dict:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
         t0 = time.perf_counter()
-        tok = model.step(tok, cache).argmax(-1)
+        tok = one_step(tok)
         if cuda:
             e1.record()
             e1.synchronize()
@@ -104,7 +114,8 @@ def bench(args, device) -> dict:
         dist.all_reduce(total, op=dist.ReduceOp.MAX)
     res = {"metric": "decode tokens/s", "value": args.batch * args.decode_tokens / total.item(),
            "p50_latency_ms": t.median().item() * 1e3, "batch": args.batch, "prefill": args.seq_len,
-           "decode_tokens": args.decode_tokens, "tp": ps.get_tensor_model_parallel_size(), "model": args.model}
+           "decode_tokens": args.decode_tokens, "tp": ps.get_tensor_model_parallel_size(), "model": args.model,
+           "cuda_graph": graphed is not None}
     if ps.is_master():
         print(json.dumps(res))
     return res
@@ -127,6 +138,7 @@ def main(argv=None):
     ap.add_argument("--rmsnorm_across_groups", action="store_true")
     ap.add_argument("--checkpoint_path", default=None)
     ap.add_argument("--device", default=None)
+    ap.add_argument("--no_graph", action="store_true", help="decode with eager launches instead of a CUDA graph")
     args = ap.parse_args(argv)
     ps.initialize_model_parallel(args.tp)
     device = torch.device(args.device) if args.device else (

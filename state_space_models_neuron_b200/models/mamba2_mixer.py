@@ -126,9 +126,19 @@ class Mamba2Mixer(nn.Module):
             _mark(p, 0)
         self.norm = MambaRMSNormGated(self.intermediate_size, eps=self.layer_norm_epsilon, n_groups=self.n_groups,
                                       rmsnorm_within_groups=config.rmsnorm_within_groups, dtype=dtype, device=device)
+        out_init = None
+        if getattr(config, "rescale_prenorm_residual", False):
+            # GPT-2 style: residual-branch output projections are drawn as usual and scaled by 1/sqrt(n_layers)
+            # (mamba2/modeling_mamba2.py:172-187 of the reference)
+            from ..parallel.layers import default_linear_init
+            scale = 1.0 / math.sqrt(config.num_hidden_layers)
+
+            def out_init(w, generator=None):
+                default_linear_init(w, generator=generator)
+                w.mul_(scale)
         self.out_proj = RowParallelLinear(self.intermediate_size, self.hidden_size, bias=config.use_bias,
-                                          dtype=dtype, sequence_parallel_enabled=config.sequence_parallel_enabled,
-                                          device=device)
+                                          init_method=out_init, dtype=dtype,
+                                          sequence_parallel_enabled=config.sequence_parallel_enabled, device=device)
 
     def _core_kwargs(self):
         return dict(d_inner=self.intermediate_size_tp, n_groups=self.n_groups_tp, d_state=self.ssm_state_size,

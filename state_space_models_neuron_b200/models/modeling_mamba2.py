@@ -143,6 +143,15 @@ class Mamba2Model(Mamba2PreTrainedModel):
             hidden = mp.scatter_to_sequence_parallel_region(inputs_embeds) if sp else inputs_embeds
         if use_cache and cache_params is None:
             cache_params = Mamba2Cache(self.config, hidden.shape[0], dtype=hidden.dtype, device=hidden.device)
+        if use_cache and cache_params.seqlen_offset > 0 and hidden.shape[1] == 1 and not self.training:
+            # incremental decoding (what `generate()` does after the prompt): one token over the cached states
+            residual = None
+            for block in self.layers:
+                hidden, residual = block.step(hidden, residual, cache_params)
+            rd = torch.float32 if self.config.residual_in_fp32 else None
+            hidden, _ = self.norm_f.forward_add(hidden, residual, rd)
+            cache_params.seqlen_offset += 1
+            return Mamba2Output(last_hidden_state=hidden, cache_params=cache_params)
         all_hidden = () if output_hidden_states else None
         residual = None
         for block in self.layers:
@@ -245,6 +254,43 @@ class Mamba2ForCausalLM(Mamba2PreTrainedModel, GenerationMixin):
             cache_params = Mamba2Cache(self.config, input_ids.shape[0], dtype=p.dtype, device=p.device)
         out = self.backbone(input_ids=input_ids, cache_params=cache_params, use_cache=True)
         return self.lm_head(out.last_hidden_state[:, -1:, :]).float(), cache_params
+
+    @torch.no_grad()
+    def generate_tokens(self, input_ids, max_new_tokens: int, temperature: float = 0.0, top_k: Optional[int] = None,
+                        eos_token_id: Optional[int] = None, generator=None):
+        """Prompt -> continuation with the cached decode path: the longest 128-multiple prefix of the prompt goes
+        through the chunked scan (prefill), the rest of the prompt and every new token through `step`.
+        temperature 0 = greedy.  Returns [B, L + new] token ids.  (HuggingFace's `generate()` plumbing is kept for
+        API compatibility, but like in the reference it does not drive this cache.)"""
+        B, L = input_ids.shape
+        p = next(self.parameters())
+        cache = Mamba2Cache(self.config, B, dtype=p.dtype, device=p.device)
+        chunk = 128
+        Lp = (L // chunk) * chunk
+        logits = None
+        if Lp:
+            logits, cache = self.prefill(input_ids[:, :Lp], cache)
+        for t in range(Lp, L):
+            logits = self.step(input_ids[:, t:t + 1], cache)
+        out = [input_ids]
+        done = torch.zeros(B, dtype=torch.bool, device=input_ids.device)
+        for _ in range(max_new_tokens):
+            last = logits[:, -1].float()
+            if temperature and temperature > 0:
+                last = last / temperature
+                if top_k:
+                    kth = torch.topk(last, top_k, dim=-1).values[:, -1:]
+                    last = last.masked_fill(last < kth, float("-inf"))
+                nxt = torch.multinomial(torch.softmax(last, -1), 1, generator=generator)
+            else:
+                nxt = last.argmax(-1, keepdim=True)
+            out.append(nxt)
+            if eos_token_id is not None:
+                done |= nxt[:, 0] == eos_token_id
+                if bool(done.all()):
+                    break
+            logits = self.step(nxt, cache)
+        return torch.cat(out, dim=1)
 
     @torch.no_grad()
     def step(self, input_ids, cache_params: Mamba2Cache):

@@ -61,3 +61,42 @@ class GraphedTrainStep:
         self.optimizer.step_count += 1
         self.replays += 1
         return self.static_loss
+
+
+class GraphedDecodeStep:
+    """One autoregressive decode step (all layers, LM head, greedy argmax) captured as a CUDA graph.
+
+    The conv/SSM caches are updated in place by the kernels, so replaying the graph advances them; the token
+    buffer is static.  Warm-up and capture run on a copy of the cache contents which is restored afterwards, so
+    constructing the object does not disturb the decoding state."""
+
+    def __init__(self, model, cache, batch_size: int, warmup: int = 2):
+        self.model, self.cache = model, cache
+        dev = next(model.parameters()).device
+        self.token = torch.zeros(batch_size, 1, dtype=torch.long, device=dev)
+        saved = {k: (cache.conv_states[k].clone(), cache.ssm_states[k].clone()) for k in cache.conv_states}
+        offset = cache.seqlen_offset
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side), torch.no_grad():
+            for _ in range(warmup):
+                model.step(self.token, cache)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.no_grad(), torch.cuda.graph(self.graph):
+            self.logits = model.step(self.token, cache)
+            self.next_token = self.logits[:, -1].argmax(-1, keepdim=True)
+        for k, (c, s) in saved.items():
+            cache.conv_states[k].copy_(c)
+            cache.ssm_states[k].copy_(s)
+        cache.seqlen_offset = offset
+
+    @torch.no_grad()
+    def __call__(self, token: torch.Tensor) -> torch.Tensor:
+        """token [B, 1] -> next greedy token [B, 1] (device tensor, overwritten by the next call); the logits of
+        this step are in `self.logits`."""
+        self.token.copy_(token, non_blocking=True)
+        self.graph.replay()
+        self.cache.seqlen_offset += 1
+        return self.next_token

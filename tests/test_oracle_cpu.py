@@ -121,3 +121,17 @@ def test_matches_huggingface_mamba2_mixer():
         ours = model(input_ids=ids).logits
         theirs = hf(input_ids=ids).logits
     assert torch.allclose(ours, theirs, atol=2e-4, rtol=1e-3), (ours - theirs).abs().max()
+
+
+def test_generate_tokens_matches_full_forward_greedy():
+    model, _ = _tiny_model()
+    model.eval()
+    ids = torch.randint(0, 1024, (2, 150))          # 128 tokens prefilled, 22 stepped
+    out = model.generate_tokens(ids, max_new_tokens=3)
+    assert out.shape == (2, 153) and torch.equal(out[:, :150], ids)
+    with torch.no_grad():
+        cache = Mamba2Cache(model.config, 2, dtype=torch.float32)
+        ref = None
+        for t in range(150):
+            ref = model.step(ids[:, t:t + 1], cache)
+    assert torch.equal(out[:, 150], ref[:, -1].argmax(-1))
