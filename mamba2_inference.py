@@ -17,6 +17,7 @@ import torch.distributed as dist
 
 from state_space_models_neuron_b200.models import Mamba2Cache, Mamba2ForCausalLM, get_config
 from state_space_models_neuron_b200.parallel import state as ps
+from state_space_models_neuron_b200.parallel.cross_entropy import parallel_argmax
 from state_space_models_neuron_b200.parallel.layers import set_init_seed
 
 
@@ -78,7 +79,7 @@ def bench(args, device) -> dict:
     g = torch.Generator().manual_seed(args.seed)
     prompt = torch.randint(0, args.vocab_size, (args.batch, args.seq_len), generator=g).to(device)
     logits, cache = model.prefill(prompt)
-    tok = logits[:, -1].argmax(-1, keepdim=True)
+    tok = parallel_argmax(logits[:, -1]).unsqueeze(-1)
     cuda = device.type == "cuda"
     graphed = None
     if cuda and not args.no_graph:
@@ -88,7 +89,7 @@ def bench(args, device) -> dict:
     def one_step(t):
         if graphed is not None:
             return graphed(t).clone()
-        return model.step(t, cache).argmax(-1)
+        return parallel_argmax(model.step(t, cache)[:, -1]).unsqueeze(-1)
 
     for _ in range(args.warmup):
         tok = one_step(tok)

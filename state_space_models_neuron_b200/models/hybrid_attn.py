@@ -46,16 +46,25 @@ class Mamba2HybridAttention(nn.Module):
                                         sequence_parallel_enabled=config.sequence_parallel_enabled)
 
     def forward(self, hidden_states: torch.Tensor, cache_params=None) -> torch.Tensor:
+        qkv = None
         if self.sequence_parallel_enabled:
-            x = mp.gather_from_sequence_parallel_region(hidden_states, True)
+            from ..parallel import fused
+            if fused.enabled_for(hidden_states):
+                qkv = fused.all_gather_multi_linear(
+                    hidden_states, (self.q_proj.weight, self.k_proj.weight, self.v_proj.weight))
+            if qkv is None:
+                x = mp.gather_from_sequence_parallel_region(hidden_states, True)
         else:
             x = mp.copy_to_tensor_parallel_region(hidden_states)
-        B, L, _ = x.shape
-        q = ops.linear(x, self.q_proj.weight).view(B, L, self.num_heads, self.head_dim)
-        k = ops.linear(x, self.k_proj.weight).view(B, L, self.num_kv_heads, self.head_dim)
-        v = ops.linear(x, self.v_proj.weight).view(B, L, self.num_kv_heads, self.head_dim)
+        if qkv is None:
+            qkv = (ops.linear(x, self.q_proj.weight), ops.linear(x, self.k_proj.weight),
+                   ops.linear(x, self.v_proj.weight))
+        B, L = qkv[0].shape[0], qkv[0].shape[1]
+        q = qkv[0].view(B, L, self.num_heads, self.head_dim)
+        k = qkv[1].view(B, L, self.num_kv_heads, self.head_dim)
+        v = qkv[2].view(B, L, self.num_kv_heads, self.head_dim)
         if self.rotary_emb_dim is not None:
-            cos, sin = ops.oracle.rotary_tables(L, self.rotary_emb_dim, self.rope_theta, device=x.device)
+            cos, sin = ops.oracle.rotary_tables(L, self.rotary_emb_dim, self.rope_theta, device=q.device)
             q = ops.oracle.apply_rotary(q, cos, sin)
             k = ops.oracle.apply_rotary(k, cos, sin)
         o = ops.attention(q, k, v, causal=True)

@@ -19,7 +19,7 @@ from transformers.utils import ModelOutput
 from .. import ops
 from ..parallel import mappings as mp
 from ..parallel import state as ps
-from ..parallel.cross_entropy import parallel_cross_entropy
+from ..parallel.cross_entropy import parallel_argmax, parallel_cross_entropy
 from ..parallel.layers import ColumnParallelLinear, ParallelEmbedding, normal_init
 from .cache import Mamba2Cache
 from .configuration_mamba2 import Mamba2Config
@@ -170,6 +170,9 @@ class Mamba2Model(Mamba2PreTrainedModel):
     @torch.no_grad()
     def step(self, input_ids, cache_params: Mamba2Cache):
         """One decode token through all blocks (mamba2/modeling_mamba2.py:337-350)."""
+        if ps.get_tensor_model_parallel_size() > 1 and input_ids.is_cuda:
+            from ..parallel import symm
+            symm.advance_step()      # fresh sequence numbers for this token's fused collectives
         hidden = self.embeddings(input_ids)
         residual = None
         for block in self.layers:
@@ -277,13 +280,17 @@ class Mamba2ForCausalLM(Mamba2PreTrainedModel, GenerationMixin):
         for _ in range(max_new_tokens):
             last = logits[:, -1].float()
             if temperature and temperature > 0:
+                if ps.get_tensor_model_parallel_size() > 1:      # sampling needs the whole vocabulary
+                    parts = [torch.empty_like(last) for _ in range(ps.get_tensor_model_parallel_size())]
+                    torch.distributed.all_gather(parts, last.contiguous(), group=ps.get_tensor_model_parallel_group())
+                    last = torch.cat(parts, dim=-1)
                 last = last / temperature
                 if top_k:
                     kth = torch.topk(last, top_k, dim=-1).values[:, -1:]
                     last = last.masked_fill(last < kth, float("-inf"))
                 nxt = torch.multinomial(torch.softmax(last, -1), 1, generator=generator)
             else:
-                nxt = last.argmax(-1, keepdim=True)
+                nxt = parallel_argmax(last).unsqueeze(-1)
             out.append(nxt)
             if eos_token_id is not None:
                 done |= nxt[:, 0] == eos_token_id

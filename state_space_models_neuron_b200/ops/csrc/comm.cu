@@ -348,3 +348,228 @@ extern "C" int ssm_zero1_wait(const void* flags, int flag_base, int nranks, int 
   zero1_wait_kernel<<<1, 32, 0, st>>>(reinterpret_cast<const int*>(flags), flag_base, nranks, seq, seq_base, status);
   return (int)cudaGetLastError();
 }
+
+namespace ssm {
+
+// =====================================================================================================
+// One-shot all-reduce (sum) of a bf16 activation over the TP group, for the latency-bound decode path
+// (row-parallel out_proj of one token per sequence: [batch, d_model] per layer).  Every rank stores its vector
+// into slot[me] of every rank, the last CTA publishes the flag, all CTAs wait (bounded) for the T sources and sum
+// the T slots in fp32.  The grid must be co-resident (<= number of SMs): CTAs wait for peers, not for each other.
+// =====================================================================================================
+__global__ void __launch_bounds__(256)
+oneshot_allreduce_bf16_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, long long nvec,
+                              PeerPtrs slots, long long slot_stride, int nranks, int me, PeerPtrs flags,
+                              int flag_base, int seq_off, const int* seq_base, int* counter, int* status) {
+  const int seq = seq_off + (seq_base ? *seq_base : 0);
+  const long long step = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += step) {
+    const uint4 v = reinterpret_cast<const uint4*>(in)[i];
+    #pragma unroll
+    for (int k = 0; k < MAX_RANKS; ++k) {
+      const int t = (me + k) % MAX_RANKS;
+      if (t < nranks) reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(slots.p[t]) + me * slot_stride)[i] = v;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    s_ok = 1;
+    const int done = atomicAdd(counter, 1) + 1;
+    if (done == (int)gridDim.x) {
+      __threadfence_system();
+      for (int t = 0; t < nranks; ++t) st_release_sys(reinterpret_cast<int*>(flags.p[t]) + flag_base + me, seq);
+      *counter = 0;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < nranks) {
+    if (!wait_flag_ge(reinterpret_cast<const int*>(flags.p[me]) + flag_base + threadIdx.x, seq, status)) s_ok = 0;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const __nv_bfloat16* mine = reinterpret_cast<const __nv_bfloat16*>(slots.p[me]);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += step) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < nranks; ++s) {
+      const uint4 u = reinterpret_cast<const uint4*>(mine + s * slot_stride)[i];
+      acc[0] += bf16_lo(u.x); acc[1] += bf16_hi(u.x); acc[2] += bf16_lo(u.y); acc[3] += bf16_hi(u.y);
+      acc[4] += bf16_lo(u.z); acc[5] += bf16_hi(u.z); acc[6] += bf16_lo(u.w); acc[7] += bf16_hi(u.w);
+    }
+    uint4 o;
+    o.x = pack_bf16(acc[0], acc[1]); o.y = pack_bf16(acc[2], acc[3]);
+    o.z = pack_bf16(acc[4], acc[5]); o.w = pack_bf16(acc[6], acc[7]);
+    reinterpret_cast<uint4*>(out)[i] = o;
+  }
+}
+
+// =====================================================================================================
+// Vocabulary-parallel embedding over peer memory.
+// The reference sums T masked partial lookups with an all-reduce and then keeps one sequence slice
+// (mamba2/modeling_mamba2.py:276,300-301).  Every token's row lives on exactly one rank, so nothing has to be
+// summed: the rank that holds row ids[t] stores it straight into the output buffer of the rank that owns token
+// t's sequence slice, and a flag per source says "all my rows have landed".
+//   embed_lookup    : local masked lookup (ids outside [vocab_start, vocab_start + vloc) give zero rows)
+//   vocab_embed_push: for token (b, l) with a local id: dst[l / Ls][(b * Ls + l % Ls), :] = weight[id - vocab_start]
+//   embed_wait_copy : wait (bounded) for all sources, copy the landing buffer to the output tensor
+//   embed_bwd       : grad32[id - vocab_start, :] += g[row(t), :] for the local ids; g is either the local
+//                     gradient (one rank) or the gather buffer that the push kernel above filled (waits first)
+// =====================================================================================================
+__global__ void __launch_bounds__(256)
+embed_lookup_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ weight, long long vocab_start,
+                    long long vloc, __nv_bfloat16* __restrict__ out, long long ntok, int D) {
+  const int vec = D / 8;
+  for (long long t = blockIdx.x; t < ntok; t += gridDim.x) {
+    const long long id = ids[t] - vocab_start;
+    const bool in = id >= 0 && id < vloc;
+    for (int c = threadIdx.x; c < vec; c += blockDim.x) {
+      const uint4 v = in ? *reinterpret_cast<const uint4*>(weight + id * D + c * 8) : make_uint4(0, 0, 0, 0);
+      *reinterpret_cast<uint4*>(out + t * D + c * 8) = v;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+vocab_embed_push_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ weight,
+                        long long vocab_start, long long vloc, PeerPtrs dst, int B, int L, int Ls, int D, int nranks,
+                        int me, PeerPtrs flags, int flag_base, int seq_off, const int* seq_base, int* counter) {
+  const int seq = seq_off + (seq_base ? *seq_base : 0);
+  const int vec = D / 8;
+  const long long ntok = (long long)B * L;
+  for (long long t = blockIdx.x; t < ntok; t += gridDim.x) {
+    const long long id = ids[t] - vocab_start;
+    if (id < 0 || id >= vloc) continue;
+    const int b = (int)(t / L), l = (int)(t % L);
+    const int owner = l / Ls;
+    if (owner >= nranks) continue;
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(dst.p[owner]) + ((long long)b * Ls + (l % Ls)) * D;
+    for (int c = threadIdx.x; c < vec; c += blockDim.x)
+      *reinterpret_cast<uint4*>(o + c * 8) = *reinterpret_cast<const uint4*>(weight + id * D + c * 8);
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int done = atomicAdd(counter, 1) + 1;
+    if (done == (int)gridDim.x) {
+      __threadfence_system();
+      for (int t = 0; t < nranks; ++t) st_release_sys(reinterpret_cast<int*>(flags.p[t]) + flag_base + me, seq);
+      *counter = 0;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+embed_wait_copy_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ out, long long nvec,
+                       int nranks, const int* flags, int flag_base, int seq_off, const int* seq_base, int* status) {
+  const int seq = seq_off + (seq_base ? *seq_base : 0);
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (threadIdx.x < nranks) {
+    if (!wait_flag_ge(flags + flag_base + threadIdx.x, seq, status)) s_ok = 0;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x)
+    reinterpret_cast<uint4*>(out)[i] = reinterpret_cast<const uint4*>(src)[i];
+}
+
+__global__ void __launch_bounds__(256)
+embed_bwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ g, long long g_ld,
+                 float* __restrict__ grad32, long long vocab_start, long long vloc, int B, int L, int Ls, int D,
+                 int nranks, const int* flags, int flag_base, int seq_off, const int* seq_base, int* status) {
+  if (nranks > 1) {
+    const int seq = seq_off + (seq_base ? *seq_base : 0);
+    __shared__ int s_ok;
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if (threadIdx.x < nranks) {
+      if (!wait_flag_ge(flags + flag_base + threadIdx.x, seq, status)) s_ok = 0;
+    }
+    __syncthreads();
+    if (!s_ok) return;
+  }
+  const int vec = D / 4;
+  const long long ntok = (long long)B * L;
+  for (long long t = blockIdx.x; t < ntok; t += gridDim.x) {
+    const long long id = ids[t] - vocab_start;
+    if (id < 0 || id >= vloc) continue;
+    const int b = (int)(t / L), l = (int)(t % L);
+    // row of token (b, l) in g: [B, L] order on one rank, [owner][b][l % Ls] in the gather buffer
+    const long long r = nranks > 1 ? ((long long)(l / Ls) * B + b) * Ls + (l % Ls) : t;
+    const __nv_bfloat16* src = g + r * g_ld;
+    float* dstp = grad32 + id * D;
+    for (int c = threadIdx.x; c < vec; c += blockDim.x) {
+      const uint2 u = *reinterpret_cast<const uint2*>(src + c * 4);
+      asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dstp + c * 4), "f"(bf16_lo(u.x)),
+                   "f"(bf16_hi(u.x)), "f"(bf16_lo(u.y)), "f"(bf16_hi(u.y)) : "memory");
+    }
+  }
+}
+
+}  // namespace ssm
+using namespace ssm;
+
+extern "C" int ssm_embed_lookup(const void* ids, const void* weight, long long vocab_start, long long vloc, void* out,
+                                long long ntok, int D, cudaStream_t st) {
+  if (D % 8 || ntok < 1) return -SSM_ERR_BAD_ARG;
+  const int blocks = (int)(ntok < 148 * 8 ? ntok : 148 * 8);
+  embed_lookup_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const long long*>(ids),
+                                              reinterpret_cast<const __nv_bfloat16*>(weight), vocab_start, vloc,
+                                              reinterpret_cast<__nv_bfloat16*>(out), ntok, D);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ssm_vocab_embed_push(const void* ids, const void* weight, long long vocab_start, long long vloc,
+                                    const void* const* dst_ptrs, int B, int L, int Ls, int D, int nranks, int me,
+                                    const void* const* flag_ptrs, int flag_base, int seq, const int* seq_base,
+                                    int* counter, cudaStream_t st) {
+  if (D % 8 || nranks > MAX_RANKS || nranks < 1 || Ls < 1 || L != Ls * nranks) return -SSM_ERR_BAD_ARG;
+  const long long ntok = (long long)B * L;
+  const int blocks = (int)(ntok < 148 * 4 ? ntok : 148 * 4);
+  vocab_embed_push_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const long long*>(ids),
+                                                  reinterpret_cast<const __nv_bfloat16*>(weight), vocab_start, vloc,
+                                                  to_peers(dst_ptrs, nranks), B, L, Ls, D, nranks, me,
+                                                  to_peers(flag_ptrs, nranks), flag_base, seq, seq_base, counter);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ssm_embed_wait_copy(const void* src, void* out, long long nelem, int nranks, const void* flags,
+                                   int flag_base, int seq, const int* seq_base, int* status, cudaStream_t st) {
+  if (nelem % 8 || nranks > MAX_RANKS) return -SSM_ERR_BAD_ARG;
+  const long long nvec = nelem / 8;
+  const int blocks = (int)((nvec + 255) / 256 < 148 * 4 ? (nvec + 255) / 256 : 148 * 4);
+  embed_wait_copy_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(src),
+                                                 reinterpret_cast<__nv_bfloat16*>(out), nvec, nranks,
+                                                 reinterpret_cast<const int*>(flags), flag_base, seq, seq_base, status);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ssm_embed_bwd(const void* ids, const void* g, long long g_ld, void* grad32, long long vocab_start,
+                             long long vloc, int B, int L, int Ls, int D, int nranks, const void* flags, int flag_base,
+                             int seq, const int* seq_base, int* status, cudaStream_t st) {
+  if (D % 4 || g_ld % 4 || nranks > MAX_RANKS || nranks < 1) return -SSM_ERR_BAD_ARG;
+  const long long ntok = (long long)B * L;
+  const int blocks = (int)(ntok < 148 * 8 ? ntok : 148 * 8);
+  embed_bwd_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const long long*>(ids),
+                                           reinterpret_cast<const __nv_bfloat16*>(g), g_ld,
+                                           reinterpret_cast<float*>(grad32), vocab_start, vloc, B, L, Ls, D, nranks,
+                                           reinterpret_cast<const int*>(flags), flag_base, seq, seq_base, status);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ssm_allreduce_bf16(const void* in, void* out, long long n, const void* const* slot_ptrs,
+                                  long long slot_stride, int nranks, int me, const void* const* flag_ptrs,
+                                  int flag_base, int seq, const int* seq_base, int* counter, int* status,
+                                  cudaStream_t st) {
+  if (n % 8 || slot_stride % 8 || n > slot_stride || nranks > MAX_RANKS || nranks < 1) return -SSM_ERR_BAD_ARG;
+  const long long nvec = n / 8;
+  long long blocks = (nvec + 255) / 256;
+  if (blocks > 64) blocks = 64;            // co-resident by a wide margin; 64 x 256 x 16 B per pass
+  oneshot_allreduce_bf16_kernel<<<(int)blocks, 256, 0, st>>>(
+      reinterpret_cast<const __nv_bfloat16*>(in), reinterpret_cast<__nv_bfloat16*>(out), nvec,
+      to_peers(slot_ptrs, nranks), slot_stride, nranks, me, to_peers(flag_ptrs, nranks), flag_base, seq, seq_base,
+      counter, status);
+  return (int)cudaGetLastError();
+}

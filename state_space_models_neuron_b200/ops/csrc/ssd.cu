@@ -287,6 +287,14 @@ ssd_chunk_scan_fwd_kernel(const __grid_constant__ CUtensorMap tm_xbc, const __gr
     const float li = s_l[i];
     #pragma unroll 1
     for (int jb = 0; jb < 4; ++jb) {
+      if (jb > warp) {      // columns j > i for every row of this warp: the causal mask zeroes the whole block
+        #pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          const int jc = jb * 32 + ch * 8;
+          *reinterpret_cast<uint4*>(sC + (jc >> 6) * (TILE128 / 2) + sw128_offset(i, (jc & 63) >> 3)) = make_uint4(0, 0, 0, 0);
+        }
+        continue;
+      }
       uint32_t v[32];
       tmem_ld32(tmem_addr(tmem, warp * 32, jb * 32), v);
       tmem_ld_wait();
@@ -378,7 +386,19 @@ struct ScanBwdParams {
 
 constexpr int BWD_SMEM = 2 * TILE128 /*C,B*/ + 4 * TILE64 /*X,dY,Sin,dSout*/ + 2 * TILE128 /*M0,dCB*/ + TILE64 /*dY'*/;
 
-__global__ void __launch_bounds__(128, 1)
+// 256 threads = two warpgroups.  Row r = tid & 127 of every 128-row tile is shared by the two threads (r, wg = 0/1):
+// in the operand-building phase warpgroup wg handles the 32-column blocks jb with (jb & 1) == wg, in the scaling
+// and epilogue phases it handles channel half wg (32 of the 64 channels).  Two warps per scheduler hide the
+// TMEM-load / MUFU / shared-memory latencies that a single warpgroup leaves exposed.
+__device__ __forceinline__ float block_sum256(float v, float* red) {   // red: >= 8 floats; two __syncthreads
+  v = warp_sum128(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  return red[0] + red[1] + red[2] + red[3] + red[4] + red[5] + red[6] + red[7];
+}
+
+__global__ void __launch_bounds__(256, 1)
 ssd_chunk_scan_bwd_kernel(const __grid_constant__ CUtensorMap tm_xbc, const __grid_constant__ CUtensorMap tm_dy,
                           const __grid_constant__ CUtensorMap tm_sin, const __grid_constant__ CUtensorMap tm_dsout,
                           const __grid_constant__ CUtensorMap tm_dx, const ScanBwdParams p) {
@@ -395,12 +415,14 @@ ssd_chunk_scan_bwd_kernel(const __grid_constant__ CUtensorMap tm_xbc, const __gr
   uint8_t* sDYs = sDCB + TILE128;      // exp(l_i) * dY
   float* s_l = reinterpret_cast<float*>(sDYs + TILE64);
   float* s_dt = s_l + CT;
-  float* s_red = s_dt + CT;            // 8 floats
-  float* s_col = s_red + 8;            // [4 warps][128] column sums of W
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_col + 4 * CT);
+  float* s_red = s_dt + CT;            // 16 floats
+  float* s_col = s_red + 16;           // [4 row-warps][128] column sums of W
+  float* s_pair = s_col + 4 * CT;      // [5][128] per-row partials handed from warpgroup 1 to warpgroup 0
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_pair + 5 * CT);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
 
   const int c = blockIdx.x, b = blockIdx.z, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int row = tid & 127, wg = tid >> 7, rw = warp & 3;      // tile row, warpgroup, row-warp (TMEM lane quarter)
   const int psplit = p.Hv / p.H;
   const int hv_per_group = (p.H / p.G) * psplit;
   const int splits = hv_per_group / p.hpc;
@@ -445,8 +467,8 @@ ssd_chunk_scan_bwd_kernel(const __grid_constant__ CUtensorMap tm_xbc, const __gr
       tma_load_2d(sDS, &tm_dsout, 0, srow, &bars[0]);
     }
     const long long lo = ((long long)b * p.H + h) * p.L + (long long)c * CT;
-    s_l[tid] = p.l[lo + tid];
-    s_dt[tid] = p.dt[lo + tid];
+    if (wg == 0) s_l[row] = p.l[lo + row];
+    else s_dt[row] = p.dt[lo + row];
     __syncthreads();
     // ---------------------------------------------------------------- phase 1: CB, dM
     if (tid == 0) {
@@ -457,10 +479,9 @@ ssd_chunk_scan_bwd_kernel(const __grid_constant__ CUtensorMap tm_xbc, const __gr
         #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
           umma_bf16(tmem, desc_kmajor(aC, kk, TILE128 / 2), desc_kmajor(aB, kk, TILE128 / 2), id_cb, kk != 0);
-        const uint32_t id_dm = make_idesc_bf16(128, 128, 0, 0);   // dM[i][j] = sum_p dY[i][p] x[j][p]
         #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_bf16(tmem + 128, desc_kmajor(aDY, kk, 0), desc_kmajor(aX, kk, 0), id_dm, kk != 0);
+        for (int kk = 0; kk < 4; ++kk)                            // dM[i][j] = sum_p dY[i][p] x[j][p]
+          umma_bf16(tmem + 128, desc_kmajor(aDY, kk, 0), desc_kmajor(aX, kk, 0), id_cb, kk != 0);
         umma_commit(&bars[1]);
       }
     }
@@ -468,16 +489,28 @@ ssd_chunk_scan_bwd_kernel(const __grid_constant__ CUtensorMap tm_xbc, const __gr
     ok = __syncthreads_and(mbar_wait(&bars[1], par, p.status));   // uniform outcome for the whole CTA
     tc_fence_after_sync();
     if (!ok) break;
-    // ---------------------------------------------------------------- thread-built operands (row = tid)
-    const float li = s_l[tid], dti = s_dt[tid], lT = s_l[CT - 1];
+    // ---------------------------------------------------------------- thread-built operands
+    const float li = s_l[row], dti = s_dt[row], lT = s_l[CT - 1];
     const float a_left = __expf(li), a_right = __expf(lT - li);
-    float r1 = 0.f;                      // sum_{j<i} W[i][j]
+    float r1 = 0.f;                      // this thread's share of sum_{j<i} W[i][j]
     #pragma unroll 1
-    for (int jb = 0; jb < 4; ++jb) {
+    for (int jq = 0; jq < 2; ++jq) {
+      const int jb = wg + 2 * jq;        // 32-column block handled by this warpgroup
+      if (jb > rw) {                     // fully masked block (j > i for all rows of this warp)
+        #pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          const int jc = jb * 32 + ch * 8;
+          const uint32_t off = (jc >> 6) * (TILE128 / 2) + sw128_offset(row, (jc & 63) >> 3);
+          *reinterpret_cast<uint4*>(sM0 + off) = make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(sDCB + off) = make_uint4(0, 0, 0, 0);
+        }
+        s_col[rw * CT + jb * 32 + lane] = 0.f;
+        continue;
+      }
       uint32_t cb[32], dm[32];
       float wv[32];
-      tmem_ld32(tmem_addr(tmem, warp * 32, jb * 32), cb);
-      tmem_ld32(tmem_addr(tmem, warp * 32, 128 + jb * 32), dm);
+      tmem_ld32(tmem_addr(tmem, rw * 32, jb * 32), cb);
+      tmem_ld32(tmem_addr(tmem, rw * 32, 128 + jb * 32), dm);
       tmem_ld_wait();
       #pragma unroll
       for (int ch = 0; ch < 4; ++ch) {
@@ -485,20 +518,20 @@ ssd_chunk_scan_bwd_kernel(const __grid_constant__ CUtensorMap tm_xbc, const __gr
         #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const int j = jb * 32 + ch * 8 + e;
-          const float lam = (j <= tid) ? __expf(li - s_l[j]) : 0.f;
+          const float lam = (j <= row) ? __expf(li - s_l[j]) : 0.f;
           m0[e] = __uint_as_float(cb[ch * 8 + e]) * lam;
           dc[e] = __uint_as_float(dm[ch * 8 + e]) * lam * s_dt[j];
           // W[i][j] = dM[i][j] * (CB Lambda dt_j)[i][j], strictly below the diagonal
-          wv[ch * 8 + e] = (j < tid) ? __uint_as_float(dm[ch * 8 + e]) * m0[e] * s_dt[j] : 0.f;
+          wv[ch * 8 + e] = (j < row) ? __uint_as_float(dm[ch * 8 + e]) * m0[e] * s_dt[j] : 0.f;
         }
         const int jc = jb * 32 + ch * 8;
-        const uint32_t off = (jc >> 6) * (TILE128 / 2) + sw128_offset(tid, (jc & 63) >> 3);
+        const uint32_t off = (jc >> 6) * (TILE128 / 2) + sw128_offset(row, (jc & 63) >> 3);
         *reinterpret_cast<uint4*>(sM0 + off) = pack8(m0);
         *reinterpret_cast<uint4*>(sDCB + off) = pack8(dc);
       }
-      // column sums of this 32x32 block over the warp's rows: recursive halving, lane c ends with column c
       #pragma unroll
       for (int e = 0; e < 32; ++e) r1 += wv[e];
+      // column sums of this 32x32 block over the warp's rows: recursive halving, lane c ends with column c
       #pragma unroll
       for (int sft = 16; sft >= 1; sft >>= 1) {
         const bool up = (lane & sft) != 0;
@@ -509,17 +542,19 @@ ssd_chunk_scan_bwd_kernel(const __grid_constant__ CUtensorMap tm_xbc, const __gr
           wv[k] = keep + __shfl_xor_sync(0xffffffffu, send, sft);
         }
       }
-      s_col[warp * CT + jb * 32 + lane] = wv[0];
+      s_col[rw * CT + jb * 32 + lane] = wv[0];
     }
-    uint4 xrow[8];   // x[row][0..63] kept for the epilogue
+    // scaled copies of this thread's channel half (4 chunks of 8): x in place, dY into its own tile
+    uint4 xrow[4];
+    float dot_ss = 0.f;                  // share of <dS_out, S_in> (row n = `row`, channel half wg)
     {
       const float sx = a_right * dti;
       #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
-        const uint32_t off = sw128_offset(tid, ch);
-        xrow[ch] = *reinterpret_cast<const uint4*>(sX + off);
-        float f[8];
-        unpack8(xrow[ch], f);
+      for (int q = 0; q < 4; ++q) {
+        const uint32_t off = sw128_offset(row, wg * 4 + q);
+        xrow[q] = *reinterpret_cast<const uint4*>(sX + off);
+        float f[8], f2[8];
+        unpack8(xrow[q], f);
         #pragma unroll
         for (int e = 0; e < 8; ++e) f[e] *= sx;
         *reinterpret_cast<uint4*>(sX + off) = pack8(f);
@@ -527,19 +562,13 @@ ssd_chunk_scan_bwd_kernel(const __grid_constant__ CUtensorMap tm_xbc, const __gr
         #pragma unroll
         for (int e = 0; e < 8; ++e) f[e] *= a_left;
         *reinterpret_cast<uint4*>(sDYs + off) = pack8(f);
+        unpack8(*reinterpret_cast<const uint4*>(sSin + off), f);
+        unpack8(*reinterpret_cast<const uint4*>(sDS + off), f2);
+        #pragma unroll
+        for (int e = 0; e < 8; ++e) dot_ss += f[e] * f2[e];
       }
     }
-    // <dS_out, S_in> over row n = tid
-    float dot_ss = 0.f;
-    #pragma unroll
-    for (int ch = 0; ch < 8; ++ch) {
-      float f1[8], f2[8];
-      const uint32_t off = sw128_offset(tid, ch);
-      unpack8(*reinterpret_cast<const uint4*>(sSin + off), f1);
-      unpack8(*reinterpret_cast<const uint4*>(sDS + off), f2);
-      #pragma unroll
-      for (int e = 0; e < 8; ++e) dot_ss += f1[e] * f2[e];
-    }
+    if (wg == 1) s_pair[row] = r1;
     fence_proxy_async_smem();
     tc_fence_before_sync();
     __syncthreads();
@@ -580,21 +609,20 @@ ssd_chunk_scan_bwd_kernel(const __grid_constant__ CUtensorMap tm_xbc, const __gr
     ok = __syncthreads_and(mbar_wait(&bars[2], par, p.status));
     tc_fence_after_sync();
     if (!ok) break;
-    // ---------------------------------------------------------------- epilogue (row j = tid)
+    // ---------------------------------------------------------------- epilogue (row j = `row`, channel half wg)
     const float Dh = p.D[h];
     float ddt_direct = 0.f, r2 = 0.f, q = 0.f, dD = 0.f;
-    #pragma unroll
-    for (int half = 0; half < 2; ++half) {
+    {
       uint32_t ud[32], us[32], yo[32];
-      tmem_ld32(tmem_addr(tmem, warp * 32, half * 32), ud);
-      tmem_ld32(tmem_addr(tmem, warp * 32, 64 + half * 32), us);
-      tmem_ld32(tmem_addr(tmem, warp * 32, 128 + half * 32), yo);
+      tmem_ld32(tmem_addr(tmem, rw * 32, wg * 32), ud);
+      tmem_ld32(tmem_addr(tmem, rw * 32, 64 + wg * 32), us);
+      tmem_ld32(tmem_addr(tmem, rw * 32, 128 + wg * 32), yo);
       tmem_ld_wait();
       #pragma unroll
       for (int ch = 0; ch < 4; ++ch) {
         float xv[8], gy[8], o[8];
-        unpack8(xrow[half * 4 + ch], xv);
-        unpack8(*reinterpret_cast<const uint4*>(sDY + sw128_offset(tid, half * 4 + ch)), gy);
+        unpack8(xrow[ch], xv);
+        unpack8(*reinterpret_cast<const uint4*>(sDY + sw128_offset(row, wg * 4 + ch)), gy);
         #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const float usr = __uint_as_float(us[ch * 8 + e]);
@@ -605,16 +633,28 @@ ssd_chunk_scan_bwd_kernel(const __grid_constant__ CUtensorMap tm_xbc, const __gr
           dD += gy[e] * xv[e];
           o[e] = dti * dU + Dh * gy[e];
         }
-        *reinterpret_cast<uint4*>(sX + sw128_offset(tid, half * 4 + ch)) = pack8(o);   // dx staging (x tile is dead)
+        *reinterpret_cast<uint4*>(sX + sw128_offset(row, wg * 4 + ch)) = pack8(o);   // dx staging (x tile is dead)
       }
     }
-    const float c1 = s_col[tid] + s_col[CT + tid] + s_col[2 * CT + tid] + s_col[3 * CT + tid];
-    const float dl = r1 + a_left * r2 - c1 - a_right * dti * q;
     fence_proxy_async_smem();
-    // E = exp(l_T) <dS_out, S_in> + sum_j a_right dt_j q_j
-    const float E = block_sum128(__expf(lT) * dot_ss + a_right * dti * q, s_red);
+    if (wg == 1) {                        // hand the per-row partials of the upper channel half to warpgroup 0
+      s_pair[CT + row] = ddt_direct;
+      s_pair[2 * CT + row] = r2;
+      s_pair[3 * CT + row] = q;
+    }
+    // E = exp(l_T) <dS_out, S_in> + sum_j a_right dt_j q_j   (both are plain sums over all 256 threads)
+    const float E = block_sum256(__expf(lT) * dot_ss + a_right * dti * q, s_red);
     if (tid == 0) { tma_store_2d(&tm_dx, sX, hv * PS, row0); tma_store_commit(); }
-    // suffix sum of dl over the 128 rows
+    float dl = 0.f;
+    if (wg == 0) {
+      r1 += s_pair[row];
+      ddt_direct += s_pair[CT + row];
+      r2 += s_pair[2 * CT + row];
+      q += s_pair[3 * CT + row];
+      const float c1 = s_col[row] + s_col[CT + row] + s_col[2 * CT + row] + s_col[3 * CT + row];
+      dl = r1 + a_left * r2 - c1 - a_right * dti * q;
+    }
+    // suffix sum of dl over the 128 rows (warpgroup 0; warpgroup 1 carries zeros through the same barriers)
     float suf = dl;
     #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -622,19 +662,23 @@ ssd_chunk_scan_bwd_kernel(const __grid_constant__ CUtensorMap tm_xbc, const __gr
       if (lane + o < 32) suf += n;
     }
     __syncthreads();
-    if (lane == 0) s_red[4 + warp] = suf;      // warp totals
+    if (lane == 0 && wg == 0) s_red[8 + rw] = suf;      // warp totals
     __syncthreads();
-    float tail = 0.f;
-    for (int w = warp + 1; w < 4; ++w) tail += s_red[4 + w];
-    const float da = suf + tail + E;
-    const float ddt = ddt_direct + p.A[h] * da;
-    const float sig = sigmoid_f(__bfloat162float(p.dt_raw[(long long)(row0 + tid) * p.dt_raw_stride + h]) + p.dt_bias[h]);
-    const float ddr = ddt * sig;
-    if (p.ddt32 != nullptr) p.ddt32[((long long)b * p.Hv + hv) * p.L + (long long)c * CT + tid] = ddr;
-    else p.ddt_raw[(long long)(row0 + tid) * p.ddt_stride + h] = __float2bfloat16(ddr);
-    const float sA = block_sum128(dti * da, s_red);
-    const float sD = block_sum128(dD, s_red);
-    const float sb = block_sum128(ddr, s_red);
+    float ddr = 0.f, dta = 0.f;
+    if (wg == 0) {
+      float tail = 0.f;
+      for (int w = rw + 1; w < 4; ++w) tail += s_red[8 + w];
+      const float da = suf + tail + E;
+      const float ddt = ddt_direct + p.A[h] * da;
+      const float sig = sigmoid_f(__bfloat162float(p.dt_raw[(long long)(row0 + row) * p.dt_raw_stride + h]) + p.dt_bias[h]);
+      ddr = ddt * sig;
+      dta = dti * da;
+      if (p.ddt32 != nullptr) p.ddt32[((long long)b * p.Hv + hv) * p.L + (long long)c * CT + row] = ddr;
+      else p.ddt_raw[(long long)(row0 + row) * p.ddt_stride + h] = __float2bfloat16(ddr);
+    }
+    const float sA = block_sum256(dta, s_red);
+    const float sD = block_sum256(dD, s_red);
+    const float sb = block_sum256(ddr, s_red);
     if (tid == 0) {
       float* hp = p.hpart + (((long long)b * p.nc + c) * p.Hv + hv) * 3;
       hp[0] = sA; hp[1] = sD; hp[2] = sb;
@@ -643,25 +687,21 @@ ssd_chunk_scan_bwd_kernel(const __grid_constant__ CUtensorMap tm_xbc, const __gr
     tc_fence_before_sync();
     __syncthreads();
   }
-  // ---------------------------------------------------------------- flush dB, dC (fp32 red.add)
+  // ---------------------------------------------------------------- flush dB (warpgroup 0), dC (warpgroup 1)
   if (ok) {
     tc_fence_after_sync();
     const int GN = p.G * NS;
-    float* rowp = p.dBC + (long long)(row0 + tid) * (2 * GN);
+    float* dst = p.dBC + (long long)(row0 + row) * (2 * GN) + wg * GN + g * NS;
     #pragma unroll 1
-    for (int which = 0; which < 2; ++which) {
-      float* dst = rowp + which * GN + g * NS;
-      #pragma unroll 1
-      for (int nb = 0; nb < 4; ++nb) {
-        uint32_t v[32];
-        tmem_ld32(tmem_addr(tmem, warp * 32, 256 + which * 128 + nb * 32), v);
-        tmem_ld_wait();
-        #pragma unroll
-        for (int k4 = 0; k4 < 8; ++k4)
-          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + nb * 32 + k4 * 4),
-                       "f"(__uint_as_float(v[k4 * 4])), "f"(__uint_as_float(v[k4 * 4 + 1])),
-                       "f"(__uint_as_float(v[k4 * 4 + 2])), "f"(__uint_as_float(v[k4 * 4 + 3])) : "memory");
-      }
+    for (int nb = 0; nb < 4; ++nb) {
+      uint32_t v[32];
+      tmem_ld32(tmem_addr(tmem, rw * 32, 256 + wg * 128 + nb * 32), v);
+      tmem_ld_wait();
+      #pragma unroll
+      for (int k4 = 0; k4 < 8; ++k4)
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + nb * 32 + k4 * 4),
+                     "f"(__uint_as_float(v[k4 * 4])), "f"(__uint_as_float(v[k4 * 4 + 1])),
+                     "f"(__uint_as_float(v[k4 * 4 + 2])), "f"(__uint_as_float(v[k4 * 4 + 3])) : "memory");
     }
   }
   if (tid == 0) tma_store_wait_all();
@@ -762,7 +802,7 @@ extern "C" int ssm_ssd_chunk_scan_bwd(const void* xbc, long long xbc_stride, int
   const int hv_per_group = Hv / G;
   if (hpc <= 0 || hv_per_group % hpc) return -SSM_ERR_BAD_ARG;
   static bool cfg = false;
-  const int smem = BWD_SMEM + (6 * CT + 8) * 4 + 64 + 1024;
+  const int smem = BWD_SMEM + (11 * CT + 16) * 4 + 64 + 1024;
   if (!cfg) { int e = smem_opt_in((const void*)ssd_chunk_scan_bwd_kernel, smem); if (e) return e; cfg = true; }
   const int nc = L / CT;
   CUtensorMap tx, tdy, ts, tds, tdx;
@@ -786,6 +826,6 @@ extern "C" int ssm_ssd_chunk_scan_bwd(const void* xbc, long long xbc_stride, int
   p.dBC = reinterpret_cast<float*>(dBC); p.hpart = reinterpret_cast<float*>(hpart);
   p.L = L; p.H = H; p.Hv = Hv; p.G = G; p.nc = nc; p.d_in = d_in; p.hpc = hpc; p.status = status;
   dim3 grid(nc, G * (hv_per_group / hpc), B);
-  ssd_chunk_scan_bwd_kernel<<<grid, 128, smem, st>>>(tx, tdy, ts, tds, tdx, p);
+  ssd_chunk_scan_bwd_kernel<<<grid, 256, smem, st>>>(tx, tdy, ts, tds, tdx, p);
   return (int)cudaGetLastError();
 }

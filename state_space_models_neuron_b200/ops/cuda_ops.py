@@ -372,6 +372,56 @@ def gelu(x):
 
 
 # ======================================================================================
+# embedding
+# ======================================================================================
+def embed_grad_target(w):
+    """(fp32 [V, D] buffer to accumulate into, direct).  With an optimizer-owned `main_grad` the embedding backward
+    adds into it in place (after the tied LM-head wgrad, which ran earlier in the backward pass)."""
+    mg = getattr(w, "main_grad", None)
+    if mg is not None and mg.dtype == torch.float32 and mg.is_contiguous():
+        if getattr(w, "grad_stale", False):
+            mg.zero_()
+            w.grad_stale = False
+        return mg, True
+    return torch.zeros(w.shape, dtype=torch.float32, device=w.device), False
+
+
+class _Embedding(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, w, vocab_start):
+        ids_c = ids.contiguous()
+        out = torch.empty(*ids.shape, w.shape[1], dtype=w.dtype, device=w.device)
+        _run("ssm_embed_lookup", _P(ids_c), _P(w), _ll(vocab_start), _ll(w.shape[0]), _P(out), _ll(ids_c.numel()),
+             w.shape[1], _st())
+        ctx.save_for_backward(ids_c)
+        ctx.w, ctx.vocab_start = w, vocab_start
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        (ids,), w = ctx.saved_tensors, ctx.w
+        D = w.shape[1]
+        g2 = g.reshape(-1, D)
+        if g2.stride(1) != 1 or g2.stride(0) % 4:
+            g2 = g2.contiguous()
+        tgt, direct = embed_grad_target(w)
+        n = ids.numel()
+        _run("ssm_embed_bwd", _P(ids), _P(g2), _ll(g2.stride(0)), _P(tgt), _ll(ctx.vocab_start), _ll(w.shape[0]), 1, n, n,
+             D, 1, None, 0, 0, None, _P(status_tensor(w.device)), _st())
+        return None, (None if direct else tgt.to(w.dtype)), None
+
+
+def embedding(ids, w, vocab_start: int = 0):
+    """Rows `w[ids - vocab_start]`, zeros for ids outside the local shard; the gradient is scatter-added in fp32."""
+    if w.dtype != torch.bfloat16 or ids.dtype != torch.int64 or w.shape[1] % 8 or not w.is_contiguous():
+        local = ids - vocab_start
+        inside = (local >= 0) & (local < w.shape[0])
+        return torch.nn.functional.embedding(torch.where(inside, local, torch.zeros_like(local)), w) \
+            * inside[..., None].to(w.dtype)
+    return _Embedding.apply(ids, w, int(vocab_start))
+
+
+# ======================================================================================
 # cross entropy
 # ======================================================================================
 def ce_partials(logits, labels, vocab_start):

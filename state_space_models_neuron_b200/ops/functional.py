@@ -161,6 +161,16 @@ def gelu(x):
     return F.gelu(x)
 
 
+# ---- embedding ----------------------------------------------------------------------------
+def embedding(ids, weight, vocab_start: int = 0):
+    """Vocabulary-shard lookup: rows `weight[ids - vocab_start]`, zeros for ids outside the shard."""
+    if _native(weight):
+        return _cuda().embedding(ids, weight, vocab_start)
+    local = ids - vocab_start
+    inside = (local >= 0) & (local < weight.shape[0])
+    return F.embedding(torch.where(inside, local, torch.zeros_like(local)), weight) * inside[..., None].to(weight.dtype)
+
+
 # ---- cross entropy ------------------------------------------------------------------------
 def ce_partials(logits, labels, vocab_start: int):
     if _native(logits):

@@ -51,3 +51,25 @@ def parallel_cross_entropy(logits: torch.Tensor, labels: torch.Tensor, ignore_in
     tp, r = ps.get_tensor_model_parallel_size(), ps.get_tensor_model_parallel_rank()
     vocab_start = r * logits.shape[-1] if tp > 1 else 0
     return _ParallelCrossEntropy.apply(logits, labels, vocab_start, ignore_index)
+
+
+@torch.no_grad()
+def parallel_argmax(logits: torch.Tensor) -> torch.Tensor:
+    """Greedy token over vocabulary-sharded logits `[..., V/TP]`: global index of the maximum (lowest index on
+    ties), identical on every TP rank.  Two tiny all-reduces (max of the values, then max of the negated
+    candidate index), through the fused small all-reduce when it is available."""
+    tp, r = ps.get_tensor_model_parallel_size(), ps.get_tensor_model_parallel_rank()
+    val, idx = logits.float().max(dim=-1)
+    if tp == 1:
+        return idx
+    from . import fused
+    grp = ps.get_tensor_model_parallel_group()
+    shape = val.shape
+    gmax = val.reshape(-1).contiguous().clone()
+    if not fused.small_allreduce(gmax, "max"):
+        dist.all_reduce(gmax, op=dist.ReduceOp.MAX, group=grp)
+    cand = torch.where(val.reshape(-1) == gmax, -(idx.reshape(-1) + r * logits.shape[-1]).float(),
+                       torch.full_like(gmax, -float(1 << 24))).contiguous()
+    if not fused.small_allreduce(cand, "max"):
+        dist.all_reduce(cand, op=dist.ReduceOp.MAX, group=grp)
+    return (-cand).long().reshape(shape)

@@ -39,6 +39,11 @@ def all_gather_linear(x, weight, bias=None):
     return _IMPL[0].all_gather_linear(x, weight, bias)
 
 
+def all_gather_multi_linear(x, weights):
+    """Outputs of several column-parallel weights behind one fused sequence all-gather, or None."""
+    return _IMPL[0].all_gather_multi_linear(x, list(weights))
+
+
 def linear_reduce_scatter(x, weight):
     return _IMPL[0].linear_reduce_scatter(x, weight)
 
@@ -49,3 +54,25 @@ def small_allreduce(data, op: str = "sum") -> bool:
         return False
     from . import fused_ops
     return fused_ops.small_allreduce(data, op)
+
+
+def vocab_embed_scatter(ids, weight, vocab_start: int):
+    """Fused vocabulary-parallel embedding with sequence-parallel output; None means "use the library path"."""
+    if not (_ENABLED[0] and weight.is_cuda):
+        return None
+    if _IMPL[0] is None:
+        from . import fused_ops
+        fused_ops.install()
+    from . import fused_ops
+    return fused_ops.vocab_embed_scatter(ids, weight, vocab_start)
+
+
+def allreduce_bf16(x):
+    """One-kernel all-reduce of a bf16 activation outside autograd (decode); None means "use the library"."""
+    if not (_ENABLED[0] and x.is_cuda):
+        return None
+    if _IMPL[0] is None:
+        from . import fused_ops
+        fused_ops.install()
+    from . import fused_ops
+    return fused_ops.allreduce_bf16(x)

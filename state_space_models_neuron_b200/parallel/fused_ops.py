@@ -118,6 +118,93 @@ def small_allreduce(data: torch.Tensor, op: str = "sum") -> bool:
     return True
 
 
+def allreduce_bf16(x: torch.Tensor):
+    """Sum of a bf16 activation over the TP group in one kernel (stores into every rank's slot, flag, bounded wait,
+    fp32 sum): the decode-time replacement of the all-reduce after the row-parallel out_proj
+    (mamba2/mamba2_mixer.py:233 with sequence parallelism off).  Returns None when it does not apply."""
+    T = ps.get_tensor_model_parallel_size()
+    if (T < 2 or T > symm.MAX_RANKS or not x.is_cuda or x.dtype != torch.bfloat16 or x.numel() % 8
+            or x.numel() > (1 << 21) or torch.is_grad_enabled() and x.requires_grad):
+        return None
+    n = x.numel()
+    ws = _ws_for(T * max(1, -(-n // x.shape[-1])), x.shape[-1], x.device)
+    if ws is None or n * T * 2 > ws.gather_bytes:
+        return None
+    xc = x.contiguous()
+    out = torch.empty_like(xc)
+    CALLS["allreduce_bf16"] = CALLS.get("allreduce_bf16", 0) + 1
+    seq = ws.next_seq()
+    par = seq & 1
+    stride = ws.gather_bytes // 2 // T // 8 * 8
+    _run("ssm_allreduce_bf16", _P(xc), _P(out), _ll(n), ws.peer_ptrs(ws.gather_offset(par)), _ll(stride), T, ws.me,
+         ws.flag_ptr_array, ws.flag_base(symm.KIND_AG, par), seq, _P(ws.seq_base), _c.c_void_p(ws.counter_ptr(34)),
+         _P(status_tensor(ws.device)), _st())
+    return out
+
+
+class _VocabEmbedScatter(torch.autograd.Function):
+    """Vocabulary-parallel embedding whose output is already scattered along the sequence.  The reference sums
+    the T masked partial lookups with an all-reduce and slices (mamba2/modeling_mamba2.py:276,300-301); here the
+    rank that holds a token's row stores it into the sequence owner's buffer over NVLink (no reduction needed: one
+    rank holds each row).  Backward: the output gradients are pushed to every rank's gather buffer and each rank
+    scatter-adds the rows of its own vocabulary range into the fp32 gradient."""
+
+    @staticmethod
+    def forward(ctx, ids, w, vocab_start, ws):
+        B, L = ids.shape
+        T, D = ws.nranks, w.shape[1]
+        Ls = L // T
+        ids_c = ids.contiguous()
+        CALLS["vocab_embed"] = CALLS.get("vocab_embed", 0) + 1
+        seq = ws.next_seq()
+        par = seq & 1
+        off = ws.embed_offset(par)
+        base = ws.flag_base(symm.KIND_EMB, par)
+        _run("ssm_vocab_embed_push", _P(ids_c), _P(w), _ll(vocab_start), _ll(w.shape[0]), ws.peer_ptrs(off), B, L, Ls, D,
+             T, ws.me, ws.flag_ptr_array, base, seq, _P(ws.seq_base), _c.c_void_p(ws.counter_ptr(32)), _st())
+        out = torch.empty(B, Ls, D, dtype=w.dtype, device=w.device)
+        _run("ssm_embed_wait_copy", _P(ws.local_view(off, B * Ls, D)), _P(out), _ll(B * Ls * D), T,
+             _c.c_void_p(ws.base_ptrs[ws.me]), base, seq, _P(ws.seq_base), _P(status_tensor(ws.device)), _st())
+        ctx.save_for_backward(ids_c)
+        ctx.w, ctx.ws, ctx.vocab_start = w, ws, vocab_start
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        (ids,), w, ws = ctx.saved_tensors, ctx.w, ctx.ws
+        B, L = ids.shape
+        T, D = ws.nranks, w.shape[1]
+        Ls = L // T
+        g2 = g.reshape(B * Ls, D)
+        if g2.stride(1) != 1 or g2.stride(0) % 8:
+            g2 = g2.contiguous()
+        seq = ws.next_seq()
+        par = seq & 1
+        off = ws.gather_offset(par)
+        base = ws.flag_base(symm.KIND_AG, par)
+        _run("ssm_push_shard", _P(g2), _ll(g2.stride(0)), ws.peer_ptrs(off), _ll(D), _ll(ws.me * B * Ls), B * Ls, D, T,
+             ws.me, ws.flag_ptr_array, base, seq, _P(ws.seq_base), _c.c_void_p(ws.counter_ptr(33)),
+             min(148, max(1, B * Ls * D // 8 // 256)), _st())
+        tgt, direct = cuda_ops.embed_grad_target(w)
+        _run("ssm_embed_bwd", _P(ids), _P(ws.local_view(off, B * L, D)), _ll(D), _P(tgt), _ll(ctx.vocab_start),
+             _ll(w.shape[0]), B, L, Ls, D, T, _c.c_void_p(ws.base_ptrs[ws.me]), base, seq, _P(ws.seq_base),
+             _P(status_tensor(ws.device)), _st())
+        return None, (None if direct else tgt.to(w.dtype)), None, None
+
+
+def vocab_embed_scatter(ids, w, vocab_start):
+    """Fused vocabulary-parallel embedding + sequence scatter, or None when the shapes do not fit the kernels."""
+    T = ps.get_tensor_model_parallel_size()
+    if (T < 2 or T > symm.MAX_RANKS or ids.dim() != 2 or ids.dtype != torch.int64 or w.dtype != torch.bfloat16
+            or not w.is_cuda or not w.is_contiguous() or w.shape[1] % 8 or ids.shape[1] % T):
+        return None
+    B, L = ids.shape
+    ws = _ws_for(B * L, w.shape[1], w.device)
+    if ws is None or not ws.fits(B * L, w.shape[1]):
+        return None
+    return _VocabEmbedScatter.apply(ids, w, int(vocab_start), ws)
+
+
 def _shape_ok(Ls, K, N, ws):
     return Ls % 128 == 0 and K % 8 == 0 and N % 8 == 0 and ws is not None
 
@@ -153,6 +240,50 @@ class _AllGatherLinear(torch.autograd.Function):
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = dy2.float().sum(0).to(dy.dtype)
         return dx, dw, db, None
+
+
+class _AllGatherMultiLinear(torch.autograd.Function):
+    """Several column-parallel projections of the same sequence-parallel input (q, k, v of the hybrid attention,
+    mamba2hybrid/mamba2hybrid_attn.py:411-413) behind ONE fused all-gather: the first GEMM carries the push of
+    the shard and waits per source, the others read the gathered rows that are then complete.  Backward: one
+    GEMM + reduce-scatter over the concatenated output gradients and weights, one wgrad GEMM per weight."""
+
+    @staticmethod
+    def forward(ctx, x, ws, *weights):
+        Ls, K = x.shape[1], x.shape[2]
+        gathered, y0 = _ag_gemm(x.reshape(Ls, K), weights[0], False, None, ws)
+        xg = gathered.clone()
+        outs = [y0] + [cuda_ops.gemm(xg, w) for w in weights[1:]]
+        ctx.save_for_backward(xg, *weights)
+        ctx.ws = ws
+        return tuple(y.reshape(1, y.shape[0], w.shape[0]) for y, w in zip(outs, weights))
+
+    @staticmethod
+    def backward(ctx, *dys):
+        xg, *weights = ctx.saved_tensors
+        ws = ctx.ws
+        dy2 = [dy.reshape(-1, w.shape[0]) for dy, w in zip(dys, weights)]
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dcat = torch.cat(dy2, dim=1)
+            wcat = torch.cat(list(weights), dim=0)
+            dx = _gemm_rs(dcat, wcat, True, ws)
+            dx = dx.reshape(1, dx.shape[0], dx.shape[1])
+        dws = []
+        for i, (d, w) in enumerate(zip(dy2, weights)):
+            if not ctx.needs_input_grad[2 + i]:
+                dws.append(None)
+                continue
+            d = d if d.stride(1) == 1 and d.stride(0) % 8 == 0 else d.contiguous()
+            mg = getattr(w, "main_grad", None)
+            if mg is not None and mg.dtype == torch.float32:
+                stale = getattr(w, "grad_stale", False)
+                cuda_ops.gemm(d, xg, a_mn=True, b_mn=True, out=mg, accumulate=not stale)
+                w.grad_stale = False
+                dws.append(None)
+            else:
+                dws.append(cuda_ops.gemm(d, xg, a_mn=True, b_mn=True).contiguous())
+        return (dx, None, *dws)
 
 
 class _LinearReduceScatter(torch.autograd.Function):
@@ -198,6 +329,17 @@ class _Impl:
             from .. import ops
             return ops.linear(mp.gather_from_sequence_parallel_region(x, True), w, bias)
         return _AllGatherLinear.apply(x, w, bias, ws)
+
+    @staticmethod
+    def all_gather_multi_linear(x, weights):
+        T = ps.get_tensor_model_parallel_size()
+        Ls, K = x.shape[1], x.shape[2]
+        ws = _ws_for(T * Ls, K, x.device)
+        ntot = sum(w.shape[0] for w in weights)
+        if (not all(_shape_ok(Ls, K, w.shape[0], ws) for w in weights) or not ws.fits(T * Ls, K)
+                or not ws.fits(T * Ls, ntot)):
+            return None
+        return _AllGatherMultiLinear.apply(x, ws, *weights)
 
     @staticmethod
     def linear_reduce_scatter(x, w):

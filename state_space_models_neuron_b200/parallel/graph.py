@@ -15,6 +15,8 @@ from typing import Callable, Dict, Optional
 
 import torch
 
+from .cross_entropy import parallel_argmax
+
 
 class GraphedTrainStep:
     def __init__(self, model, optimizer, example_batch: Dict[str, torch.Tensor], loss_fn: Optional[Callable] = None,
@@ -86,7 +88,7 @@ class GraphedDecodeStep:
         self.graph = torch.cuda.CUDAGraph()
         with torch.no_grad(), torch.cuda.graph(self.graph):
             self.logits = model.step(self.token, cache)
-            self.next_token = self.logits[:, -1].argmax(-1, keepdim=True)
+            self.next_token = parallel_argmax(self.logits[:, -1]).unsqueeze(-1)
         for k, (c, s) in saved.items():
             cache.conv_states[k].copy_(c)
             cache.ssm_states[k].copy_(s)

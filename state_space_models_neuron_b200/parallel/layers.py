@@ -233,9 +233,20 @@ class ParallelEmbedding(nn.Module):
 
     def forward(self, ids: torch.Tensor, scatter_to_sequence_parallel: bool = False) -> torch.Tensor:
         tp = ps.get_tensor_model_parallel_size()
+        from .. import ops
         if tp == 1:
+            if self.weight.is_cuda:
+                return ops.embedding(ids, self.weight, 0)
             return torch.nn.functional.embedding(ids, self.weight)
-        part = _VocabParallelLookup.apply(ids, self.weight, self.vocab_start)
+        if scatter_to_sequence_parallel and self.weight.is_cuda:
+            from . import fused
+            out = fused.vocab_embed_scatter(ids, self.weight, self.vocab_start)
+            if out is not None:
+                return out
+        if self.weight.is_cuda:
+            part = ops.embedding(ids, self.weight, self.vocab_start)
+        else:
+            part = _VocabParallelLookup.apply(ids, self.weight, self.vocab_start)
         if scatter_to_sequence_parallel:
             return mp.reduce_scatter_to_sequence_parallel_region(part)
         return mp.reduce_from_tensor_parallel_region(part)

@@ -125,7 +125,14 @@ def copy_to_tensor_parallel_region(x):
 
 
 def reduce_from_tensor_parallel_region(x):
-    return x if ps.get_tensor_model_parallel_size() == 1 else _ReduceFromTP.apply(x)
+    if ps.get_tensor_model_parallel_size() == 1:
+        return x
+    if x.is_cuda and not (torch.is_grad_enabled() and x.requires_grad):
+        from . import fused
+        y = fused.allreduce_bf16(x)
+        if y is not None:
+            return y
+    return _ReduceFromTP.apply(x)
 
 
 def scatter_to_sequence_parallel_region(x, dim: int = SEQ_DIM):

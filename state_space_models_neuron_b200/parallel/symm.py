@@ -4,11 +4,12 @@ Every rank allocates the same layout through `torch.distributed._symmetric_memor
 addresses of all peers' copies; the fused kernels take those addresses and move data with P2P stores over
 NVLink.  Layout (per rank):
 
-    flags    int32 [3 kinds][2 parities][8 sources]   published sequence numbers (all-gather, reduce-scatter,
-                                                       small all-reduce); monotonically increasing, never reset
+    flags    int32 [4 kinds][2 parities][8 sources]   published sequence numbers (all-gather, reduce-scatter,
+                                                       small all-reduce, embedding); monotonically increasing
     gather   2 x [rows_total, cols] bf16              all-gather destinations, alternating by call parity
     land     2 x [nranks][rows_per_owner, cols] bf16  reduce-scatter landing zones, alternating by call parity
     slots    2 x [nranks][n_max] fp32                 small all-reduce staging
+    embed    2 x [rows_total / nranks, cols] bf16      vocabulary-parallel embedding landing buffer
 
 Two alternating buffers are enough because a rank can be at most one fused call of a kind ahead of its peers:
 each call needs data that every peer only produces after finishing its own previous call of that kind.
@@ -21,7 +22,7 @@ from typing import List, Optional
 import torch
 import torch.distributed as dist
 
-KIND_AG, KIND_RS, KIND_AR = 0, 1, 2
+KIND_AG, KIND_RS, KIND_AR, KIND_EMB = 0, 1, 2, 3
 MAX_RANKS = 8
 SMALL_N_MAX = 16384
 
@@ -46,7 +47,8 @@ class SymmWorkspace:
         self.gather_bytes = elems * 2
         self.flags_bytes = 4096
         self.slots_bytes = 2 * MAX_RANKS * SMALL_N_MAX * 4
-        total = self.flags_bytes + 4 * self.gather_bytes + self.slots_bytes
+        self.embed_bytes = (-(-elems // nranks) * 2 + 255) // 256 * 256
+        total = self.flags_bytes + 4 * self.gather_bytes + self.slots_bytes + 2 * self.embed_bytes
         self.buf = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
         self.handle = symm_mem.rendezvous(self.buf, group)
         self.base_ptrs = [int(p) for p in self.handle.buffer_ptrs]
@@ -72,6 +74,9 @@ class SymmWorkspace:
 
     def slots_offset(self, parity: int) -> int:
         return self.flags_bytes + 4 * self.gather_bytes + parity * MAX_RANKS * SMALL_N_MAX * 4
+
+    def embed_offset(self, parity: int) -> int:
+        return self.flags_bytes + 4 * self.gather_bytes + self.slots_bytes + parity * self.embed_bytes
 
     def peer_ptrs(self, byte_offset: int):
         return _ptr_array([p + byte_offset for p in self.base_ptrs])

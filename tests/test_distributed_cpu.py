@@ -100,3 +100,47 @@ def _ref_entry(rank, world, hybrid, steps, path):
 
 def _run_reference(hybrid, steps, path):
     run_ranks(_ref_entry, 1, hybrid, steps, path)
+
+
+def _tp_decode_worker(rank, world, hybrid):
+    """TP=2 prefill + token-by-token decode gives the vocabulary shards of the single-rank full forward."""
+    from state_space_models_neuron_b200 import parallel as nxd
+    from state_space_models_neuron_b200.models import Mamba2Cache, Mamba2ForCausalLM, Mamba2HybridForCausalLM
+    from state_space_models_neuron_b200.parallel import state as ps
+    from state_space_models_neuron_b200.parallel.layout import shard_state_dict
+    cls = Mamba2HybridForCausalLM if hybrid else Mamba2ForCausalLM
+    mcfg = _cfg(False, hybrid)
+    # full model on every rank (TP=1 state) as the oracle
+    ps.initialize_model_parallel(1)
+    torch.manual_seed(11)
+    full = cls(mcfg).eval()
+    ids = torch.randint(0, 256, (2, 256), generator=torch.Generator().manual_seed(5))
+    with torch.no_grad():
+        ref = full(input_ids=ids).logits
+    sd = {k: v.clone() for k, v in full.state_dict().items()}
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel(world)
+    cfg = nxd.parallel_config(world, {"zero_one_enabled": False}, device="cpu", init_seed=7)
+    model = nxd.initialize_parallel_model(cfg, lambda: cls(mcfg)).eval()
+    model.load_state_dict(shard_state_dict(sd, mcfg, world, rank), strict=False)
+    per = 256 // world
+    mine = ref[..., rank * per:(rank + 1) * per]
+    with torch.no_grad():
+        logits, cache = model.prefill(ids[:, :128])
+        assert torch.allclose(logits[:, -1], mine[:, 127], atol=2e-4, rtol=1e-3)
+        for t in range(128, 152):
+            out = model.step(ids[:, t:t + 1], cache)
+            assert torch.allclose(out[:, 0], mine[:, t], atol=3e-4, rtol=1e-3), (t, (out[:, 0] - mine[:, t]).abs().max())
+        # greedy generation picks the same tokens as the single-rank model (parallel argmax over vocab shards)
+        ps.destroy_model_parallel()
+        ps.initialize_model_parallel(1)
+        want = full.generate_tokens(ids[:, :130], 6)
+        ps.destroy_model_parallel()
+        ps.initialize_model_parallel(world)
+        got = model.generate_tokens(ids[:, :130], 6)
+        assert torch.equal(got, want), (got[:, -6:], want[:, -6:])
+
+
+def test_tensor_parallel_decode_matches_full_forward():
+    # the hybrid model has no decode cache (the reference asserts use_cache is False, mamba2hybrid_attn.py:379)
+    run_ranks(_tp_decode_worker, 2, False)

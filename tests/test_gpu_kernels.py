@@ -321,3 +321,33 @@ def test_flash_attention_fwd_bwd(B, L, Hq, Hkv):
     _close(q.grad, qr.grad, atol=3e-2, rtol=3e-2, frac=0.995)
     _close(k.grad, kr.grad, atol=3e-2, rtol=3e-2, frac=0.995)
     _close(v.grad, vr.grad, atol=3e-2, rtol=3e-2, frac=0.995)
+
+
+@pytest.mark.parametrize("vocab_start,vloc", [(0, 1000), (300, 256)])
+def test_embedding_lookup_and_scatter_add(vocab_start, vloc):
+    """Masked vocabulary-shard lookup and its fp32 scatter-add gradient (duplicates, ids outside the shard),
+    both the returned-gradient path and the in-place `main_grad` path."""
+    from state_space_models_neuron_b200.ops import cuda_ops
+    g = torch.Generator(device="cuda").manual_seed(5)
+    D = 512
+    w = torch.randn(vloc, D, device="cuda", generator=g).bfloat16().requires_grad_(True)
+    ids = torch.randint(0, 1000, (2, 333), device="cuda", generator=g)
+    ids[0, :7] = vocab_start + 3          # duplicates
+    out = cuda_ops.embedding(ids, w, vocab_start)
+    local = ids - vocab_start
+    inside = (local >= 0) & (local < vloc)
+    ref = w.detach().float()[local.clamp(0, vloc - 1)] * inside[..., None]
+    assert torch.equal(out.float(), ref)
+    go = torch.randn(out.shape, device="cuda", generator=g).bfloat16()
+    out.backward(go)
+    gref = torch.zeros(vloc, D, device="cuda")
+    gref.index_add_(0, local.clamp(0, vloc - 1).reshape(-1), (go.float() * inside[..., None]).reshape(-1, D))
+    _close(w.grad, gref, atol=2e-2, rtol=1e-2)
+    # in-place accumulation into an optimizer-owned fp32 buffer, first stale (overwrite) then accumulating
+    w2 = w.detach().clone().requires_grad_(True)
+    w2.main_grad = torch.full((vloc, D), 7.0, device="cuda")
+    w2.grad_stale = True
+    for rep in range(2):
+        cuda_ops.embedding(ids, w2, vocab_start).backward(go)
+    assert w2.grad is None and w2.grad_stale is False
+    _close(w2.main_grad, 2 * gref, atol=1e-3, rtol=1e-4)
