@@ -58,14 +58,18 @@ def is_current() -> bool:
 
 def build(force: bool = False, verbose: bool = False) -> str:
     """Compile all kernels (parallel over files) and link the shared library.  Returns its path."""
-    with _lock:
+    import fcntl
+    os.makedirs(OUT_DIR, exist_ok=True)
+    # one builder at a time, across threads and across processes (several ranks may find a stale library at once)
+    with _lock, open(os.path.join(OUT_DIR, "build.lock"), "w") as lockf:
+        fcntl.flock(lockf, fcntl.LOCK_EX)
         if not force and is_current():
             return LIB_PATH
-        os.makedirs(OUT_DIR, exist_ok=True)
         nvcc = _nvcc()
+        tag = f".{os.getpid()}"
 
         def compile_one(src):
-            obj = os.path.join(OUT_DIR, src[:-3] + ".o")
+            obj = os.path.join(OUT_DIR, src[:-3] + tag + ".o")
             cmd = [nvcc, *NVCC_FLAGS, "-I", CSRC, "-c", os.path.join(CSRC, src), "-o", obj]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
@@ -78,12 +82,14 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
         with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as ex:
             objs = list(ex.map(compile_one, _sources()))
-        tmp = LIB_PATH + ".tmp"
+        tmp = LIB_PATH + tag + ".tmp"
         r = subprocess.run([nvcc, "-shared", "-o", tmp, *objs, "-gencode", "arch=compute_100a,code=sm_100a"],
                            capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
         os.replace(tmp, LIB_PATH)
+        for o in objs:
+            os.remove(o)
         with open(os.path.join(OUT_DIR, "build.hash"), "w") as f:
             f.write(_source_hash())
         return LIB_PATH
