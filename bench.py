@@ -93,6 +93,10 @@ def main():
     ap.add_argument("--no_e2e", action="store_true")
     ap.add_argument("--graph", default="on", choices=["on", "off"],
                     help="replay the whole training step as one CUDA graph (off = eager launches)")
+    ap.add_argument("--shard_of", type=int, default=1,
+                    help="analysis only: run ONE rank's share of a TP=k model on one GPU without communication "
+                         "(heads, groups and vocabulary divided by k) to see the per-rank compute of TP=k; not a "
+                         "benchmark value")
     ap.add_argument("--profile_mode", action="store_true",
                     help="allow fewer than 3 warm-up steps (for profiler captures; not a benchmark value)")
     args = ap.parse_args()
@@ -121,6 +125,10 @@ def main():
     m = dict(SMALL if args.small else MODEL)
     if args.layers:
         m["num_hidden_layers"] = args.layers
+    if args.shard_of > 1:
+        k = args.shard_of
+        m.update(num_heads=m["num_heads"] // k, n_groups=max(1, m["n_groups"] // k), vocab_size=m["vocab_size"] // k,
+                 expand=2.0 / k, name=m["name"] + f" (1/{k} shard, analysis)")
     fused = args.fused_comm == "on" and args.impl == "ours"
     if args.impl == "baseline":
         from baseline import nccl_cublas
@@ -130,7 +138,7 @@ def main():
         sequence_parallel=tp > 1, fused_comm=fused, init_seed=0)
     mc = Mamba2Config(num_heads=m["num_heads"], head_dim=m["head_dim"], vocab_size=m["vocab_size"],
                       hidden_size=m["hidden_size"], state_size=m["state_size"], num_hidden_layers=m["num_hidden_layers"],
-                      n_groups=m["n_groups"], conv_kernel=4, tie_word_embeddings=True, rmsnorm_within_groups=False,
+                      n_groups=m["n_groups"], expand=m.get("expand", 2), conv_kernel=4, tie_word_embeddings=True, rmsnorm_within_groups=False,
                       sequence_parallel_enabled=tp > 1, dtype=torch.bfloat16, initializer_range=0.02, use_cache=False)
     model = nxd.initialize_parallel_model(cfg, lambda: Mamba2ForCausalLM(mc, device="cuda").to(torch.bfloat16))
     model.train()

@@ -63,17 +63,18 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 // =====================================================================================
 // causal depthwise conv1d (4 taps) + SiLU, channels-last
 // =====================================================================================
-constexpr int CONV_TOK = 32;   // tokens per thread
+constexpr int CONV_TOK = 32;   // tokens per thread at full size; small problems use shorter tiles (more CTAs)
 constexpr int CONV_K = 4;
 
 // x [B, L, C] with row stride xs (elements); out row stride os.  init [B, 3, C] (tokens preceding x) or null.
+template <int TOK>
 __global__ void __launch_bounds__(128)
 conv1d_silu_fwd_kernel(const __nv_bfloat16* __restrict__ x, long long xs, const __nv_bfloat16* __restrict__ w,
                        const __nv_bfloat16* __restrict__ bias, const __nv_bfloat16* __restrict__ init,
                        __nv_bfloat16* __restrict__ out, long long os, int L, int C) {
   const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (c0 >= C) return;
-  const int t0 = blockIdx.y * CONV_TOK;
+  const int t0 = blockIdx.y * TOK;
   const int b = blockIdx.z;
   float wt[CONV_K][8], bs[8];
   #pragma unroll
@@ -96,7 +97,7 @@ conv1d_silu_fwd_kernel(const __nv_bfloat16* __restrict__ x, long long xs, const 
     }
   }
   #pragma unroll 4
-  for (int i = 0; i < CONV_TOK; ++i) {
+  for (int i = 0; i < TOK; ++i) {
     const int t = t0 + i;
     if (t >= L) break;
     float cur[8], o[8];
@@ -122,6 +123,7 @@ __device__ __forceinline__ void unpack4(const uint2 u, float (&f)[4]) {
   f[0] = bf16_lo(u.x); f[1] = bf16_hi(u.x); f[2] = bf16_lo(u.y); f[3] = bf16_hi(u.y);
 }
 
+template <int TOK>
 __global__ void __launch_bounds__(128, 4)
 conv1d_silu_bwd_kernel(const __nv_bfloat16* __restrict__ x, long long xs, const __nv_bfloat16* __restrict__ w,
                        const __nv_bfloat16* __restrict__ bias, const __nv_bfloat16* __restrict__ dy16, long long ds16,
@@ -129,7 +131,7 @@ conv1d_silu_bwd_kernel(const __nv_bfloat16* __restrict__ x, long long xs, const 
                        __nv_bfloat16* __restrict__ dx, long long dxs, float* __restrict__ part, int L, int C) {
   const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * CONV_CPT;
   if (c0 >= C) return;
-  const int t0 = blockIdx.y * CONV_TOK;
+  const int t0 = blockIdx.y * TOK;
   const int b = blockIdx.z;
   float wt[CONV_K][CONV_CPT], bs[CONV_CPT];
   #pragma unroll
@@ -156,7 +158,7 @@ conv1d_silu_bwd_kernel(const __nv_bfloat16* __restrict__ x, long long xs, const 
       for (int e = 0; e < CONV_CPT; ++e) xw[k][e] = 0.f;
     }
   }
-  constexpr int NSTEP = CONV_TOK + 3;
+  constexpr int NSTEP = TOK + 3;
   constexpr int NB = (NSTEP + 3) / 4;
   #pragma unroll 1
   for (int ib = 0; ib < NB; ++ib) {
@@ -190,7 +192,7 @@ conv1d_silu_bwd_kernel(const __nv_bfloat16* __restrict__ x, long long xs, const 
           const float pre = bs[e] + wt[0][e] * xw[0][e] + wt[1][e] * xw[1][e] + wt[2][e] * xw[2][e] + wt[3][e] * cur[e];
           const float sg = sigmoid_f(pre);
           dpre = g[e] * sg * (1.f + pre * (1.f - sg));
-          if (i < CONV_TOK) {
+          if (i < TOK) {
             dw[0][e] += xw[0][e] * dpre; dw[1][e] += xw[1][e] * dpre; dw[2][e] += xw[2][e] * dpre;
             dw[3][e] += cur[e] * dpre; db[e] += dpre;
           }
@@ -618,31 +620,68 @@ struct SmallGradArgs {
 
 __device__ __forceinline__ void put(float* dst, float v, bool acc) { *dst = acc ? *dst + v : v; }
 
+// fp32 copies of the per-head mixer parameters in one launch: out[0:H] = -exp(A_log), out[H:2H] = D,
+// out[2H:3H] = dt_bias (the three parameters may be bf16 or fp32)
+__global__ void mixer_param_prep_kernel(const void* A_log, const void* D, const void* dt_bias, int bf16_mask, int H,
+                                        float* __restrict__ out) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= 3 * H) return;
+  const int which = i / H, h = i % H;
+  const void* src = which == 0 ? A_log : which == 1 ? D : dt_bias;
+  const float v = (bf16_mask >> which) & 1 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(src)[h])
+                                           : reinterpret_cast<const float*>(src)[h];
+  out[i] = which == 0 ? -expf(v) : v;
+}
+
+// Column sums with the rows split over 8 thread groups: block = 32 columns x 8 row groups, each thread adds
+// every 8th row of its column (coalesced 128-byte row reads), the 8 partial sums meet in shared memory.
+// A one-thread-per-column loop over all rows is latency-bound on these small matrices.
+constexpr int CS_COLS = 32, CS_GROUPS = 8;
+
+__device__ __forceinline__ float colsum_groups(float s, float (*red)[CS_COLS + 1]) {
+  const int tx = threadIdx.x & (CS_COLS - 1), tg = threadIdx.x / CS_COLS;
+  red[tg][tx] = s;
+  __syncthreads();
+  float r = 0.f;
+  if (tg == 0) {
+    #pragma unroll
+    for (int k = 0; k < CS_GROUPS; ++k) r += red[k][tx];
+  }
+  return r;
+}
+
 __global__ void __launch_bounds__(256) mixer_small_grads_kernel(const SmallGradArgs a) {
+  __shared__ float red[CS_GROUPS][CS_COLS + 1];
+  const int tx = threadIdx.x & (CS_COLS - 1), tg = threadIdx.x / CS_COLS;
   const long long n_conv = (long long)a.C * 5, n_gated = a.d_in, n_h = (long long)a.H * 3;
-  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  long long i = (long long)blockIdx.x * CS_COLS + tx;
+  int seg = 3;
+  float s = 0.f;
   if (i < n_conv) {
-    float s = 0.f;
-    for (int t = 0; t < a.T1; ++t) s += a.conv_part[(long long)t * n_conv + i];
+    seg = 0;
+    for (int t = tg; t < a.T1; t += CS_GROUPS) s += a.conv_part[(long long)t * n_conv + i];
+  } else if (i - n_conv < n_gated) {
+    seg = 1;
+    i -= n_conv;
+    for (int t = tg; t < a.S; t += CS_GROUPS) s += a.gated_part[(long long)t * n_gated + i];
+  } else if (i - n_conv - n_gated < n_h) {
+    seg = 2;
+    i -= n_conv + n_gated;
+    const int h = (int)(i / 3), which = (int)(i % 3);
+    const int psplit = a.Hv / a.H;
+    for (int t = tg; t < a.T2; t += CS_GROUPS)
+      for (int ps = 0; ps < psplit; ++ps) s += a.hpart[((long long)t * a.Hv + h * psplit + ps) * 3 + which];
+  }
+  s = colsum_groups(s, red);
+  if (tg != 0) return;
+  if (seg == 0) {
     const int c = (int)(i / 5), k = (int)(i % 5);
     if (k < 4) put(a.g_conv_w + c * 4 + k, s, a.acc_mask & 1);
     else if (a.g_conv_b) put(a.g_conv_b + c, s, a.acc_mask & 2);
-    return;
-  }
-  i -= n_conv;
-  if (i < n_gated) {
-    float s = 0.f;
-    for (int t = 0; t < a.S; ++t) s += a.gated_part[(long long)t * n_gated + i];
+  } else if (seg == 1) {
     put(a.g_norm_w + i, s, a.acc_mask & 4);
-    return;
-  }
-  i -= n_gated;
-  if (i < n_h) {
+  } else if (seg == 2) {
     const int h = (int)(i / 3), which = (int)(i % 3);
-    const int psplit = a.Hv / a.H;
-    float s = 0.f;
-    for (int t = 0; t < a.T2; ++t)
-      for (int ps = 0; ps < psplit; ++ps) s += a.hpart[((long long)t * a.Hv + h * psplit + ps) * 3 + which];
     if (which == 0) put(a.g_A_log + h, s * a.A[h], a.acc_mask & 8);
     else if (which == 1) put(a.g_D + h, s, a.acc_mask & 16);
     else put(a.g_dt_bias + h, s, a.acc_mask & 32);
@@ -651,11 +690,14 @@ __global__ void __launch_bounds__(256) mixer_small_grads_kernel(const SmallGradA
 
 // dst[c] (+)= sum_s part[s][c]
 __global__ void __launch_bounds__(256) colsum_kernel(const float* __restrict__ part, int S, int n, float* dst, int acc) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= n) return;
+  __shared__ float red[CS_GROUPS][CS_COLS + 1];
+  const int tx = threadIdx.x & (CS_COLS - 1), tg = threadIdx.x / CS_COLS;
+  const int c = blockIdx.x * CS_COLS + tx;
   float s = 0.f;
-  for (int t = 0; t < S; ++t) s += part[(long long)t * n + c];
-  dst[c] = acc ? dst[c] + s : s;
+  if (c < n)
+    for (int t = tg; t < S; t += CS_GROUPS) s += part[(long long)t * n + c];
+  s = colsum_groups(s, red);
+  if (tg == 0 && c < n) dst[c] = acc ? dst[c] + s : s;
 }
 
 }  // namespace ssm
@@ -670,26 +712,45 @@ using namespace ssm;
 #define BF(p) reinterpret_cast<const __nv_bfloat16*>(p)
 #define BFM(p) reinterpret_cast<__nv_bfloat16*>(p)
 
+// Token-tile length: 32 at full size; shorter tiles when that grid would leave most warp slots empty (the
+// per-rank channel counts of tensor parallelism), at the price of re-reading the 3-token halo more often.
+static int conv_tok_for(int B, int L, int C, int ch_per_thread, int min_tok) {
+  const long long warps = (long long)((C / ch_per_thread + 31) / 32) * ((L + 31) / 32) * B;
+  int tok = warps >= 2048 ? 32 : warps >= 1024 ? 16 : 8;
+  return tok < min_tok ? min_tok : tok;
+}
+
 extern "C" int ssm_conv1d_silu_fwd(const void* x, long long xs, const void* w, const void* bias, const void* init,
                                    void* out, long long os, int B, int L, int C, cudaStream_t st) {
   if (C % 8 || xs % 8 || os % 8) return -SSM_ERR_BAD_ARG;
-  dim3 grid((C / 8 + 127) / 128, (L + CONV_TOK - 1) / CONV_TOK, B);
-  conv1d_silu_fwd_kernel<<<grid, 128, 0, st>>>(BF(x), xs, BF(w), BF(bias), BF(init), BFM(out), os, L, C);
+  const int tok = conv_tok_for(B, L, C, 8, 8);
+  dim3 grid((C / 8 + 127) / 128, (L + tok - 1) / tok, B);
+  if (tok == 32) conv1d_silu_fwd_kernel<32><<<grid, 128, 0, st>>>(BF(x), xs, BF(w), BF(bias), BF(init), BFM(out), os, L, C);
+  else if (tok == 16) conv1d_silu_fwd_kernel<16><<<grid, 128, 0, st>>>(BF(x), xs, BF(w), BF(bias), BF(init), BFM(out), os, L, C);
+  else conv1d_silu_fwd_kernel<8><<<grid, 128, 0, st>>>(BF(x), xs, BF(w), BF(bias), BF(init), BFM(out), os, L, C);
   return (int)cudaGetLastError();
 }
 
-// part must hold B * ceil(L / 32) * C * 5 floats.
+// tokens per partial-sum tile of the backward kernel for this problem size
+extern "C" int ssm_conv_bwd_tok_tile(int B, int L, int C) { return conv_tok_for(B, L, C, CONV_CPT, 16); }
+
+// part must hold B * ceil(L / tile) * C * 5 floats, tile = ssm_conv_bwd_tok_tile(B, L, C).
 extern "C" int ssm_conv1d_silu_bwd(const void* x, long long xs, const void* w, const void* bias, const void* dy16,
                                    long long ds16, const void* dy32, long long ds32, int c_split, void* dx,
                                    long long dxs, void* part, int B, int L, int C, cudaStream_t st) {
   if (C % 8 || xs % 8 || dxs % 8 || c_split % 8 || ds16 % 4 || ds32 % 4) return -SSM_ERR_BAD_ARG;
-  dim3 grid((C / CONV_CPT + 127) / 128, (L + CONV_TOK - 1) / CONV_TOK, B);
-  conv1d_silu_bwd_kernel<<<grid, 128, 0, st>>>(BF(x), xs, BF(w), BF(bias), BF(dy16), ds16,
-                                               reinterpret_cast<const float*>(dy32), ds32, c_split, BFM(dx), dxs,
-                                               reinterpret_cast<float*>(part), L, C);
+  const int tok = conv_tok_for(B, L, C, CONV_CPT, 16);
+  dim3 grid((C / CONV_CPT + 127) / 128, (L + tok - 1) / tok, B);
+  if (tok == 32)
+    conv1d_silu_bwd_kernel<32><<<grid, 128, 0, st>>>(BF(x), xs, BF(w), BF(bias), BF(dy16), ds16,
+                                                     reinterpret_cast<const float*>(dy32), ds32, c_split, BFM(dx), dxs,
+                                                     reinterpret_cast<float*>(part), L, C);
+  else
+    conv1d_silu_bwd_kernel<16><<<grid, 128, 0, st>>>(BF(x), xs, BF(w), BF(bias), BF(dy16), ds16,
+                                                     reinterpret_cast<const float*>(dy32), ds32, c_split, BFM(dx), dxs,
+                                                     reinterpret_cast<float*>(part), L, C);
   return (int)cudaGetLastError();
 }
-extern "C" int ssm_conv_tok_tile() { return CONV_TOK; }
 
 // threads per block and vectors per thread for a row (or group) of n elements; -1 if unsupported
 static int norm_threads(int n, int* maxv = nullptr) {
@@ -897,11 +958,17 @@ extern "C" int ssm_mixer_small_grads(const void* conv_part, int T1, int C, const
   a.g_D = reinterpret_cast<float*>(g_D); a.g_dt_bias = reinterpret_cast<float*>(g_dt_bias);
   a.acc_mask = acc_mask;
   const long long n = (long long)C * 5 + d_in + (long long)H * 3;
-  mixer_small_grads_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(a);
+  mixer_small_grads_kernel<<<(unsigned)((n + CS_COLS - 1) / CS_COLS), 256, 0, st>>>(a);
+  return (int)cudaGetLastError();
+}
+extern "C" int ssm_mixer_param_prep(const void* A_log, const void* D, const void* dt_bias, int bf16_mask, int H,
+                                    void* out, cudaStream_t st) {
+  mixer_param_prep_kernel<<<(3 * H + 127) / 128, 128, 0, st>>>(A_log, D, dt_bias, bf16_mask, H,
+                                                              reinterpret_cast<float*>(out));
   return (int)cudaGetLastError();
 }
 extern "C" int ssm_colsum(const void* part, int S, int n, void* dst, int acc, cudaStream_t st) {
-  colsum_kernel<<<(n + 255) / 256, 256, 0, st>>>(reinterpret_cast<const float*>(part), S, n,
+  colsum_kernel<<<(n + CS_COLS - 1) / CS_COLS, 256, 0, st>>>(reinterpret_cast<const float*>(part), S, n,
                                                  reinterpret_cast<float*>(dst), acc);
   return (int)cudaGetLastError();
 }

@@ -10,6 +10,7 @@
 // This is the GEMM behind every Linear layer (the reference leaves those to the XLA compiler:
 // mamba2/mamba2_mixer.py:228,233; mamba2/modeling_mamba2.py:498).
 #include "common.cuh"
+#include <stdlib.h>
 #include <string.h>
 
 namespace ssm {
@@ -28,6 +29,10 @@ struct GemmParams {
   const __nv_bfloat16* bias;  // [N] or null (mode 0 only)
   float* c32;            // modes 1, 2
   long long ldc32;
+  __nv_bfloat16* c16;    // mode 0 (direct-store epilogue)
+  long long ldc16;
+  unsigned long long* trace;   // optional [grid][16] timestamps (ns) for pipeline analysis, else null
+  int direct;            // 1: epilogue warps store their rows straight from registers (no smem staging / TMA store)
   int* status;
   int tiles_m, tiles_n;
   int gemm_ctas;         // CTAs that run GEMM tiles (the grid may hold extra communication CTAs)
@@ -57,6 +62,7 @@ struct GemmComm {
   // reduce-scatter side
   int rs, rows_per_owner, rs_flag_base;
   int* rs_counters;                    // local [nranks]
+  PeerPtrs rs_land; long long rs_land_ld;   // landing slots as plain pointers (direct-store epilogue)
 };
 struct RsMaps { CUtensorMap m[MAX_RANKS]; };
 
@@ -85,6 +91,10 @@ __device__ __forceinline__ bool wait_flag(const int* flag, int seq, int* status)
 __device__ __forceinline__ int rotate_m(int tm, int tiles_m, int tiles_per_block, int first_block) {
   int v = tm + first_block * tiles_per_block;
   return v >= tiles_m ? v - tiles_m : v;
+}
+
+__device__ __forceinline__ void trace_mark(const GemmParams& p, int slot) {
+  if (p.trace != nullptr) p.trace[(size_t)blockIdx.x * 16 + slot] = global_timer_ns();
 }
 
 template <int BN, int STAGES>
@@ -166,6 +176,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) trace_mark(p, 0);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -211,8 +222,10 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
               tma_load_2d(sb + j * 8192, &tmap_b, n0 + 64 * j, k0, &full_bar[stage]);  // box {64 n, 64 k}
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          if (tile == (int)blockIdx.x && kb == 0) trace_mark(p, 8);
         }
       }
+      trace_mark(p, 9);
       if (!ok) {
         // error path: let copies that are still in flight land before the CTA's shared memory goes away
         #pragma unroll
@@ -238,6 +251,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, p.status)) { ok = false; break; }
           tc_fence_after_sync();
+          if (tile == (int)blockIdx.x && kb == 0) trace_mark(p, 1);
           const uint32_t sa = smem_u32(smem + stage * L::STAGE_BYTES);
           const uint32_t sb = sa + L::A_BYTES;
           const uint64_t da = make_smem_desc_sw128(sa, a_lbo, 1024);
@@ -249,6 +263,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (ok) umma_commit(&tfull_bar[acc]);      // accumulator complete
+        trace_mark(p, tile == (int)blockIdx.x ? 2 : 3);
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
     }
@@ -291,6 +306,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         ok = all != 0;
       }
       tc_fence_after_sync();
+      if (epi_tid == 0) trace_mark(p, tile == (int)blockIdx.x ? 4 : 6);
       if (ok) {
         #pragma unroll 1
         for (int j = 0; j < BN / EPI_BLOCK_COLS; ++j) {
@@ -300,27 +316,115 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           tmem_ld32(tmem_addr(tmem_base, q * 32, acc * BN + j * 64), v[0]);
           tmem_ld32(tmem_addr(tmem_base, q * 32, acc * BN + j * 64 + 32), v[1]);
           tmem_ld_wait();
-          if (p.mode == 0 || p.mode == 3) {
-            uint8_t* buf = epi_buf + (stores_issued & 1) * EPI_BUF_BYTES;
-            if (epi_tid == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (p.direct && p.mode == 3) {
+            // reduce-scatter: the row goes straight into the owner's landing slot (peer memory, P2P stores)
+            __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(cm.rs_land.p[owner]) +
+                                  (long long)(m0 - owner * cm.rows_per_owner + row) * cm.rs_land_ld;
             #pragma unroll
             for (int h = 0; h < 2; ++h) {
               #pragma unroll
-              for (int c = 0; c < 4; ++c) {           // 16-byte chunk = 8 bf16
-                float f[8];
-                #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                  float x = __uint_as_float(v[h][c * 8 + e]);
-                  const int col = nb + h * 32 + c * 8 + e;
-                  if (p.bias != nullptr && col < p.N) x += __bfloat162float(p.bias[col]);
-                  if (p.act == 1) x = gelu_f(x);
-                  f[e] = x;
-                }
+              for (int c = 0; c < 4; ++c) {
+                const int col = nb + h * 32 + c * 8;
+                if (col >= p.N) break;
                 uint4 o;
-                o.x = pack_bf16(f[0], f[1]); o.y = pack_bf16(f[2], f[3]);
-                o.z = pack_bf16(f[4], f[5]); o.w = pack_bf16(f[6], f[7]);
-                *reinterpret_cast<uint4*>(buf + sw128_offset(row, h * 4 + c)) = o;
+                o.x = pack_bf16(__uint_as_float(v[h][c * 8 + 0]), __uint_as_float(v[h][c * 8 + 1]));
+                o.y = pack_bf16(__uint_as_float(v[h][c * 8 + 2]), __uint_as_float(v[h][c * 8 + 3]));
+                o.z = pack_bf16(__uint_as_float(v[h][c * 8 + 4]), __uint_as_float(v[h][c * 8 + 5]));
+                o.w = pack_bf16(__uint_as_float(v[h][c * 8 + 6]), __uint_as_float(v[h][c * 8 + 7]));
+                *reinterpret_cast<uint4*>(base + col) = o;        // N % 8 == 0 on this path
+              }
+            }
+          } else if (p.direct) {
+            // every thread owns one output row: 64 consecutive columns = 128 B (bf16) or 2 x 128 B (fp32)
+            const int r = m0 + row;
+            if (r < p.M) {
+              #pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                #pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                  const int col = nb + h * 32 + c * 8;
+                  if (col >= p.N) break;
+                  float f[8];
+                  #pragma unroll
+                  for (int e = 0; e < 8; ++e) {
+                    float x = __uint_as_float(v[h][c * 8 + e]);
+                    if (p.mode == 0) {
+                      if (p.bias != nullptr && col + e < p.N) x += __bfloat162float(p.bias[col + e]);
+                      if (p.act == 1) x = gelu_f(x);
+                    }
+                    f[e] = x;
+                  }
+                  if (p.mode == 0) {
+                    __nv_bfloat16* dst = p.c16 + (long long)r * p.ldc16 + col;
+                    if (col + 8 <= p.N) {
+                      uint4 o;
+                      o.x = pack_bf16(f[0], f[1]); o.y = pack_bf16(f[2], f[3]);
+                      o.z = pack_bf16(f[4], f[5]); o.w = pack_bf16(f[6], f[7]);
+                      *reinterpret_cast<uint4*>(dst) = o;
+                    } else {
+                      for (int e = 0; e < 8 && col + e < p.N; ++e) dst[e] = __float2bfloat16(f[e]);
+                    }
+                  } else {
+                    float* dst = p.c32 + (long long)r * p.ldc32 + col;
+                    #pragma unroll
+                    for (int q4 = 0; q4 < 2; ++q4) {
+                      const int cc = col + q4 * 4;
+                      if (cc + 4 <= p.N) {
+                        if (p.mode == 1)
+                          *reinterpret_cast<float4*>(dst + q4 * 4) = make_float4(f[q4 * 4], f[q4 * 4 + 1], f[q4 * 4 + 2], f[q4 * 4 + 3]);
+                        else
+                          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + q4 * 4), "f"(f[q4 * 4]),
+                                       "f"(f[q4 * 4 + 1]), "f"(f[q4 * 4 + 2]), "f"(f[q4 * 4 + 3]) : "memory");
+                      } else {
+                        for (int e = 0; e < 4 && cc + e < p.N; ++e) {
+                          if (p.mode == 1) dst[q4 * 4 + e] = f[q4 * 4 + e];
+                          else atomicAdd(dst + q4 * 4 + e, f[q4 * 4 + e]);
+                        }
+                      }
+                    }
+                  }
+                }
+              }
+            }
+          } else if (p.mode == 0 || p.mode == 3) {
+            uint8_t* buf = epi_buf + (stores_issued & 1) * EPI_BUF_BYTES;
+            if (epi_tid == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (p.bias == nullptr && p.act == 0) {
+              // plain output (every GEMM of the training step except the MLP up-projection): convert and stage only;
+              // keeping the bias / GELU arithmetic out of this loop matters, the compiler otherwise evaluates it
+              // for every element and selects
+              #pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                #pragma unroll
+                for (int c = 0; c < 4; ++c) {           // 16-byte chunk = 8 bf16
+                  uint4 o;
+                  o.x = pack_bf16(__uint_as_float(v[h][c * 8 + 0]), __uint_as_float(v[h][c * 8 + 1]));
+                  o.y = pack_bf16(__uint_as_float(v[h][c * 8 + 2]), __uint_as_float(v[h][c * 8 + 3]));
+                  o.z = pack_bf16(__uint_as_float(v[h][c * 8 + 4]), __uint_as_float(v[h][c * 8 + 5]));
+                  o.w = pack_bf16(__uint_as_float(v[h][c * 8 + 6]), __uint_as_float(v[h][c * 8 + 7]));
+                  *reinterpret_cast<uint4*>(buf + sw128_offset(row, h * 4 + c)) = o;
+                }
+              }
+            } else {
+              #pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                #pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                  float f[8];
+                  #pragma unroll
+                  for (int e = 0; e < 8; ++e) {
+                    float x = __uint_as_float(v[h][c * 8 + e]);
+                    const int col = nb + h * 32 + c * 8 + e;
+                    if (p.bias != nullptr && col < p.N) x += __bfloat162float(p.bias[col]);
+                    if (p.act == 1) x = gelu_f(x);
+                    f[e] = x;
+                  }
+                  uint4 o;
+                  o.x = pack_bf16(f[0], f[1]); o.y = pack_bf16(f[2], f[3]);
+                  o.z = pack_bf16(f[4], f[5]); o.w = pack_bf16(f[6], f[7]);
+                  *reinterpret_cast<uint4*>(buf + sw128_offset(row, h * 4 + c)) = o;
+                }
               }
             }
             fence_proxy_async_smem();
@@ -362,8 +466,15 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       }
       tc_fence_before_sync();
       __syncwarp();
+      if (epi_tid == 0) trace_mark(p, tile == (int)blockIdx.x ? 5 : 7);
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+    if (cm.rs && p.direct) {
+      // the rows were written with ordinary stores by all epilogue threads: make them visible system-wide before
+      // thread 0 reports this CTA's tiles
+      __threadfence_system();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
     }
     if (epi_tid == 0) {
       tma_store_wait_all();
@@ -388,11 +499,47 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0) trace_mark(p, 10);
   if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
 }
 
 // ------------------------------------------------------------------------------------ host
 static int g_num_sms = 0;
+
+// SSM_GEMM_EPI=direct makes the epilogue warps store their rows straight from registers instead of staging them in
+// shared memory for a TMA store (measured slower: each lane then writes its own 128-byte row segment, which costs
+// most for the fp32 gradient outputs; kept for experiments).
+static unsigned long long* g_trace = nullptr;
+
+static int epilogue_direct() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("SSM_GEMM_EPI");
+    v = (e && strcmp(e, "direct") == 0) ? 1 : 0;
+  }
+  return v;
+}
+
+// Tile width: 128x256 tiles have the better operand reuse, 128x128 tiles fill the SMs better when the 256-wide
+// tiling leaves the last wave mostly empty (the per-rank shapes of tensor parallelism).  Compare the SM-time of
+// both tilings (waves x tile cost; a 128-wide tile costs a little more than half of a 256-wide one).
+// SSM_GEMM_FORCE_BN=128|256 overrides the choice (experiments).
+static bool pick_wide_tiles(int M, int N) {
+  static int forced = -1;
+  if (forced < 0) {
+    const char* e = getenv("SSM_GEMM_FORCE_BN");
+    forced = e ? atoi(e) : 0;
+  }
+  if (N <= 128) return false;
+  if (forced == 128) return false;
+  if (forced == 256) return true;
+  const int sms = g_num_sms > 0 ? g_num_sms : 148;
+  const long long tm = (M + GEMM_BM - 1) / GEMM_BM;
+  const long long t256 = tm * ((N + 255) / 256), t128 = tm * ((N + 127) / 128);
+  const double c256 = (double)((t256 + sms - 1) / sms) * 1.0;
+  const double c128 = (double)((t128 + sms - 1) / sms) * 0.80;   // measured: 128-wide tiles run at ~0.65 of the rate
+  return c256 <= c128;
+}
 
 template <int BN, int STAGES>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, GemmParams p,
@@ -437,7 +584,7 @@ extern "C" int ssm_gemm_bf16(const void* A, const void* B, void* C, int M, int N
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
   }
-  const bool wide = N > 128;
+  const bool wide = pick_wide_tiles(M, N);
   const int BN = wide ? 256 : 128;
   CUtensorMap ta, tb, tc;
   int r;
@@ -460,6 +607,8 @@ extern "C" int ssm_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.c32 = mode == 0 ? nullptr : reinterpret_cast<float*>(C);
   p.ldc32 = ldc; p.status = status; p.tiles_m = 0; p.tiles_n = 0; p.gemm_ctas = 0;
+  p.c16 = mode == 0 ? reinterpret_cast<__nv_bfloat16*>(C) : nullptr;
+  p.ldc16 = ldc; p.direct = epilogue_direct(); p.trace = g_trace;
   return wide ? launch_gemm<256, 4>(ta, tb, tc, p, stream) : launch_gemm<128, 6>(ta, tb, tc, p, stream);
 }
 
@@ -492,7 +641,7 @@ extern "C" int ssm_gemm_bf16_fused(const void* A, const void* B, void* C, int M,
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
   }
-  const bool wide = N > 128;
+  const bool wide = pick_wide_tiles(M, N);
   const int BN = wide ? 256 : 128;
   CUtensorMap ta, tb, tc;
   int r;
@@ -527,6 +676,8 @@ extern "C" int ssm_gemm_bf16_fused(const void* A, const void* B, void* C, int M,
   }
   if (rs) {
     cm.rs = 1; cm.rows_per_owner = rows_per_owner; cm.rs_flag_base = rs_flag_base; cm.rs_counters = rs_counters;
+    cm.rs_land_ld = land_ld;
+    for (int t = 0; t < nranks; ++t) cm.rs_land.p[t] = const_cast<void*>(land_ptrs[t]);
     for (int t = 0; t < nranks; ++t) {
       r = make_tmap_2d_bf16(&maps.m[t], land_ptrs[t], (uint64_t)N, (uint64_t)rows_per_owner, (uint64_t)land_ld * 2, 64, 128);
       if (r) return -400 - r;
@@ -537,6 +688,17 @@ extern "C" int ssm_gemm_bf16_fused(const void* A, const void* B, void* C, int M,
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.c32 = (mode == 1 || mode == 2) ? reinterpret_cast<float*>(C) : nullptr;
   p.ldc32 = ldc; p.status = status; p.tiles_m = 0; p.tiles_n = 0; p.gemm_ctas = 0;
+  p.c16 = mode == 0 ? reinterpret_cast<__nv_bfloat16*>(C) : nullptr;
+  p.ldc16 = ldc; p.direct = epilogue_direct(); p.trace = g_trace;
   return wide ? launch_gemm<256, 4>(ta, tb, tc, p, stream, &cm, &maps)
               : launch_gemm<128, 6>(ta, tb, tc, p, stream, &cm, &maps);
+}
+
+// Pipeline analysis: buf = device array of gridDim * 16 uint64 (or null to switch tracing off).  Slots (ns, global
+// timer): 0 CTA set-up done, 8 first TMA load issued, 1 first stage landed, 2/3 MMAs of the first / a later tile
+// issued, 4/6 first / later accumulator complete (seen by the epilogue), 5/7 epilogue of that tile done, 9 producer
+// finished, 10 CTA done.
+extern "C" int ssm_gemm_set_trace(void* buf) {
+  ssm::g_trace = reinterpret_cast<unsigned long long*>(buf);
+  return 0;
 }

@@ -194,7 +194,7 @@ def _conv_bwd(xBC, w2, bias, dy16, dy32, c_split, dx_out, raw=False):
     """dx_out [B,L,C] view (row stride may exceed C); returns (dw [C,K], db [C]) fp32, or the per-tile partial
     buffer [tiles, C, 5] when `raw`."""
     B, L, C = xBC.shape
-    tile = _lib().ssm_conv_tok_tile()
+    tile = _lib().ssm_conv_bwd_tok_tile(B, L, C)
     ntile = (L + tile - 1) // tile
     part = torch.empty(B * ntile, C, 5, dtype=torch.float32, device=xBC.device)
     _run("ssm_conv1d_silu_bwd", _p(xBC), _ll(xBC.stride(1)), _p(w2), _p(bias), _p(dy16),
@@ -556,6 +556,19 @@ def _final_states(final, xBC, H, psplit, K):
     return tail.transpose(1, 2).contiguous(), ssm
 
 
+def _mixer_params_fp32(A_log, D, dt_bias):
+    """(-exp(A_log), D, dt_bias) as fp32 [H] views of one buffer, one launch."""
+    H = A_log.numel()
+    ok = all(t.dtype in (torch.bfloat16, torch.float32) and t.is_contiguous() and t.numel() == H
+             for t in (A_log, D, dt_bias))
+    if not ok:
+        return -torch.exp(A_log.float()), D.float(), dt_bias.float()
+    out = torch.empty(3, H, dtype=torch.float32, device=A_log.device)
+    mask = sum(1 << i for i, t in enumerate((A_log, D, dt_bias)) if t.dtype == torch.bfloat16)
+    _run("ssm_mixer_param_prep", _P(A_log), _P(D), _P(dt_bias), mask, H, _P(out), _st())
+    return out[0], out[1], out[2]
+
+
 class _MixerCore(torch.autograd.Function):
     @staticmethod
     def forward(ctx, zxBCdt, conv_w, conv_b, dt_bias, A_log, D, norm_w, d_inner, G, N, P, eps, gs, recompute,
@@ -577,8 +590,7 @@ class _MixerCore(torch.autograd.Function):
         z2, xBC, dt_raw2 = flat[:, :d_inner], zxBCdt[..., d_inner:d_inner + C], flat[:, d_inner + C:]
         w2 = conv_w.reshape(C, -1).contiguous()
         conv_out = _conv_fwd(xBC, w2, conv_b, None).view(B * L, C)
-        A = -torch.exp(A_log.float())
-        Df, bf = D.float(), dt_bias.float()
+        A, Df, bf = _mixer_params_fp32(A_log, D, dt_bias)
         y, dt, l, s_in, final = _ssd_forward(conv_out, dt_raw2, ld, A, Df, bf, B, L, d_inner, G, H, Hv,
                                              want_final=want_final)
         out = _gated_fwd(y, z2, norm_w, eps, gs)

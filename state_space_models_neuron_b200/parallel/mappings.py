@@ -33,6 +33,10 @@ def all_gather_seq(x: torch.Tensor) -> torch.Tensor:
     if n == 1:
         return x
     x = x.contiguous()
+    if x.shape[0] == 1 and dist.get_backend(g) != "gloo":       # batch 1: the gathered tensor is one flat buffer
+        out = torch.empty(1, n * x.shape[1], *x.shape[2:], dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(out, x, group=g)
+        return out
     parts = [torch.empty_like(x) for _ in range(n)]
     dist.all_gather(parts, x, group=g)
     return torch.cat(parts, dim=SEQ_DIM)
@@ -44,6 +48,11 @@ def reduce_scatter_seq(x: torch.Tensor) -> torch.Tensor:
         return x
     if x.shape[SEQ_DIM] % n:
         raise ValueError(f"sequence length {x.shape[SEQ_DIM]} is not divisible by TP size {n}")
+    if x.shape[0] == 1 and dist.get_backend(g) != "gloo":
+        x = x.contiguous()
+        out = torch.empty(1, x.shape[1] // n, *x.shape[2:], dtype=x.dtype, device=x.device)
+        dist.reduce_scatter_tensor(out, x, group=g)
+        return out
     parts = [p.contiguous() for p in x.chunk(n, dim=SEQ_DIM)]
     out = torch.empty_like(parts[0])
     if dist.get_backend(g) == "gloo":

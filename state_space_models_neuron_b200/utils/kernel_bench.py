@@ -4,6 +4,11 @@ timing behind the roofline numbers in `profiles/`.
     python -m state_space_models_neuron_b200.utils.kernel_bench gemm --m 2048 --n 18560 --k 4096 --iters 20
     python -m state_space_models_neuron_b200.utils.kernel_bench ssd --seq 2048 --heads 128 --groups 8 --iters 10
     python -m state_space_models_neuron_b200.utils.kernel_bench norm|conv|attn|adamw ...
+    python -m torch.distributed.run --nproc-per-node T --master-addr 127.0.0.1 -m \
+        state_space_models_neuron_b200.utils.kernel_bench ag_gemm|gemm_rs --seq 2048 --gemm_k 4096 --gemm_n 18560
+        (fused collective + GEMM over T ranks; --gemm_n / --gemm_k are the GLOBAL sizes, each rank takes 1/T; the time is the
+        max over ranks and the roofline is the slower of FLOPs at the measured GEMM peak and NVLink bytes at the
+        measured 770 GB/s per direction)
 
 Prints one JSON line: time per launch (CUDA events, after warm-up, L2 flushed between launches by writing a
 256 MiB buffer), achieved TFLOP/s or GB/s and the fraction of the measured peak from MEASURED_PEAKS.json.
@@ -144,12 +149,85 @@ def bench_adamw(a):
     return time_kernel(fn, a.iters, flush=False), None, 30.0 * n
 
 
+NVLINK_GBS = 770.0      # measured peer-copy bandwidth per direction per GPU on this pool
+
+
+def _dist_setup():
+    from ..parallel import state as ps
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    ps.initialize_model_parallel(world, backend="nccl")
+    return ps, world
+
+
+def _time_collective(fn, iters, warmup=5):
+    import torch.distributed as dist
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    cuda_ops.check_status()
+    t = torch.tensor([a.elapsed_time(b) / iters], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.item()
+
+
+def bench_fused(a):
+    """all-gather + GEMM (`ag_gemm`) or GEMM + reduce-scatter (`gemm_rs`) as the training step runs them, and the
+    same operation through NCCL + the plain GEMM kernel for comparison."""
+    import torch.distributed as dist
+    from ..parallel import fused_ops, mappings as mp, symm
+    ps, T = _dist_setup()
+    L, Ls = a.seq, a.seq // T
+    ws = symm.get_workspace(L, max(a.k, a.n) if a.kernel == "ag_gemm" else a.n, torch.device("cuda"))
+    g = torch.Generator(device="cuda").manual_seed(ps.get_rank())
+    if a.kernel == "ag_gemm":
+        K, N = a.k, a.n // T
+        x = torch.randn(1, Ls, K, device="cuda", generator=g).bfloat16()
+        w = torch.randn(N, K, device="cuda", generator=g).bfloat16()
+        fused_fn = lambda: fused_ops._ag_gemm(x.reshape(Ls, K), w, False, None, ws)
+        lib_fn = lambda: cuda_ops.gemm(mp.all_gather_seq(x).reshape(L, K), w)
+        flops, link = 2.0 * L * N * K, (T - 1) * Ls * K * 2.0
+    else:
+        K, N = a.k // T, a.n
+        x = torch.randn(L, K, device="cuda", generator=g).bfloat16()
+        w = torch.randn(N, K, device="cuda", generator=g).bfloat16()
+        fused_fn = lambda: fused_ops._gemm_rs(x, w, False, ws)
+        lib_fn = lambda: mp.reduce_scatter_seq(cuda_ops.gemm(x, w).reshape(1, L, N))
+        flops, link = 2.0 * L * N * K, (T - 1) * Ls * N * 2.0
+
+    def stepped(fn):
+        def run():
+            symm.advance_step()
+            fn()
+        return run
+    ms = _time_collective(stepped(fused_fn), a.iters)
+    ms_lib = _time_collective(lib_fn, a.iters)
+    tf_peak, _, src = _peaks()
+    roof_ms = max(flops / (tf_peak * 1e9), link / (NVLINK_GBS * 1e6))
+    if dist.get_rank() == 0:
+        print(json.dumps({"kernel": a.kernel, "ranks": T, "M": L, "N": N, "K": K, "ms_fused": ms, "ms_nccl_plus_gemm": ms_lib,
+                          "roofline_ms": roof_ms, "compute_ms_at_%s_peak" % src: flops / (tf_peak * 1e9),
+                          "nvlink_ms_at_770GBs": link / (NVLINK_GBS * 1e6), "frac_of_roofline": roof_ms / ms,
+                          "timing": "back-to-back launches, CUDA events, max over ranks"}))
+    torch.cuda.synchronize()
+    dist.barrier()
+    os._exit(0)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "ssd", "norm", "conv", "attn", "adamw"])
-    ap.add_argument("--m", type=int, default=2048)
-    ap.add_argument("--n", type=int, default=4096)
-    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("kernel", choices=["gemm", "ssd", "norm", "conv", "attn", "adamw", "ag_gemm", "gemm_rs"])
+    ap.add_argument("--m", "--gemm_m", type=int, default=2048)
+    ap.add_argument("--n", "--gemm_n", type=int, default=4096)   # --gemm_* spellings: torchrun rejects "--n"
+    ap.add_argument("--k", "--gemm_k", type=int, default=4096)
     ap.add_argument("--layout", default="tn", choices=["tn", "nn", "tt"])
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--batch", type=int, default=1)
@@ -161,6 +239,8 @@ def main(argv=None):
     ap.add_argument("--backward", action="store_true")
     ap.add_argument("--iters", type=int, default=10)
     a = ap.parse_args(argv)
+    if a.kernel in ("ag_gemm", "gemm_rs"):
+        return bench_fused(a)
     ms, flops, byts = {"gemm": bench_gemm, "ssd": bench_ssd, "norm": bench_norm, "conv": bench_conv,
                        "attn": bench_attn, "adamw": bench_adamw}[a.kernel](a)
     tf_peak, bw_peak, src = _peaks()
