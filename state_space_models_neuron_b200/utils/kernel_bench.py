@@ -2,6 +2,7 @@
 timing behind the roofline numbers in `profiles/`.
 
     python -m state_space_models_neuron_b200.utils.kernel_bench gemm --m 2048 --n 18560 --k 4096 --iters 20
+    python -m state_space_models_neuron_b200.utils.kernel_bench gemm --m 2048 --n 4096 --k 1024 --trace
     python -m state_space_models_neuron_b200.utils.kernel_bench ssd --seq 2048 --heads 128 --groups 8 --iters 10
     python -m state_space_models_neuron_b200.utils.kernel_bench norm|conv|attn|adamw ...
     python -m torch.distributed.run --nproc-per-node T --master-addr 127.0.0.1 -m \
@@ -68,6 +69,39 @@ def bench_gemm(a):
         fn = lambda: cuda_ops.gemm(At, Bt, a_mn=True, b_mn=True, out=out, accumulate=False)
     ms = time_kernel(fn, a.iters)
     return ms, 2.0 * a.m * a.n * a.k, None
+
+
+def trace_gemm(a):
+    """Timeline of one GEMM launch from the kernel's own timestamps (global timer, one record per CTA): when the
+    first operands land, when each accumulator is complete, how long the epilogue takes."""
+    import ctypes
+    from ..ops import native
+    lib = native.lib()
+    A = torch.randn(a.m, a.k, device="cuda").bfloat16()
+    B = torch.randn(a.n, a.k, device="cuda").bfloat16()
+    odt = torch.float32 if a.fp32_out else torch.bfloat16
+    for _ in range(3):
+        cuda_ops.gemm(A, B, out_dtype=odt)
+    torch.cuda.synchronize()
+    tr = torch.zeros(148 * 16, dtype=torch.int64, device="cuda")
+    lib.ssm_gemm_set_trace(ctypes.c_void_p(tr.data_ptr()))
+    cuda_ops.gemm(A, B, out_dtype=odt)
+    torch.cuda.synchronize()
+    lib.ssm_gemm_set_trace(ctypes.c_void_p(0))
+    t = tr.view(148, 16).cpu().double()
+    t0 = t[:, 0][t[:, 0] > 0].min()
+    names = [(0, "CTA set-up done"), (8, "first TMA load issued"), (1, "first stage landed"),
+             (2, "first tile: MMAs issued"), (4, "first tile: accumulator complete"), (5, "first tile: epilogue done"),
+             (3, "last tile: MMAs issued"), (6, "last tile: accumulator complete"), (7, "last tile: epilogue done")]
+    out = {"kernel": "gemm-trace", "m": a.m, "n": a.n, "k": a.k, "out": str(odt), "events_us": {}}
+    for slot, name in names:
+        col = t[:, slot]
+        col = col[col > 0]
+        if len(col):
+            out["events_us"][name] = {"ctas": int(len(col)), "min": round(float((col.min() - t0) / 1e3), 2),
+                                      "median": round(float((col.median() - t0) / 1e3), 2),
+                                      "max": round(float((col.max() - t0) / 1e3), 2)}
+    print(json.dumps(out))
 
 
 def bench_ssd(a):
@@ -237,10 +271,14 @@ def main(argv=None):
     ap.add_argument("--cols", type=int, default=8192)
     ap.add_argument("--group", type=int, default=8192)
     ap.add_argument("--backward", action="store_true")
+    ap.add_argument("--trace", action="store_true", help="gemm: print the in-kernel pipeline timeline instead of timing")
+    ap.add_argument("--fp32_out", action="store_true", help="gemm --trace: fp32 output (gradient epilogue)")
     ap.add_argument("--iters", type=int, default=10)
     a = ap.parse_args(argv)
     if a.kernel in ("ag_gemm", "gemm_rs"):
         return bench_fused(a)
+    if a.kernel == "gemm" and a.trace:
+        return trace_gemm(a)
     ms, flops, byts = {"gemm": bench_gemm, "ssd": bench_ssd, "norm": bench_norm, "conv": bench_conv,
                        "attn": bench_attn, "adamw": bench_adamw}[a.kernel](a)
     tf_peak, bw_peak, src = _peaks()
