@@ -163,11 +163,21 @@ def main():
     step, gstep, graph_note = eager_step, None, "off"
     if args.graph == "on" and args.impl == "ours":
         from state_space_models_neuron_b200.parallel.graph import GraphedTrainStep
-        gstep = GraphedTrainStep(model, opt, {"input_ids": dev[0], "labels": dev[0]})
-        graph_note = "whole step (fwd+bwd+optimizer+collectives) captured once, replayed per step"
+        try:
+            gstep = GraphedTrainStep(model, opt, {"input_ids": dev[0], "labels": dev[0]})
+        except Exception as e:                       # fall back to eager launches, on every rank or on none
+            print(f"[rank {rank}] CUDA graph capture failed, running eager: {e!r}", file=sys.stderr, flush=True)
+            gstep = None
+        ok = torch.tensor([1 if gstep is not None else 0], device="cuda")
+        if world > 1:
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()) == 0:
+            gstep = None
+        else:
+            graph_note = "whole step (fwd+bwd+optimizer+collectives) captured once, replayed per step"
 
-        def step(ids):
-            return gstep({"input_ids": ids, "labels": ids})
+            def step(ids):
+                return gstep({"input_ids": ids, "labels": ids})
 
     def barrier():
         if world > 1:

@@ -131,6 +131,38 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   const int nctas = p.gemm_ctas;
   const int seqv = cm.seq + (cm.seq_base != nullptr ? *cm.seq_base : 0);
 
+  if (cm.ag && cm.comm_ctas == 0) {
+    // ------------------------------------------------------------------ cooperative all-gather push
+    // Every CTA first moves a slice of the local shard into all ranks' gather buffers (P2P stores), the last one
+    // to finish publishes this rank's flag everywhere; only then do the CTAs turn to their tiles.  The tiles of
+    // remote shards could not start before the data has crossed NVLink anyway, and all SMs storing together get
+    // the shard out several times faster than a few dedicated CTAs.
+    const int vec_per_row = cm.ag_cols / 8;
+    const long long total = (long long)cm.rows_per_shard * vec_per_row;
+    const long long row_off = (long long)cm.me * cm.rows_per_shard;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+      const long long r = i / vec_per_row;
+      const int c = (int)(i % vec_per_row) * 8;
+      const uint4 v = *reinterpret_cast<const uint4*>(cm.ag_src + r * cm.ag_src_ld + c);
+      #pragma unroll
+      for (int k = 0; k < MAX_RANKS; ++k) {
+        const int t = (cm.me + k) % MAX_RANKS;
+        if (t < cm.nranks)
+          *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(cm.ag_dst.p[t]) + (row_off + r) * cm.ag_dst_ld + c) = v;
+      }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const int done = atomicAdd(cm.ag_counter, 1) + 1;
+      if (done == (int)gridDim.x) {
+        __threadfence_system();
+        for (int t = 0; t < cm.nranks; ++t)
+          st_release_sys_s32(reinterpret_cast<int*>(cm.flag_ptrs.p[t]) + cm.ag_flag_base + cm.me, seqv);
+        *cm.ag_counter = 0;
+      }
+    }
+  }
   if ((int)blockIdx.x >= nctas) {
     // ------------------------------------------------------------------ communication CTA (all-gather push)
     const int ci = blockIdx.x - nctas;
@@ -630,7 +662,7 @@ extern "C" int ssm_gemm_bf16_fused(const void* A, const void* B, void* C, int M,
   if (M <= 0 || N <= 0 || K <= 0 || nranks < 1 || nranks > MAX_RANKS || me < 0 || me >= nranks) return -SSM_ERR_BAD_ARG;
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
     return -SSM_ERR_BAD_ARG;
-  if (ag && (a_mn || rows_per_shard % GEMM_BM || (long long)rows_per_shard * nranks != M || K % 8 || comm_ctas < 1 ||
+  if (ag && (a_mn || rows_per_shard % GEMM_BM || (long long)rows_per_shard * nranks != M || K % 8 || comm_ctas < 0 ||
              ag_src_ld % 8 || ag_dst_ld % 8))
     return -SSM_ERR_BAD_ARG;
   if (rs && (rows_per_owner % GEMM_BM || (long long)rows_per_owner * nranks != M || land_ld % 8)) return -SSM_ERR_BAD_ARG;

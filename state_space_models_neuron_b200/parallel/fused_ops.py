@@ -25,7 +25,11 @@ from . import symm
 from ..ops import cuda_ops
 from ..ops.cuda_ops import _P, _ceil8, _ll, _run, _st, status_tensor
 
-COMM_CTAS = 16
+import os
+
+# CTAs of the all-gather GEMM that only push the local shard to the peers.  0 (default): every CTA pushes a slice
+# first and then computes tiles; N > 0: N dedicated CTAs push while the others start on the local shard's tiles.
+COMM_CTAS = int(os.environ.get("SSM_AG_COMM_CTAS", "0"))
 CALLS = {"ag_gemm": 0, "gemm_rs": 0}     # how many fused kernels this process has launched
 _c = ctypes
 

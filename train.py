@@ -141,9 +141,13 @@ def run(args):
                 scheduler.step()
                 global_step += 1
                 if is_root and global_step % args.logging_interval == 0:
+                    ev_end.record()
+                    ev_end.synchronize()
+                    dev_time = ev_start.elapsed_time(ev_end) / 1e3 / args.logging_interval
+                    ev_start.record()
                     step_time, tput, mfu = throughput.get_throughput()
                     logger.log(global_step, reduced.item(), optimizer.param_groups[0]["lr"], step_time, tput, mfu,
-                               tokens_per_s=tput * args.seq_len)
+                               tokens_per_s=tput * args.seq_len, device_step_time=dev_time)
                 if args.checkpoint_freq > 0 and global_step % args.checkpoint_freq == 0:
                     save(global_step)
                 if global_step >= args.max_steps:
