@@ -203,7 +203,8 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     if (p.mode != 3) tma_prefetch_desc(&tmap_c);
     if (p.mode == 3) for (int t = 0; t < cm.nranks; ++t) tma_prefetch_desc(&rsm.m[t]);
   }
-  if (warp == 1) { tmem_alloc(tmem_slot, 2 * BN); tmem_relinquish(); }
+  constexpr int TMEM_COLS = 2 * BN <= 256 ? 256 : 512;      // allocation sizes are powers of two
+  if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -532,7 +533,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   tc_fence_before_sync();
   __syncthreads();
   if (threadIdx.x == 0) trace_mark(p, 10);
-  if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
 // ------------------------------------------------------------------------------------ host
@@ -552,25 +553,31 @@ static int epilogue_direct() {
   return v;
 }
 
-// Tile width: 128x256 tiles have the better operand reuse, 128x128 tiles fill the SMs better when the 256-wide
-// tiling leaves the last wave mostly empty (the per-rank shapes of tensor parallelism).  Compare the SM-time of
-// both tilings (waves x tile cost; a 128-wide tile costs a little more than half of a 256-wide one).
-// SSM_GEMM_FORCE_BN=128|256 overrides the choice (experiments).
-static bool pick_wide_tiles(int M, int N) {
+// Tile width.  128x256 tiles have the best operand reuse; 128x192 and 128x128 tiles fill the SMs better when the
+// 256-wide tiling leaves the last wave mostly empty (the per-rank shapes of tensor parallelism).  Compare the
+// SM-time of the tilings: waves x relative tile cost (measured: a 128-wide tile costs 0.8 of a 256-wide one, a
+// 192-wide one is taken as 0.8 = 0.75 / 0.94); a narrower tiling must win by 10 % to be chosen.
+// SSM_GEMM_FORCE_BN=128|192|256 overrides the choice (experiments).
+static int pick_tile_n(int M, int N) {
   static int forced = -1;
   if (forced < 0) {
     const char* e = getenv("SSM_GEMM_FORCE_BN");
     forced = e ? atoi(e) : 0;
   }
-  if (N <= 128) return false;
-  if (forced == 128) return false;
-  if (forced == 256) return true;
+  if (N <= 128) return 128;
+  if (forced == 128 || forced == 192 || forced == 256) return forced;
   const int sms = g_num_sms > 0 ? g_num_sms : 148;
   const long long tm = (M + GEMM_BM - 1) / GEMM_BM;
-  const long long t256 = tm * ((N + 255) / 256), t128 = tm * ((N + 127) / 128);
-  const double c256 = (double)((t256 + sms - 1) / sms) * 1.0;
-  const double c128 = (double)((t128 + sms - 1) / sms) * 0.80;   // measured: 128-wide tiles run at ~0.65 of the rate
-  return c256 <= c128;
+  auto cost = [&](int bn, double tile_cost) {
+    const long long t = tm * ((N + bn - 1) / bn);
+    return (double)((t + sms - 1) / sms) * tile_cost;
+  };
+  const double c256 = cost(256, 1.0), c192 = cost(192, 0.8), c128 = cost(128, 0.8);
+  int best = 256;
+  double cb = c256;
+  if (c192 < 0.9 * cb) { best = 192; cb = c192; }
+  if (c128 < 0.9 * c256 && c128 < cb) best = 128;
+  return best;
 }
 
 template <int BN, int STAGES>
@@ -616,8 +623,7 @@ extern "C" int ssm_gemm_bf16(const void* A, const void* B, void* C, int M, int N
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
   }
-  const bool wide = pick_wide_tiles(M, N);
-  const int BN = wide ? 256 : 128;
+  const int BN = pick_tile_n(M, N);
   CUtensorMap ta, tb, tc;
   int r;
   if (!a_mn) r = make_tmap_2d_bf16(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, 64, 128);
@@ -641,7 +647,9 @@ extern "C" int ssm_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   p.ldc32 = ldc; p.status = status; p.tiles_m = 0; p.tiles_n = 0; p.gemm_ctas = 0;
   p.c16 = mode == 0 ? reinterpret_cast<__nv_bfloat16*>(C) : nullptr;
   p.ldc16 = ldc; p.direct = epilogue_direct(); p.trace = g_trace;
-  return wide ? launch_gemm<256, 4>(ta, tb, tc, p, stream) : launch_gemm<128, 6>(ta, tb, tc, p, stream);
+  if (BN == 256) return launch_gemm<256, 4>(ta, tb, tc, p, stream);
+  if (BN == 192) return launch_gemm<192, 4>(ta, tb, tc, p, stream);
+  return launch_gemm<128, 6>(ta, tb, tc, p, stream);
 }
 
 // GEMM fused with a tensor-parallel collective over peer memory (see GemmComm).
@@ -673,8 +681,7 @@ extern "C" int ssm_gemm_bf16_fused(const void* A, const void* B, void* C, int M,
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
   }
-  const bool wide = pick_wide_tiles(M, N);
-  const int BN = wide ? 256 : 128;
+  const int BN = pick_tile_n(M, N);
   CUtensorMap ta, tb, tc;
   int r;
   if (!a_mn) r = make_tmap_2d_bf16(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, 64, 128);
@@ -722,8 +729,9 @@ extern "C" int ssm_gemm_bf16_fused(const void* A, const void* B, void* C, int M,
   p.ldc32 = ldc; p.status = status; p.tiles_m = 0; p.tiles_n = 0; p.gemm_ctas = 0;
   p.c16 = mode == 0 ? reinterpret_cast<__nv_bfloat16*>(C) : nullptr;
   p.ldc16 = ldc; p.direct = epilogue_direct(); p.trace = g_trace;
-  return wide ? launch_gemm<256, 4>(ta, tb, tc, p, stream, &cm, &maps)
-              : launch_gemm<128, 6>(ta, tb, tc, p, stream, &cm, &maps);
+  if (BN == 256) return launch_gemm<256, 4>(ta, tb, tc, p, stream, &cm, &maps);
+  if (BN == 192) return launch_gemm<192, 4>(ta, tb, tc, p, stream, &cm, &maps);
+  return launch_gemm<128, 6>(ta, tb, tc, p, stream, &cm, &maps);
 }
 
 // Pipeline analysis: buf = device array of gridDim * 16 uint64 (or null to switch tracing off).  Slots (ns, global
