@@ -15,7 +15,7 @@ import torch.nn as nn
 from .. import ops
 from ..parallel import mappings as mp
 from ..parallel import state as ps
-from ..parallel.layers import ColumnParallelLinear, RowParallelLinear, normal_init
+from ..parallel.layers import ColumnParallelLinear, GQAQKVColumnParallelLinear, RowParallelLinear, normal_init
 
 
 class Mamba2HybridAttention(nn.Module):
@@ -27,10 +27,12 @@ class Mamba2HybridAttention(nn.Module):
         self.total_heads = config.attn_num_heads
         self.total_kv_heads = config.attn_key_value_heads
         self.head_dim = config.attn_head_dim
-        if self.total_heads % tp or self.total_kv_heads % tp:
-            raise ValueError("attention heads and kv heads must be divisible by the TP size")
+        self.qkv_linear = bool(getattr(config, "qkv_linear", False))
+        kv_mult = int(getattr(config, "kv_shared_group_size", 1)) if self.qkv_linear else 1
+        if self.total_heads % tp or (self.total_kv_heads * kv_mult) % tp:
+            raise ValueError("attention heads and kv heads (times kv_shared_group_size) must be divisible by the TP size")
         self.num_heads = self.total_heads // tp
-        self.num_kv_heads = self.total_kv_heads // tp
+        self.num_kv_heads = self.total_kv_heads * kv_mult // tp
         self.sequence_parallel_enabled = config.sequence_parallel_enabled and tp > 1
         self.rotary_emb_dim = getattr(config, "rotary_emb_dim", None)
         self.rope_theta = getattr(config, "rope_theta", 10000.0)
@@ -38,16 +40,24 @@ class Mamba2HybridAttention(nn.Module):
         init = normal_init(config.initializer_range)
         kw = dict(bias=False, init_method=init, dtype=dtype, device=device,
                   sequence_parallel_enabled=config.sequence_parallel_enabled)
-        self.q_proj = ColumnParallelLinear(self.hidden_size, self.total_heads * self.head_dim, **kw)
-        self.k_proj = ColumnParallelLinear(self.hidden_size, self.total_kv_heads * self.head_dim, **kw)
-        self.v_proj = ColumnParallelLinear(self.hidden_size, self.total_kv_heads * self.head_dim, **kw)
+        if self.qkv_linear:
+            # one layer for q, k, v with optional KV-head replication (mamba2hybrid_attn.py:291-303 of the reference)
+            self.qkv_proj = GQAQKVColumnParallelLinear(
+                self.hidden_size, [self.total_heads * self.head_dim, self.total_kv_heads * self.head_dim],
+                kv_size_multiplier=kv_mult, fuse_qkv=bool(getattr(config, "fuse_qkv", False)), head_dim=self.head_dim, **kw)
+        else:
+            self.q_proj = ColumnParallelLinear(self.hidden_size, self.total_heads * self.head_dim, **kw)
+            self.k_proj = ColumnParallelLinear(self.hidden_size, self.total_kv_heads * self.head_dim, **kw)
+            self.v_proj = ColumnParallelLinear(self.hidden_size, self.total_kv_heads * self.head_dim, **kw)
         self.o_proj = RowParallelLinear(self.total_heads * self.head_dim, self.hidden_size, bias=False,
                                         init_method=init, dtype=dtype, device=device,
                                         sequence_parallel_enabled=config.sequence_parallel_enabled)
 
     def forward(self, hidden_states: torch.Tensor, cache_params=None) -> torch.Tensor:
         qkv = None
-        if self.sequence_parallel_enabled:
+        if self.qkv_linear:
+            qkv = self.qkv_proj(hidden_states)
+        elif self.sequence_parallel_enabled:
             from ..parallel import fused
             if fused.enabled_for(hidden_states):
                 qkv = fused.all_gather_multi_linear(

@@ -145,6 +145,116 @@ class ColumnParallelLinear(nn.Module):
         return y
 
 
+class _ReplicaGradSync(torch.autograd.Function):
+    """Identity whose gradient is summed over the ranks that hold copies of the same weight rows."""
+
+    @staticmethod
+    def forward(ctx, w, group):
+        ctx.group = group
+        return w.view_as(w)
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous()
+        torch.distributed.all_reduce(g, group=ctx.group)
+        return g, None
+
+
+_KV_REPLICA_GROUPS = {}
+
+
+def _kv_replica_group(multiplier: int):
+    """Process group of the `multiplier` consecutive TP ranks that share one replicated KV head block.  Created
+    collectively (every rank creates every group, in the same order) on first use."""
+    if multiplier == 1 or not torch.distributed.is_initialized():
+        return None
+    key = (multiplier, id(ps.get_tensor_model_parallel_group()))
+    if key not in _KV_REPLICA_GROUPS:
+        world = torch.distributed.get_world_size()
+        tp = ps.get_tensor_model_parallel_size()
+        mine = None
+        for base in range(0, world, tp):                 # every TP group of the job
+            for j in range(0, tp, multiplier):
+                ranks = list(range(base + j, base + j + multiplier))
+                grp = torch.distributed.new_group(ranks)
+                if torch.distributed.get_rank() in ranks:
+                    mine = grp
+        _KV_REPLICA_GROUPS[key] = mine
+    return _KV_REPLICA_GROUPS[key]
+
+
+class GQAQKVColumnParallelLinear(nn.Module):
+    """Query / key / value projections of grouped-query attention as one column-parallel layer that returns
+    `(q, k, v)` (neuronx-distributed's GQAQKVColumnParallelLinear as the reference would use it when
+    `config.qkv_linear` is set, mamba2hybrid/mamba2hybrid_attn.py:291-303; the hybrid presets leave it off).
+
+    `output_sizes = [q_size, kv_size]`.  Parameters: `weight_q [q_size/TP, in]`, `weight_k`, `weight_v`
+    `[kv_size * kv_size_multiplier / TP, in]`.  `kv_size_multiplier` > 1 replicates every KV head that many times
+    (adjacent copies, so query head h still meets the copy of its original KV head) which lets TP exceed the number
+    of KV heads; the copies start equal and stay equal because their gradients are summed over the ranks that hold
+    them.  All three projections share one sequence all-gather (the fused all-gather GEMM on the GPU path)."""
+
+    def __init__(self, input_size: int, output_sizes: Sequence[int], bias: bool = False, gather_output: bool = False,
+                 init_method: Optional[Callable] = None, dtype: torch.dtype = torch.float32,
+                 sequence_parallel_enabled: bool = False, sequence_dimension: int = 1, kv_size_multiplier: int = 1,
+                 fuse_qkv: bool = False, head_dim: Optional[int] = None, device=None):
+        super().__init__()
+        assert sequence_dimension == 1 and not gather_output
+        tp, r = ps.get_tensor_model_parallel_size(), ps.get_tensor_model_parallel_rank()
+        q_size, kv_size = int(output_sizes[0]), int(output_sizes[1])
+        m = int(kv_size_multiplier)
+        if q_size % tp or (kv_size * m) % tp:
+            raise ValueError("q size and kv size * kv_size_multiplier must be divisible by the TP size")
+        if m > 1 and (tp % m or head_dim is None or kv_size % head_dim):
+            raise ValueError("kv_size_multiplier > 1 needs head_dim and a TP size that is a multiple of it")
+        self.input_size, self.q_size, self.kv_size, self.kv_size_multiplier = input_size, q_size, kv_size, m
+        self.sequence_parallel_enabled = sequence_parallel_enabled and tp > 1
+        self.fuse_qkv = fuse_qkv       # accepted for API parity; the three GEMMs already share the all-gather
+        init = init_method or default_linear_init
+        gen = _next_generator(device if device is not None else "cpu")
+
+        def make(rows, replicate):
+            full = torch.empty(rows, input_size, dtype=torch.float32, device=device)
+            init(full, generator=gen)
+            if replicate > 1:      # copy whole heads, copies adjacent
+                full = full.view(rows // head_dim, 1, head_dim, input_size).expand(-1, replicate, -1, -1) \
+                           .reshape(rows * replicate, input_size)
+            p = nn.Parameter(shard_rows(full, None, r, tp).to(dtype).contiguous())
+            _mark(p, 0)
+            return p
+
+        self.weight_q = make(q_size, 1)
+        self.weight_k = make(kv_size, m)
+        self.weight_v = make(kv_size, m)
+        if bias:
+            self.bias_q = nn.Parameter(torch.zeros(self.weight_q.shape[0], dtype=dtype, device=device))
+            self.bias_k = nn.Parameter(torch.zeros(self.weight_k.shape[0], dtype=dtype, device=device))
+            self.bias_v = nn.Parameter(torch.zeros(self.weight_v.shape[0], dtype=dtype, device=device))
+            for b in (self.bias_q, self.bias_k, self.bias_v):
+                _mark(b, 0)
+        else:
+            self.bias_q = self.bias_k = self.bias_v = None
+        self._replica_group = _kv_replica_group(m) if tp > 1 else None
+
+    def forward(self, x: torch.Tensor):
+        wq, wk, wv = self.weight_q, self.weight_k, self.weight_v
+        bk, bv = self.bias_k, self.bias_v
+        if self._replica_group is not None:
+            wk, wv = _ReplicaGradSync.apply(wk, self._replica_group), _ReplicaGradSync.apply(wv, self._replica_group)
+            if bk is not None:
+                bk, bv = _ReplicaGradSync.apply(bk, self._replica_group), _ReplicaGradSync.apply(bv, self._replica_group)
+        if self.sequence_parallel_enabled:
+            from . import fused
+            if self.bias_q is None and self._replica_group is None and fused.enabled_for(x):
+                out = fused.all_gather_multi_linear(x, (wq, wk, wv))
+                if out is not None:
+                    return out
+            xg = mp.gather_from_sequence_parallel_region(x, True)
+        else:
+            xg = mp.copy_to_tensor_parallel_region(x)
+        return ops.linear(xg, wq, self.bias_q), ops.linear(xg, wk, bk), ops.linear(xg, wv, bv)
+
+
 class RowParallelLinear(nn.Module):
     """Y = X W^T with W split along its input columns; X arrives already split on its last dim.
 

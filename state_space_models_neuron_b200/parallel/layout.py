@@ -48,6 +48,8 @@ def partition_rule(key: str, config) -> Rule:
         return 0, None
     if re.search(r"(embeddings|embedding|lm_head|q_proj|k_proj|v_proj)\.weight$", key):
         return 0, None
+    if re.search(r"qkv_proj\.(weight|bias)_[qkv]$", key):      # kv_size_multiplier 1 only (no replicated heads)
+        return 0, None
     return None, None  # block norms, norm_f: replicated
 
 

@@ -144,3 +144,37 @@ def _tp_decode_worker(rank, world, hybrid):
 def test_tensor_parallel_decode_matches_full_forward():
     # the hybrid model has no decode cache (the reference asserts use_cache is False, mamba2hybrid_attn.py:379)
     run_ranks(_tp_decode_worker, 2, False)
+
+
+def _gqa_qkv_worker(rank, world):
+    """GQAQKVColumnParallelLinear with one KV head replicated over two TP ranks: outputs equal the single-rank
+    projections and both copies of the KV weights receive the same (summed) gradient."""
+    import torch.distributed as dist
+    from state_space_models_neuron_b200.parallel import state as ps
+    from state_space_models_neuron_b200.parallel.layers import GQAQKVColumnParallelLinear, set_init_seed
+    hd, Hq, Hkv, D = 8, 4, 1, 32
+    x = torch.randn(2, 16, D, generator=torch.Generator().manual_seed(1))
+    ps.initialize_model_parallel(1)
+    set_init_seed(3)
+    ref = GQAQKVColumnParallelLinear(D, [Hq * hd, Hkv * hd], kv_size_multiplier=1, head_dim=hd)
+    q0, k0, v0 = ref(x)
+    (q0.square().sum() + (k0 * 2).sum() + v0.square().sum()).backward()
+    ps.destroy_model_parallel()
+    ps.initialize_model_parallel(world)
+    set_init_seed(3)
+    lay = GQAQKVColumnParallelLinear(D, [Hq * hd, Hkv * hd], kv_size_multiplier=2, head_dim=hd)
+    assert lay.weight_k.shape == (hd, D) and torch.equal(lay.weight_k, ref.weight_k)      # a full copy per rank
+    xr = x.clone().requires_grad_(True)
+    q, k, v = lay(xr)
+    per = Hq * hd // world
+    assert torch.allclose(q, q0[..., rank * per:(rank + 1) * per], atol=1e-6)
+    assert torch.allclose(k, k0, atol=1e-6) and torch.allclose(v, v0, atol=1e-6)
+    # each rank uses its copy for half of the query heads: loss split accordingly, gradients summed over the copies
+    (q.square().sum() + (k * 2).sum() / world + v.square().sum() / world).backward()
+    assert torch.allclose(lay.weight_k.grad, ref.weight_k.grad, atol=1e-5), (lay.weight_k.grad - ref.weight_k.grad).abs().max()
+    assert torch.allclose(lay.weight_v.grad, ref.weight_v.grad, atol=1e-5)
+    assert torch.allclose(lay.weight_q.grad, ref.weight_q.grad[rank * per:(rank + 1) * per], atol=1e-5)
+
+
+def test_gqa_qkv_linear_kv_replication():
+    run_ranks(_gqa_qkv_worker, 2)
