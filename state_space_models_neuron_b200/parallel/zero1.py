@@ -172,17 +172,33 @@ class Zero1Optimizer(torch.optim.Optimizer):
         tagged = [p for p, *_ in self.layout if getattr(p, "sequence_parallel_enabled", False)]
         if not tagged:
             return
-        bucket = torch.cat([p.main_grad.reshape(-1) for p in tagged])
+        rng = self._sp_grad_range()
+        # the tagged parameters normally sit next to each other in the flat buffer: reduce that slice in place
+        bucket = self.flat_grads[rng[0]:rng[1]] if rng else torch.cat([p.main_grad.reshape(-1) for p in tagged])
         from . import fused
         done = bucket.dtype == torch.float32 and all(
             fused.small_allreduce(bucket[i:i + 16384], "sum") for i in range(0, bucket.numel(), 16384)) \
             if bucket.numel() <= 32 * 16384 else False
         if not done:
             dist.all_reduce(bucket, group=self.tp_group)
+        if rng:
+            return
         off = 0
         for p in tagged:
             p.main_grad.copy_(bucket[off:off + p.numel()].view(p.shape))
             off += p.numel()
+
+    def _sp_grad_range(self):
+        """(lo, hi) of the flat-buffer slice that holds exactly the sequence-parallel-tagged gradients (padding
+        between them is zero and stays zero under a sum), or None when other parameters lie in between."""
+        if not hasattr(self, "_sp_range"):
+            spans = sorted((start, start + _ceil_to(n, _ALIGN), bool(getattr(p, "sequence_parallel_enabled", False)))
+                           for p, start, n, gi, rep in self.layout)
+            tagged = [(a, b) for a, b, t in spans if t]
+            lo, hi = tagged[0][0], tagged[-1][1]
+            clean = all(t for a, b, t in spans if a >= lo and b <= hi)
+            self._sp_range = (lo, min(hi, self.total)) if clean else None
+        return self._sp_range
 
     def _reduce_gradients(self) -> torch.Tensor:
         """Average over DP; returns this rank's fp32 gradient shard."""

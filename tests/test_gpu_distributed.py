@@ -24,3 +24,17 @@ def test_tp_matches_single_gpu(extra):
         pytest.skip("needs at least 2 GPUs")
     r = _torchrun(min(n, 8) if n in (2, 4, 8) else 2, *extra, port=29611 + len(extra))
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_tp_decode_matches_forward():
+    """Token-by-token decode under TP=2 (one-kernel all-reduce after out_proj, graph-free) reproduces the logits of
+    the full forward pass on every rank's vocabulary shard."""
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29631", os.path.join(ROOT, "mamba2_inference.py"), "--mode", "check", "--model", "Mamba130M",
+           "--tp", "2", "--n_groups", "2", "--head_dim", "64", "--batch", "2", "--seq_len", "256"]
+    r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
