@@ -160,6 +160,29 @@ def main():
         opt.zero_grad()
         return loss
 
+    if fused and tp > 1:
+        # pre-flight of the fused collective kernels: one eager step; if any rank reports a failed wait, every rank
+        # switches to the NCCL collectives (same kernels otherwise) and the JSON line says so
+        bad = 0
+        try:
+            eager_step(dev[0])
+            torch.cuda.synchronize()
+            cuda_ops.check_status()
+        except Exception as e:
+            print(f"[rank {rank}] fused collectives failed in the pre-flight step: {e!r}", file=sys.stderr, flush=True)
+            bad = 1
+        flag = torch.tensor([bad], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+        if int(flag.item()):
+            from state_space_models_neuron_b200.parallel import fused as fused_switch
+            fused_switch.set_enabled(False)
+            fused = False
+            torch.cuda.synchronize()
+            try:
+                cuda_ops.check_status()
+            except Exception:
+                pass
+            opt.zero_grad()
     step, gstep, graph_note = eager_step, None, "off"
     if args.graph == "on" and args.impl == "ours":
         from state_space_models_neuron_b200.parallel.graph import GraphedTrainStep

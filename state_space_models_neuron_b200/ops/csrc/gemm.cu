@@ -31,6 +31,7 @@ struct GemmParams {
   long long ldc32;
   __nv_bfloat16* c16;    // mode 0 (direct-store epilogue)
   long long ldc16;
+  int prefetch;          // k-blocks that the TMA producer prefetches into L2 ahead of its loads (0 = off)
   unsigned long long* trace;   // optional [grid][16] timestamps (ns) for pipeline analysis, else null
   int direct;            // 1: epilogue warps store their rows straight from registers (no smem staging / TMA store)
   int* status;
@@ -235,6 +236,27 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           }
         }
         for (int kb = 0; kb < kblocks; ++kb) {
+          if (p.prefetch > 0) {
+            // L2 prefetch of the operand tiles this CTA will load `prefetch` k-blocks from now (possibly in its next
+            // tile): the ring of STAGES loads then completes at L2 latency instead of HBM latency
+            int pk = kb + p.prefetch, ptile = tile;
+            while (pk >= kblocks) { pk -= kblocks; ptile += nctas; }
+            if (ptile < num_tiles) {
+              int ptm = ptile % p.tiles_m;
+              if (cm.ag) ptm = rotate_m(ptm, p.tiles_m, cm.rows_per_shard / GEMM_BM, cm.me);
+              if (cm.rs) ptm = rotate_m(ptm, p.tiles_m, cm.rows_per_owner / GEMM_BM, (cm.me + 1) % cm.nranks);
+              const int pm0 = ptm * GEMM_BM, pn0 = (ptile / p.tiles_m) * BN, pk0 = pk * GEMM_BK;
+              if (!cm.ag) {                       // gathered rows may not have arrived yet: weights only in that case
+                if (!p.a_mn) tma_prefetch_l2_2d(&tmap_a, pk0, pm0);
+                else { tma_prefetch_l2_2d(&tmap_a, pm0, pk0); tma_prefetch_l2_2d(&tmap_a, pm0 + 64, pk0); }
+              }
+              if (!p.b_mn) tma_prefetch_l2_2d(&tmap_b, pk0, pn0);
+              else {
+                #pragma unroll
+                for (int j = 0; j < BN / 64; ++j) tma_prefetch_l2_2d(&tmap_b, pn0 + 64 * j, pk0);
+              }
+            }
+          }
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status)) { ok = false; break; }
           uint8_t* sa = smem + stage * L::STAGE_BYTES;
           uint8_t* sb = sa + L::A_BYTES;
@@ -544,6 +566,17 @@ static int g_num_sms = 0;
 // most for the fp32 gradient outputs; kept for experiments).
 static unsigned long long* g_trace = nullptr;
 
+// SSM_GEMM_PREFETCH=n: the producer prefetches operand tiles n k-blocks ahead into L2 (0 = off).
+static int gemm_prefetch_distance() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("SSM_GEMM_PREFETCH");
+    v = e ? atoi(e) : 0;
+    if (v < 0) v = 0;
+  }
+  return v;
+}
+
 static int epilogue_direct() {
   static int v = -1;
   if (v < 0) {
@@ -646,7 +679,7 @@ extern "C" int ssm_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   p.c32 = mode == 0 ? nullptr : reinterpret_cast<float*>(C);
   p.ldc32 = ldc; p.status = status; p.tiles_m = 0; p.tiles_n = 0; p.gemm_ctas = 0;
   p.c16 = mode == 0 ? reinterpret_cast<__nv_bfloat16*>(C) : nullptr;
-  p.ldc16 = ldc; p.direct = epilogue_direct(); p.trace = g_trace;
+  p.ldc16 = ldc; p.direct = epilogue_direct(); p.trace = g_trace; p.prefetch = gemm_prefetch_distance();
   if (BN == 256) return launch_gemm<256, 4>(ta, tb, tc, p, stream);
   if (BN == 192) return launch_gemm<192, 4>(ta, tb, tc, p, stream);
   return launch_gemm<128, 6>(ta, tb, tc, p, stream);
@@ -728,7 +761,7 @@ extern "C" int ssm_gemm_bf16_fused(const void* A, const void* B, void* C, int M,
   p.c32 = (mode == 1 || mode == 2) ? reinterpret_cast<float*>(C) : nullptr;
   p.ldc32 = ldc; p.status = status; p.tiles_m = 0; p.tiles_n = 0; p.gemm_ctas = 0;
   p.c16 = mode == 0 ? reinterpret_cast<__nv_bfloat16*>(C) : nullptr;
-  p.ldc16 = ldc; p.direct = epilogue_direct(); p.trace = g_trace;
+  p.ldc16 = ldc; p.direct = epilogue_direct(); p.trace = g_trace; p.prefetch = gemm_prefetch_distance();
   if (BN == 256) return launch_gemm<256, 4>(ta, tb, tc, p, stream, &cm, &maps);
   if (BN == 192) return launch_gemm<192, 4>(ta, tb, tc, p, stream, &cm, &maps);
   return launch_gemm<128, 6>(ta, tb, tc, p, stream, &cm, &maps);
