@@ -351,3 +351,25 @@ def test_embedding_lookup_and_scatter_add(vocab_start, vloc):
         cuda_ops.embedding(ids, w2, vocab_start).backward(go)
     assert w2.grad is None and w2.grad_stale is False
     _close(w2.main_grad, 2 * gref, atol=1e-3, rtol=1e-4)
+
+
+def test_bounded_flag_wait_reports_timeout():
+    """A wait on a flag that nothing sets gives up after its limit (2 s), records status 2 (flag wait timed out)
+    for the host and leaves the context usable: the next kernel runs normally."""
+    import time
+    from state_space_models_neuron_b200.ops import cuda_ops
+    flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+    st = cuda_ops.status_tensor(flags.device)
+    torch.cuda.synchronize()
+    t0 = time.time()
+    cuda_ops._run("ssm_zero1_wait", cuda_ops._P(flags), 0, 2, 5, None, cuda_ops._P(st), cuda_ops._st())
+    torch.cuda.synchronize()
+    waited = time.time() - t0
+    assert 1.0 < waited < 10.0, waited
+    with pytest.raises(RuntimeError, match="status 2"):
+        cuda_ops.check_status()
+    a = torch.randn(128, 64, device="cuda").bfloat16()
+    out = cuda_ops.gemm(a, a)
+    torch.cuda.synchronize()
+    cuda_ops.check_status()
+    _close(out, a.float() @ a.float().t(), atol=0.5, rtol=2e-2)

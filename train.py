@@ -122,8 +122,13 @@ def run(args):
         if not use_cuda or args.grad_accum_usteps != 1:
             raise SystemExit("--cuda_graph needs a CUDA device and --grad_accum_usteps 1")
     done = global_step >= args.max_steps
+    # a resumed run continues with the batch that the interrupted run would have seen next
+    skip_batches = global_step * args.grad_accum_usteps if args.resume else 0
     while not done:
         for data in device_loader:
+            if skip_batches > 0:
+                skip_batches -= 1
+                continue
             training_step += 1
             if args.cuda_graph:
                 if graphed is None:
