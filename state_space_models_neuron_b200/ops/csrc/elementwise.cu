@@ -604,6 +604,23 @@ sumsq_kernel(const GT* __restrict__ g, long long n4, float* __restrict__ total) 
   if (threadIdx.x == 0) atomicAdd(total, s);
 }
 
+// sum of squares over a list of [lo, hi) element ranges of one fp32 buffer (lo, hi multiples of 4), one launch:
+// grid (x, number of ranges); blocks beyond the end of a short range leave at once
+__global__ void __launch_bounds__(256)
+sumsq_ranges_kernel(const float* __restrict__ g, const long long* __restrict__ ranges, float* __restrict__ total) {
+  __shared__ float red[33];
+  const long long lo = ranges[2 * blockIdx.y], n4 = (ranges[2 * blockIdx.y + 1] - lo) / 4;
+  if ((long long)blockIdx.x * blockDim.x >= n4) return;
+  const float* base = g + lo;
+  float s = 0.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    const float4 x = *reinterpret_cast<const float4*>(base + i * 4);
+    s += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+  }
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) atomicAdd(total, s);
+}
+
 // =====================================================================================
 // finalisation of small parameter gradients: column sums of per-CTA partial buffers written straight into the
 // fp32 main-gradient buffers (store or accumulate per parameter), so the mixer backward issues one launch
@@ -959,6 +976,13 @@ extern "C" int ssm_mixer_small_grads(const void* conv_part, int T1, int C, const
   a.acc_mask = acc_mask;
   const long long n = (long long)C * 5 + d_in + (long long)H * 3;
   mixer_small_grads_kernel<<<(unsigned)((n + CS_COLS - 1) / CS_COLS), 256, 0, st>>>(a);
+  return (int)cudaGetLastError();
+}
+extern "C" int ssm_sumsq_ranges(const void* g, const void* ranges, int nranges, void* total, cudaStream_t st) {
+  if (nranges < 1 || (reinterpret_cast<uintptr_t>(g) & 15)) return nranges == 0 ? 0 : -SSM_ERR_BAD_ARG;
+  dim3 grid(148 * 2, nranges);
+  sumsq_ranges_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const float*>(g), reinterpret_cast<const long long*>(ranges),
+                                            reinterpret_cast<float*>(total));
   return (int)cudaGetLastError();
 }
 extern "C" int ssm_mixer_param_prep(const void* A_log, const void* D, const void* dt_bias, int bf16_mask, int H,

@@ -31,6 +31,7 @@ struct GemmParams {
   long long ldc32;
   __nv_bfloat16* c16;    // mode 0 (direct-store epilogue)
   long long ldc16;
+  float* sumsq;          // mode 1 only: += sum of squares of every stored element (gradient-norm contribution)
   int prefetch;          // k-blocks that the TMA producer prefetches into L2 ahead of its loads (0 = off)
   unsigned long long* trace;   // optional [grid][16] timestamps (ns) for pipeline analysis, else null
   int direct;            // 1: epilogue warps store their rows straight from registers (no smem staging / TMA store)
@@ -332,6 +333,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     int acc = 0; uint32_t acc_phase = 0;
     bool ok = true;
     int stores_issued = 0;
+    float ssq = 0.f;                               // this thread's share of sum(C^2) (mode 1 with p.sumsq)
     int rs_count[MAX_RANKS];
     #pragma unroll
     for (int t = 0; t < MAX_RANKS; ++t) rs_count[t] = 0;
@@ -502,6 +504,10 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
               for (int c = 0; c < 8; ++c)
                 *reinterpret_cast<uint4*>(buf + sw128_offset(row, c)) =
                     make_uint4(v[h][c * 4], v[h][c * 4 + 1], v[h][c * 4 + 2], v[h][c * 4 + 3]);
+              if (p.sumsq != nullptr) {            // rows / columns beyond M, N hold exact zeros (TMA zero fill)
+                #pragma unroll
+                for (int e = 0; e < 32; ++e) ssq += __uint_as_float(v[h][e]) * __uint_as_float(v[h][e]);
+              }
               fence_proxy_async_smem();
               asm volatile("bar.sync 1, 128;" ::: "memory");
               if (epi_tid == 0) {
@@ -524,6 +530,11 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       if (epi_tid == 0) trace_mark(p, tile == (int)blockIdx.x ? 5 : 7);
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+    if (p.sumsq != nullptr && p.mode == 1) {
+      #pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+      if (lane == 0) atomicAdd(p.sumsq, ssq);
     }
     if (cm.rs && p.direct) {
       // the rows were written with ordinary stores by all epilogue threads: make them visible system-wide before
@@ -643,9 +654,29 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
 // b_mn = 0: B is [N,K] with row stride ldb; b_mn = 1: B is [K,N] with row stride ldb.
 // mode 0: C bf16 [M, ldc] (ldc * 2 bytes must be a multiple of 16); 1: C fp32 store; 2: C fp32 += .
 // All leading dimensions in elements; operand bases 16-byte aligned, operand row strides multiples of 8.
+static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                          long long ldc, int a_mn, int b_mn, int mode, const void* bias, int act, int* status,
+                          cudaStream_t stream, float* sumsq);
+
 extern "C" int ssm_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
                              long long ldb, long long ldc, int a_mn, int b_mn, int mode, const void* bias, int act,
                              int* status, cudaStream_t stream) {
+  return gemm_bf16_impl(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, mode, bias, act, status, stream, nullptr);
+}
+
+// Same, and with mode 1 (fp32 store) the sum of squares of the stored matrix is added to *sumsq (fp32, device):
+// the wgrad GEMM then delivers its share of the global gradient norm without a second pass over the gradient.
+extern "C" int ssm_gemm_bf16_ex(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                                long long ldb, long long ldc, int a_mn, int b_mn, int mode, const void* bias, int act,
+                                int* status, cudaStream_t stream, void* sumsq) {
+  if (sumsq != nullptr && mode != 1) return -SSM_ERR_BAD_ARG;
+  return gemm_bf16_impl(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, mode, bias, act, status, stream,
+                        reinterpret_cast<float*>(sumsq));
+}
+
+static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                          long long ldc, int a_mn, int b_mn, int mode, const void* bias, int act, int* status,
+                          cudaStream_t stream, float* sumsq) {
   using namespace ssm;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
@@ -679,7 +710,8 @@ extern "C" int ssm_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   p.c32 = mode == 0 ? nullptr : reinterpret_cast<float*>(C);
   p.ldc32 = ldc; p.status = status; p.tiles_m = 0; p.tiles_n = 0; p.gemm_ctas = 0;
   p.c16 = mode == 0 ? reinterpret_cast<__nv_bfloat16*>(C) : nullptr;
-  p.ldc16 = ldc; p.direct = epilogue_direct(); p.trace = g_trace; p.prefetch = gemm_prefetch_distance();
+  p.ldc16 = ldc; p.direct = epilogue_direct(); p.trace = g_trace; p.prefetch = gemm_prefetch_distance(); p.sumsq = sumsq;
+  if (sumsq != nullptr) p.direct = 0;      // the sum of squares is formed in the staged (TMA-store) epilogue
   if (BN == 256) return launch_gemm<256, 4>(ta, tb, tc, p, stream);
   if (BN == 192) return launch_gemm<192, 4>(ta, tb, tc, p, stream);
   return launch_gemm<128, 6>(ta, tb, tc, p, stream);
@@ -761,7 +793,7 @@ extern "C" int ssm_gemm_bf16_fused(const void* A, const void* B, void* C, int M,
   p.c32 = (mode == 1 || mode == 2) ? reinterpret_cast<float*>(C) : nullptr;
   p.ldc32 = ldc; p.status = status; p.tiles_m = 0; p.tiles_n = 0; p.gemm_ctas = 0;
   p.c16 = mode == 0 ? reinterpret_cast<__nv_bfloat16*>(C) : nullptr;
-  p.ldc16 = ldc; p.direct = epilogue_direct(); p.trace = g_trace; p.prefetch = gemm_prefetch_distance();
+  p.ldc16 = ldc; p.direct = epilogue_direct(); p.trace = g_trace; p.prefetch = gemm_prefetch_distance(); p.sumsq = nullptr;
   if (BN == 256) return launch_gemm<256, 4>(ta, tb, tc, p, stream, &cm, &maps);
   if (BN == 192) return launch_gemm<192, 4>(ta, tb, tc, p, stream, &cm, &maps);
   return launch_gemm<128, 6>(ta, tb, tc, p, stream, &cm, &maps);

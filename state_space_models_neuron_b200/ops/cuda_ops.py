@@ -103,9 +103,10 @@ def _as_operand(t: torch.Tensor) -> torch.Tensor:
 
 def gemm(a: torch.Tensor, b: torch.Tensor, a_mn: bool = False, b_mn: bool = False, out: Optional[torch.Tensor] = None,
          out_dtype=torch.bfloat16, accumulate: bool = False, bias: Optional[torch.Tensor] = None,
-         gelu: bool = False) -> torch.Tensor:
+         gelu: bool = False, sumsq: Optional[torch.Tensor] = None) -> torch.Tensor:
     """C[M,N] = A B on tcgen05.  a is [M,K] (or [K,M] when a_mn), b is [N,K] (or [K,N] when b_mn).
-    out: bf16 (fresh, row stride padded to 8) or fp32 (`accumulate` adds into `out`)."""
+    out: bf16 (fresh, row stride padded to 8) or fp32 (`accumulate` adds into `out`).
+    sumsq (fp32 scalar tensor, fp32 store only): the kernel adds sum(C^2) to it."""
     _require_bf16(a, b, bias)
     a, b = _as_operand(a), _as_operand(b)
     M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
@@ -119,7 +120,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, a_mn: bool = False, b_mn: bool = Fals
             out = torch.empty(M, (N + 3) // 4 * 4, dtype=torch.float32, device=a.device)[:, :N]
     if out.dtype == torch.float32 and (out.stride(0) % 4 or out.data_ptr() % 16) and out.stride(1) == 1:
         # TMA needs 16-byte aligned rows: go through a padded temporary
-        tmp = gemm(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
+        tmp = gemm(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32, sumsq=sumsq)
         if accumulate:
             out.add_(tmp)
         else:
@@ -133,9 +134,42 @@ def gemm(a: torch.Tensor, b: torch.Tensor, a_mn: bool = False, b_mn: bool = Fals
         mode = 2 if accumulate else 1
         if out.stride(1) != 1:
             raise ValueError("fp32 GEMM output needs unit inner stride")
+    if sumsq is not None:
+        if mode != 1 or sumsq.dtype != torch.float32:
+            raise ValueError("sumsq needs an fp32 output that is stored, not accumulated")
+        _run("ssm_gemm_bf16_ex", _p(a), _p(b), _p(out), M, N, K, _ll(a.stride(0)), _ll(b.stride(0)), _ll(out.stride(0)),
+             int(a_mn), int(b_mn), mode, _p(bias), int(gelu), _p(status_tensor(a.device)), _st(), _p(sumsq))
+        return out
     _run("ssm_gemm_bf16", _p(a), _p(b), _p(out), M, N, K, _ll(a.stride(0)), _ll(b.stride(0)), _ll(out.stride(0)),
          int(a_mn), int(b_mn), mode, _p(bias), int(gelu), _p(status_tensor(a.device)), _st())
     return out
+
+
+def wgrad_to_main_grad(dy2: torch.Tensor, x2: torch.Tensor, w) -> bool:
+    """dW = dY^T X written straight into the optimizer's fp32 `w.main_grad`: stored on the first contribution of a
+    step (lazy zeroing), added afterwards.  When the optimizer has given the weight a norm accumulator (`w.norm_acc`)
+    a stored gradient also adds its sum of squares to it (`w.norm_tracked` tells the optimizer that this weight's
+    share of the gradient norm is already there).  False: no fp32 main_grad, the caller returns dW through autograd."""
+    mg = getattr(w, "main_grad", None)
+    if mg is None or mg.dtype != torch.float32:
+        return False
+    stale = getattr(w, "grad_stale", False)
+    acc = getattr(w, "norm_acc", None) if stale else None
+    if not stale:
+        untrack_norm(w)
+    gemm(dy2, x2, a_mn=True, b_mn=True, out=mg, accumulate=not stale, sumsq=acc)
+    w.grad_stale = False
+    if acc is not None:
+        w.norm_tracked = True
+    return True
+
+
+def untrack_norm(w) -> None:
+    """The gradient of `w` is about to change after a GEMM may already have added its sum of squares to the norm
+    accumulator: mark the weight so that the optimizer recomputes the norm from the buffers this step."""
+    if getattr(w, "norm_tracked", False):
+        w.norm_tracked = False
+        w.norm_dirty = True
 
 
 class _Linear(torch.autograd.Function):
@@ -158,12 +192,7 @@ class _Linear(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = gemm(dy2, w, b_mn=True).reshape(ctx.xshape)          # dX = dY W
         if ctx.needs_input_grad[1]:
-            mg = getattr(w, "main_grad", None)
-            if mg is not None and mg.dtype == torch.float32:
-                stale = getattr(w, "grad_stale", False)                        # first contribution: plain store
-                gemm(dy2, x2, a_mn=True, b_mn=True, out=mg, accumulate=not stale)   # main_grad (+)= dY^T X
-                w.grad_stale = False
-            else:
+            if not wgrad_to_main_grad(dy2, x2, w):                       # main_grad (+)= dY^T X
                 dw = gemm(dy2, x2, a_mn=True, b_mn=True)
                 if not dw.is_contiguous():
                     dw = dw.contiguous()
@@ -382,6 +411,7 @@ def embed_grad_target(w):
         if getattr(w, "grad_stale", False):
             mg.zero_()
             w.grad_stale = False
+        untrack_norm(w)                 # scatter-added rows change the norm of a gradient a GEMM may have stored
         return mg, True
     return torch.zeros(w.shape, dtype=torch.float32, device=w.device), False
 

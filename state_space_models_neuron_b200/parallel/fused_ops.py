@@ -234,12 +234,7 @@ class _AllGatherLinear(torch.autograd.Function):
             dx = _gemm_rs(dy2, w, True, ws)         # reduce_scatter(dY W)
             dx = dx.reshape(1, dx.shape[0], dx.shape[1])
         if ctx.needs_input_grad[1]:
-            mg = getattr(w, "main_grad", None)
-            if mg is not None and mg.dtype == torch.float32:
-                stale = getattr(w, "grad_stale", False)
-                cuda_ops.gemm(dy2, xg, a_mn=True, b_mn=True, out=mg, accumulate=not stale)
-                w.grad_stale = False
-            else:
+            if not cuda_ops.wgrad_to_main_grad(dy2, xg, w):
                 dw = cuda_ops.gemm(dy2, xg, a_mn=True, b_mn=True).contiguous()
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = dy2.float().sum(0).to(dy.dtype)
@@ -279,11 +274,7 @@ class _AllGatherMultiLinear(torch.autograd.Function):
                 dws.append(None)
                 continue
             d = d if d.stride(1) == 1 and d.stride(0) % 8 == 0 else d.contiguous()
-            mg = getattr(w, "main_grad", None)
-            if mg is not None and mg.dtype == torch.float32:
-                stale = getattr(w, "grad_stale", False)
-                cuda_ops.gemm(d, xg, a_mn=True, b_mn=True, out=mg, accumulate=not stale)
-                w.grad_stale = False
+            if cuda_ops.wgrad_to_main_grad(d, xg, w):
                 dws.append(None)
             else:
                 dws.append(cuda_ops.gemm(d, xg, a_mn=True, b_mn=True).contiguous())
@@ -308,12 +299,7 @@ class _LinearReduceScatter(torch.autograd.Function):
         dyg, dx = _ag_gemm(dy.reshape(Ls, N), w, True, None, ws)      # all_gather(dY) W
         dw = None
         if ctx.needs_input_grad[1]:
-            mg = getattr(w, "main_grad", None)
-            if mg is not None and mg.dtype == torch.float32:
-                stale = getattr(w, "grad_stale", False)
-                cuda_ops.gemm(dyg, x2, a_mn=True, b_mn=True, out=mg, accumulate=not stale)
-                w.grad_stale = False
-            else:
+            if not cuda_ops.wgrad_to_main_grad(dyg, x2, w):
                 dw = cuda_ops.gemm(dyg, x2, a_mn=True, b_mn=True).contiguous()
         return dx.reshape(1, dx.shape[0], dx.shape[1]), dw, None
 

@@ -340,6 +340,9 @@ class ParallelEmbedding(nn.Module):
         (init_method or normal_init(1.0))(full, generator=gen)
         self.weight = nn.Parameter(full[self.vocab_start:self.vocab_end].to(dtype).contiguous())
         _mark(self.weight, 0)
+        # the embedding gradient is scatter-added (and, when tied, lands on top of the LM head's): its share of the
+        # gradient norm is always taken from the buffer, never from a GEMM epilogue
+        self.weight.no_norm_tracking = True
 
     def forward(self, ids: torch.Tensor, scatter_to_sequence_parallel: bool = False) -> torch.Tensor:
         tp = ps.get_tensor_model_parallel_size()

@@ -15,6 +15,7 @@ kernel per segment on GPUs (`ops/csrc/optim.cu`) and as torch ops on CPU.
 from __future__ import annotations
 
 import math
+import os
 from typing import Dict, Iterable, List, Optional, Tuple
 
 import torch
@@ -131,6 +132,7 @@ class Zero1Optimizer(torch.optim.Optimizer):
                 segs.append([lo - s, hi - s, gi, rep])
         self.segments = [tuple(x) for x in segs]
         self._norm_buf = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self._setup_norm_tracking()
         # device-resident step counter and per-group learning rates (read by the fused AdamW kernel, so a captured
         # CUDA graph of the step keeps working when the scheduler changes the rate)
         self._dev_step = torch.zeros(1, dtype=torch.int32, device=self.device)
@@ -141,6 +143,8 @@ class Zero1Optimizer(torch.optim.Optimizer):
     @staticmethod
     def _accumulate_hook(p: torch.nn.Parameter) -> None:
         if p.grad is not None:
+            if getattr(p, "norm_tracked", False):
+                p.norm_tracked, p.norm_dirty = False, True
             if getattr(p, "grad_stale", False):
                 p.main_grad.copy_(p.grad)
                 p.grad_stale = False
@@ -157,6 +161,9 @@ class Zero1Optimizer(torch.optim.Optimizer):
         for p, *_ in self.layout:
             p.grad = None
             p.grad_stale = True
+            p.norm_tracked = p.norm_dirty = False
+        if getattr(self, "_norm_acc", None) is not None:
+            self._norm_acc.zero_()
 
     def _finish_lazy_zero(self) -> None:
         for p, *_ in self.layout:
@@ -216,8 +223,64 @@ class Zero1Optimizer(torch.optim.Optimizer):
         self.shard_grad.mul_(1.0 / self.dp_size)
         return self.shard_grad
 
+    def _setup_norm_tracking(self) -> None:
+        """Let the wgrad GEMMs deliver their share of the gradient norm: every tensor-parallel 2-D weight gets a
+        pointer to one fp32 accumulator; a GEMM that STORES the gradient (first contribution of a step) adds its
+        sum of squares there.  Only without data-parallel reduction (the local gradient is the final one) and with
+        fp32 gradients on a GPU.  SSM_B200_FUSED_NORM=0 turns it off."""
+        self._norm_acc = None
+        self._norm_ranges = {}
+        on = (self.device.type == "cuda" and self.dp_size == 1 and self.grad_dtype == torch.float32
+              and os.environ.get("SSM_B200_FUSED_NORM", "1") != "0")
+        if on:
+            from ..ops.functional import _native
+            on = _native(self.flat_grads)
+        if not on:
+            return
+        self._norm_acc = torch.zeros(1, dtype=torch.float32, device=self.device)
+        for p, start, n, gi, rep in self.layout:
+            if p.dim() == 2 and not rep and not getattr(p, "no_norm_tracking", False):
+                p.norm_acc = self._norm_acc
+
+    def _tracked_norm_sq(self, g: torch.Tensor):
+        """Gradient norm^2 from the GEMM epilogues plus one multi-range pass over everything they did not cover;
+        None when tracking is off or a tracked gradient was modified after its GEMM (then the full pass runs)."""
+        if self._norm_acc is None or g is not self.flat_grads:
+            return None
+        if any(getattr(p, "norm_dirty", False) for p, *_ in self.layout):
+            return None
+        key = tuple(bool(getattr(p, "norm_tracked", False)) for p, *_ in self.layout)
+        if not any(key):
+            return None
+        if key not in self._norm_ranges:
+            spans = []
+            for (p, start, n, gi, rep), tracked in zip(self.layout, key):
+                if tracked or (rep and self.tp_rank != 0):
+                    continue
+                lo, hi = start, start + _ceil_to(n, _ALIGN)
+                if spans and spans[-1][1] == lo:
+                    spans[-1][1] = hi
+                else:
+                    spans.append([lo, hi])
+            flat = [v for sp in spans for v in sp]
+            self._norm_ranges[key] = (torch.tensor(flat, dtype=torch.int64, device=self.device), len(spans))
+        ranges, n = self._norm_ranges[key]
+        total = self._norm_buf.zero_()
+        total += self._norm_acc
+        if n:
+            from ..ops import cuda_ops
+            cuda_ops._run("ssm_sumsq_ranges", cuda_ops._P(g), cuda_ops._P(ranges), n, cuda_ops._P(total), cuda_ops._st())
+        return total
+
     def _grad_norm_sq(self, g: torch.Tensor) -> torch.Tensor:
         """Sum of squares over all distinct gradient elements of the whole model."""
+        total = self._tracked_norm_sq(g)
+        if total is not None:
+            if self.tp_size > 1:
+                from . import fused
+                if not fused.small_allreduce(total, "sum"):
+                    dist.all_reduce(total, group=self.tp_group)
+            return total
         total = self._norm_buf.zero_()
         for lo, hi, gi, rep in self.segments:
             if rep and self.tp_rank != 0:

@@ -373,3 +373,37 @@ def test_bounded_flag_wait_reports_timeout():
     torch.cuda.synchronize()
     cuda_ops.check_status()
     _close(out, a.float() @ a.float().t(), atol=0.5, rtol=2e-2)
+
+
+def test_gradient_norm_from_wgrad_epilogues():
+    """The optimizer takes the 2-D weights' share of the gradient norm from the wgrad GEMM epilogues and the rest
+    from one multi-range pass; the result equals the norm computed from the gradient buffers, also on the second
+    step (accumulator reset) and with gradient accumulation (falls back to the full pass)."""
+    from state_space_models_neuron_b200 import parallel as nxd
+    from state_space_models_neuron_b200.models import Mamba2Config, Mamba2ForCausalLM
+    from state_space_models_neuron_b200.parallel import state as ps
+    ps.initialize_model_parallel(1)
+    cfg = nxd.parallel_config(1, {"zero_one_enabled": True, "grad_clipping": True, "max_grad_norm": 1.0})
+    mc = Mamba2Config(num_heads=8, head_dim=64, vocab_size=1024, hidden_size=256, state_size=128, num_hidden_layers=2,
+                      n_groups=1, tie_word_embeddings=True, initializer_range=0.02, dtype=torch.bfloat16)
+    model = nxd.initialize_parallel_model(cfg, lambda: Mamba2ForCausalLM(mc, device="cuda").to(torch.bfloat16))
+    opt = nxd.initialize_parallel_optimizer(cfg, nxd.AdamW_FP32OptimParams,
+                                            [{"params": list(model.parameters()), "weight_decay": 0.1}], lr=1e-3)
+    assert opt._norm_acc is not None
+    params = list({id(p): p for p in model.parameters()}.values())
+    ids = torch.randint(0, 1024, (2, 256), device="cuda")
+
+    def ref_norm():
+        return torch.sqrt(sum((p.main_grad.double() ** 2).sum() for p in params)).item()
+
+    for micro_steps in (1, 1, 2):
+        opt.zero_grad()
+        for _ in range(micro_steps):
+            model(input_ids=ids, labels=ids, return_logits=False).loss.backward()
+        tracked = sum(bool(getattr(p, "norm_tracked", False)) for p in params)
+        dirty = any(getattr(p, "norm_dirty", False) for p in params)
+        assert (tracked > 0 and not dirty) if micro_steps == 1 else dirty
+        want = ref_norm()
+        opt.step()
+        got = float(opt.last_grad_norm)
+        assert abs(got - want) <= 2e-4 * want, (micro_steps, got, want)
