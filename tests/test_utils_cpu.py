@@ -1,0 +1,98 @@
+"""Data pipeline, logging / MFU arithmetic, debug helpers and profiling command builders (CPU only)."""
+import json
+import os
+import tempfile
+
+import numpy as np
+import pytest
+import torch
+
+
+def test_pack_token_lists_and_token_array_dataset_round_trip():
+    from state_space_models_neuron_b200.utils.data import TokenArrayDataset, create_pretraining_dataset, pack_token_lists
+    docs = [[1, 2, 3], [4, 5, 6, 7, 8], [9], [10, 11, 12]]
+    packed = pack_token_lists(docs, 4)
+    assert packed.tolist() == [[1, 2, 3, 4], [5, 6, 7, 8], [9, 10, 11, 12]] and packed.dtype == np.int32
+    with tempfile.TemporaryDirectory() as d:
+        np.save(os.path.join(d, "tokens.npy"), packed)
+        ds = TokenArrayDataset(d)
+        assert len(ds) == 3 and ds[1]["input_ids"].tolist() == [5, 6, 7, 8] and ds[1]["labels"].dtype == torch.int64
+        # two data-parallel ranks see disjoint samples in a fixed order
+        seen = []
+        for rank in range(2):
+            loader, sampler = create_pretraining_dataset(d, 1, 2, rank, seed=0)
+            seen.append([b["input_ids"][0].tolist() for b in loader])
+        assert seen[0] == [[1, 2, 3, 4]] and seen[1] == [[5, 6, 7, 8]]        # drop_last drops the odd third sample
+
+
+def test_synthetic_dataset_is_deterministic_per_index():
+    from state_space_models_neuron_b200.utils.data import SyntheticDataset
+    a, b = SyntheticDataset(1000, 16, seed=3), SyntheticDataset(1000, 16, seed=3)
+    assert torch.equal(a[5]["input_ids"], b[5]["input_ids"]) and not torch.equal(a[5]["input_ids"], a[6]["input_ids"])
+    assert int(a[5]["input_ids"].max()) < 1000 and torch.equal(a[5]["labels"], a[5]["input_ids"])
+
+
+def test_weight_decay_groups_follow_the_reference_rule():
+    from state_space_models_neuron_b200.models import Mamba2Config, Mamba2ForCausalLM
+    from state_space_models_neuron_b200.parallel import state as ps
+    from state_space_models_neuron_b200.utils.data import get_param_groups_by_weight_decay
+    ps.initialize_model_parallel(1)
+    m = Mamba2ForCausalLM(Mamba2Config(num_heads=4, head_dim=32, vocab_size=64, hidden_size=64, state_size=32,
+                                       num_hidden_layers=1, n_groups=1))
+    decay, no_decay = get_param_groups_by_weight_decay(m, 0.1)
+    names = {id(p): n for n, p in m.named_parameters()}
+    nd = {names[id(p)] for p in no_decay["params"]}
+    assert decay["weight_decay"] == 0.1 and no_decay["weight_decay"] == 0.0
+    assert any(n.endswith("mixer.A_log") for n in nd) and any(n.endswith("mixer.dt_bias") for n in nd)
+    assert any(n.endswith("mixer.norm.weight") for n in nd) and any(n.endswith("conv1d.bias") for n in nd)
+    assert all(not n.endswith("in_proj.weight") and not n.endswith("out_proj.weight") for n in nd)
+
+
+def test_throughput_window_and_mfu_formula():
+    from state_space_models_neuron_b200.utils import logging as lg
+    t = lg.Throughput(batch_size=2, world_size=4, grad_accum_usteps=3, tp_size=8, model="Mamba7B", seq_length=2048,
+                      chip_flops=100.0)
+    assert t.seqs_per_iteration == 24
+    D, layers, N, L = 4096, 64, 128, 2048
+    per_layer = 12 * L * D ** 2 + 8 * L * D + 2 * L * N * D
+    want = 3 * per_layer * layers * (2 * 3) / 1e12 / (100.0 * 8)     # fwd + bwd = 3x, per-DP-rank batch, flops of TP chips
+    assert abs(t.MFU_factor - want) / want < 1e-12
+    step_time, seqs_per_s, mfu = t.get_throughput()
+    assert step_time > 0 and abs(seqs_per_s - 24 / step_time) < 1e-6 and abs(mfu - want / step_time) < 1e-9
+
+
+def test_training_metrics_store_round_trip():
+    from state_space_models_neuron_b200.utils.logging import TrainingMetrics
+    with tempfile.TemporaryDirectory() as d:
+        f = os.path.join(d, "m.json")
+        m = TrainingMetrics(f)
+        m.update(loss=1.5, step=3)
+        m.store_parameters(lr=1e-3, model="Mamba130M")
+        again = TrainingMetrics(f)
+        assert again.data["metrics"] == {"loss": 1.5, "step": 3} and again.data["parameters"]["model"] == "Mamba130M"
+        assert json.load(open(f))["parameters"]["lr"] == "0.001"
+
+
+def test_debug_helpers():
+    from state_space_models_neuron_b200.utils import debug
+    buf = debug.CanaryBuffer((4, 8), torch.float32, "cpu", guard_bytes=64)
+    buf.tensor.fill_(1.0)
+    assert buf.intact()
+    buf.raw[10] = 0                     # a write before the tensor is detected
+    assert not buf.intact()
+    debug.assert_deterministic(lambda x: x * 2, [torch.ones(3)])
+    with pytest.raises(AssertionError):
+        debug.assert_deterministic(lambda x: x + torch.rand(3), [torch.ones(3)])
+    with pytest.raises(FloatingPointError):
+        debug.check_finite(torch.tensor([1.0, float("nan")]), "t")
+    # the GEMM's rotated tile order still visits every tile once, for the all-gather and reduce-scatter rotations
+    assert debug.tile_schedule_is_permutation(16, 10, 8, 132) and debug.tile_schedule_is_permutation(16, 16, 2, 148)
+
+
+def test_ncu_command_always_leaves_clocks_alone():
+    from state_space_models_neuron_b200.utils.profiling import ncu_command
+    cmd = ncu_command(["python", "bench.py", "--small"], "gemm_bf16", launches=2, skip=1, out="x/prof")
+    assert cmd[:3] == ["ncu", "--clock-control", "none"] and cmd[-3:] == ["python", "bench.py", "--small"]
+    assert "regex:gemm_bf16" in cmd and cmd[cmd.index("-c") + 1] == "2" and cmd[cmd.index("-s") + 1] == "1"
+    light = ncu_command(["python", "x.py"], None, full=False)
+    assert "gpu__time_duration.sum" in light and "--set" not in light
