@@ -616,6 +616,9 @@ static int pick_tile_n(int M, int N) {
     const long long t = tm * ((N + bn - 1) / bn);
     return (double)((t + sms - 1) / sms) * tile_cost;
   };
+  // fewer 128-wide tiles than SMs (decode-time GEMMs with a handful of rows, thin per-rank projections): every CTA
+  // is bound by its own operand stream, so the tiling with the most CTAs wins
+  if (tm * ((N + 127) / 128) <= sms) return 128;
   const double c256 = cost(256, 1.0), c192 = cost(192, 0.8), c128 = cost(128, 0.8);
   int best = 256;
   double cb = c256;
