@@ -34,7 +34,7 @@ SMALL = dict(name="Mamba2-tiny", hidden_size=512, num_hidden_layers=4, head_dim=
 def reference_arm():
     print(json.dumps({"impl": "reference", "unavailable":
                       "reference is Trainium-only (imports neuronx_distributed/torch_xla/neuronxcc NKI, asserts an XLA "
-                      "device) and has no setup.py/pyproject.toml: pip install of /root/reference fails, nothing to run on B200"}))
+                      "device) and has no setup.py/pyproject.toml: pip install of the reference tree fails, nothing to run on B200"}))
 
 
 class ClockSampler(threading.Thread):

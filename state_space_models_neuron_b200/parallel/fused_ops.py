@@ -17,6 +17,7 @@ multiple of 128).
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -24,8 +25,6 @@ from . import state as ps
 from . import symm
 from ..ops import cuda_ops
 from ..ops.cuda_ops import _P, _ceil8, _ll, _run, _st, status_tensor
-
-import os
 
 # CTAs of the all-gather GEMM that only push the local shard to the peers.  0 (default): every CTA pushes a slice
 # first and then computes tiles; N > 0: N dedicated CTAs push while the others start on the local shard's tiles.

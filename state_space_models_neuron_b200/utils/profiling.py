@@ -85,7 +85,7 @@ class StepProfiler:
         self.prof.step()
 
 
-def ncu_command(cmd: List[str], kernel: Optional[str], launches: int = 3, skip: int = 0, out: str = "gpurun_out/prof",
+def ncu_command(cmd: List[str], kernel: Optional[str], launches: int = 3, skip: int = 0, out: str = "profiles_raw/prof",
                 full: bool = True) -> List[str]:
     """`ncu` invocation for one kernel of a small case; always with `--clock-control none`."""
     base = ["ncu", "--clock-control", "none"]
@@ -118,7 +118,7 @@ def main(argv=None):
     a.add_argument("--kernel", default=None)
     a.add_argument("--launches", type=int, default=3)
     a.add_argument("--skip", type=int, default=0)
-    a.add_argument("--out", default="gpurun_out/prof")
+    a.add_argument("--out", default="profiles_raw/prof")
     a.add_argument("--run", action="store_true")
     a.add_argument("rest", nargs=argparse.REMAINDER)
     b = sub.add_parser("summarize")
