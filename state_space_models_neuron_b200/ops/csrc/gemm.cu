@@ -17,7 +17,7 @@ namespace ssm {
 
 constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 224;                       // warp 0: TMA (A), 1: MMA, 2-5: epilogue, 6: TMA (B) when dual
 constexpr int EPI_BLOCK_COLS = 64;                       // bf16 columns per TMA store block (128 bytes)
 constexpr int EPI_BUF_BYTES = GEMM_BM * EPI_BLOCK_COLS * 2;  // 16 KiB
 
@@ -32,6 +32,7 @@ struct GemmParams {
   __nv_bfloat16* c16;    // mode 0 (direct-store epilogue)
   long long ldc16;
   float* sumsq;          // mode 1 only: += sum of squares of every stored element (gradient-norm contribution)
+  int dual;              // 1: two producer warps, one issues the A loads and one the B loads of every stage
   int prefetch;          // k-blocks that the TMA producer prefetches into L2 ahead of its loads (0 = off)
   unsigned long long* trace;   // optional [grid][16] timestamps (ns) for pipeline analysis, else null
   int direct;            // 1: epilogue warps store their rows straight from registers (no smem staging / TMA store)
@@ -197,7 +198,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   }
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], p.dual ? 2 : 1); mbar_init(&empty_bar[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], 4); }
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
@@ -213,8 +214,13 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   const uint32_t tmem_base = *tmem_slot;
   if (threadIdx.x == 0) trace_mark(p, 0);
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
+  if (warp == 0 || (warp == 6 && p.dual)) {
+    // ------------------------------------------------------------------ TMA producer(s)
+    // One thread issuing every load of a stage is a bottleneck of its own: a tensor-map copy takes that thread a few
+    // hundred cycles to issue, and a stage needs 2 (K-major operands) to 6 (MN-major) of them.  With `dual` warp 0
+    // issues the A loads and warp 6 the B loads; both arm the same full barrier (two arrivals) with their byte counts.
+    const bool do_a = warp == 0, do_b = warp == 6 || !p.dual;
+    const uint32_t tx_bytes = (do_a ? L::A_BYTES : 0) + (do_b ? L::B_BYTES : 0);
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0;
       int armed[STAGES];
@@ -237,7 +243,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           }
         }
         for (int kb = 0; kb < kblocks; ++kb) {
-          if (p.prefetch > 0) {
+          if (p.prefetch > 0 && !p.dual) {
             // L2 prefetch of the operand tiles this CTA will load `prefetch` k-blocks from now (possibly in its next
             // tile): the ring of STAGES loads then completes at L2 latency instead of HBM latency
             int pk = kb + p.prefetch, ptile = tile;
@@ -261,27 +267,31 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status)) { ok = false; break; }
           uint8_t* sa = smem + stage * L::STAGE_BYTES;
           uint8_t* sb = sa + L::A_BYTES;
-          mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
+          mbar_expect_tx(&full_bar[stage], tx_bytes);
           armed[stage] = (int)phase;
           const int k0 = kb * GEMM_BK;
-          if (!p.a_mn) {
-            tma_load_2d(sa, &tmap_a, k0, m0, &full_bar[stage]);                 // box {64 k, 128 m}
-          } else {
-            tma_load_2d(sa, &tmap_a, m0, k0, &full_bar[stage]);                 // box {64 m, 64 k} x 2
-            tma_load_2d(sa + 8192, &tmap_a, m0 + 64, k0, &full_bar[stage]);
+          if (do_a) {
+            if (!p.a_mn) {
+              tma_load_2d(sa, &tmap_a, k0, m0, &full_bar[stage]);                 // box {64 k, 128 m}
+            } else {
+              tma_load_2d(sa, &tmap_a, m0, k0, &full_bar[stage]);                 // box {64 m, 64 k} x 2
+              tma_load_2d(sa + 8192, &tmap_a, m0 + 64, k0, &full_bar[stage]);
+            }
           }
-          if (!p.b_mn) {
-            tma_load_2d(sb, &tmap_b, k0, n0, &full_bar[stage]);                 // box {64 k, BN n}
-          } else {
-            #pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(sb + j * 8192, &tmap_b, n0 + 64 * j, k0, &full_bar[stage]);  // box {64 n, 64 k}
+          if (do_b) {
+            if (!p.b_mn) {
+              tma_load_2d(sb, &tmap_b, k0, n0, &full_bar[stage]);                 // box {64 k, BN n}
+            } else {
+              #pragma unroll
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_2d(sb + j * 8192, &tmap_b, n0 + 64 * j, k0, &full_bar[stage]);  // box {64 n, 64 k}
+            }
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
-          if (tile == (int)blockIdx.x && kb == 0) trace_mark(p, 8);
+          if (do_a && tile == (int)blockIdx.x && kb == 0) trace_mark(p, 8);
         }
       }
-      trace_mark(p, 9);
+      if (do_a) trace_mark(p, 9);
       if (!ok) {
         // error path: let copies that are still in flight land before the CTA's shared memory goes away
         #pragma unroll
@@ -324,7 +334,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       }
     }
     __syncwarp();
-  } else {
+  } else if (warp >= 2 && warp < 6) {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;                        // TMEM lane quarter this warp may access
     const int epi_tid = threadIdx.x - 64;          // 0..127
@@ -577,6 +587,16 @@ static int g_num_sms = 0;
 // most for the fp32 gradient outputs; kept for experiments).
 static unsigned long long* g_trace = nullptr;
 
+// SSM_GEMM_DUAL=0 goes back to one producer thread for all loads of a stage.
+static int gemm_dual_producers() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("SSM_GEMM_DUAL");
+    v = (e && atoi(e) == 0) ? 0 : 1;
+  }
+  return v;
+}
+
 // SSM_GEMM_PREFETCH=n: the producer prefetches operand tiles n k-blocks ahead into L2 (0 = off).
 static int gemm_prefetch_distance() {
   static int v = -1;
@@ -714,6 +734,7 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
   p.ldc32 = ldc; p.status = status; p.tiles_m = 0; p.tiles_n = 0; p.gemm_ctas = 0;
   p.c16 = mode == 0 ? reinterpret_cast<__nv_bfloat16*>(C) : nullptr;
   p.ldc16 = ldc; p.direct = epilogue_direct(); p.trace = g_trace; p.prefetch = gemm_prefetch_distance(); p.sumsq = sumsq;
+  p.dual = gemm_dual_producers();
   if (sumsq != nullptr) p.direct = 0;      // the sum of squares is formed in the staged (TMA-store) epilogue
   if (BN == 256) return launch_gemm<256, 4>(ta, tb, tc, p, stream);
   if (BN == 192) return launch_gemm<192, 4>(ta, tb, tc, p, stream);
@@ -797,6 +818,7 @@ extern "C" int ssm_gemm_bf16_fused(const void* A, const void* B, void* C, int M,
   p.ldc32 = ldc; p.status = status; p.tiles_m = 0; p.tiles_n = 0; p.gemm_ctas = 0;
   p.c16 = mode == 0 ? reinterpret_cast<__nv_bfloat16*>(C) : nullptr;
   p.ldc16 = ldc; p.direct = epilogue_direct(); p.trace = g_trace; p.prefetch = gemm_prefetch_distance(); p.sumsq = nullptr;
+  p.dual = 0;      // the fused variants keep the single producer that their flag protocol was validated with
   if (BN == 256) return launch_gemm<256, 4>(ta, tb, tc, p, stream, &cm, &maps);
   if (BN == 192) return launch_gemm<192, 4>(ta, tb, tc, p, stream, &cm, &maps);
   return launch_gemm<128, 6>(ta, tb, tc, p, stream, &cm, &maps);
