@@ -259,6 +259,30 @@ class Mamba2ForCausalLM(Mamba2PreTrainedModel, GenerationMixin):
         return self.lm_head(out.last_hidden_state[:, -1:, :]).float(), cache_params
 
     @torch.no_grad()
+    def generate(self, inputs=None, max_new_tokens: Optional[int] = None, max_length: Optional[int] = None,
+                 do_sample: bool = False, temperature: float = 1.0, top_k: Optional[int] = None,
+                 eos_token_id: Optional[int] = None, input_ids=None, generator=None, **unused):
+        """`GenerationMixin.generate`-style entry point on top of `generate_tokens` (the framework's own conv/SSM
+        cache drives decoding; HuggingFace's generic loop would hand the model a KV cache object it cannot use).
+        Supports greedy decoding and temperature / top-k sampling; other generation options are not implemented."""
+        ids = inputs if inputs is not None else input_ids
+        if ids is None:
+            raise ValueError("generate() needs input ids")
+        if unused:
+            ignored = sorted(k for k in unused if unused[k] is not None)
+            if ignored:
+                import logging
+                logging.getLogger(__name__).warning("generate(): ignoring unsupported options %s", ignored)
+        if max_new_tokens is None:
+            max_new_tokens = max(0, (max_length or ids.shape[1] + 20) - ids.shape[1])
+        if eos_token_id is None:
+            eos_token_id = getattr(self.generation_config, "eos_token_id", None) if hasattr(self, "generation_config") else None
+            if isinstance(eos_token_id, (list, tuple)):
+                eos_token_id = eos_token_id[0] if eos_token_id else None
+        return self.generate_tokens(ids, max_new_tokens, temperature=temperature if do_sample else 0.0, top_k=top_k,
+                                    eos_token_id=eos_token_id, generator=generator)
+
+    @torch.no_grad()
     def generate_tokens(self, input_ids, max_new_tokens: int, temperature: float = 0.0, top_k: Optional[int] = None,
                         eos_token_id: Optional[int] = None, generator=None):
         """Prompt -> continuation with the cached decode path: the longest 128-multiple prefix of the prompt goes

@@ -135,3 +135,20 @@ def test_generate_tokens_matches_full_forward_greedy():
         for t in range(150):
             ref = model.step(ids[:, t:t + 1], cache)
     assert torch.equal(out[:, 150], ref[:, -1].argmax(-1))
+
+
+def test_hf_style_generate_uses_the_cached_decode_path():
+    """`model.generate(...)` (HuggingFace calling convention) gives the same tokens as `generate_tokens`."""
+    from state_space_models_neuron_b200.models import Mamba2Config, Mamba2ForCausalLM
+    from state_space_models_neuron_b200.parallel import state as ps
+    ps.initialize_model_parallel(1)
+    torch.manual_seed(0)
+    m = Mamba2ForCausalLM(Mamba2Config(num_heads=4, head_dim=32, vocab_size=64, hidden_size=64, state_size=32,
+                                       num_hidden_layers=2, n_groups=1)).eval()
+    ids = torch.randint(1, 64, (2, 130))
+    want = m.generate_tokens(ids, 5)
+    assert torch.equal(m.generate(ids, max_new_tokens=5, do_sample=False, eos_token_id=-1), want)
+    assert torch.equal(m.generate(input_ids=ids, max_length=135, eos_token_id=-1), want)
+    sampled = m.generate(ids, max_new_tokens=3, do_sample=True, temperature=0.7, top_k=4, eos_token_id=-1,
+                         generator=torch.Generator().manual_seed(1))
+    assert sampled.shape == (2, 133) and torch.equal(sampled[:, :130], ids)
