@@ -95,6 +95,8 @@ class Mamba2PreTrainedModel(PreTrainedModel):
     config_class = Mamba2Config
     base_model_prefix = "backbone"
     _no_split_modules = ["Mamba2Block"]
+    # per-head SSM parameters are created in fp32 whatever the model dtype: loading must not round them
+    _keep_in_fp32_modules_strict = ["dt_bias", "A_log", "D"]
     supports_gradient_checkpointing = False
     _is_stateful = True
 

@@ -119,3 +119,30 @@ def test_presets_and_allocation_match_reference():
         h.save_pretrained(d)
         back = Mamba2HybridConfig.from_pretrained(d)
         assert back.hybrid_attention_ratio == 0.08 and back.model_type == "mamba2hybrid"
+
+
+@pytest.mark.parametrize("hybrid", [False, True])
+def test_save_pretrained_from_pretrained_round_trip_keeps_values_and_dtypes(hybrid):
+    """HuggingFace save/load of a bf16 model restores every tensor exactly; the fp32 per-head SSM parameters
+    (dt_bias, A_log, D) are not rounded to the model dtype on the way."""
+    import tempfile
+    from state_space_models_neuron_b200.models import (Mamba2Config, Mamba2ForCausalLM, Mamba2HybridConfig,
+                                                       Mamba2HybridForCausalLM)
+    from state_space_models_neuron_b200.parallel import state as ps
+    ps.initialize_model_parallel(1)
+    kw = dict(num_heads=4, head_dim=32, vocab_size=64, hidden_size=64, state_size=32, n_groups=2, dtype=torch.bfloat16)
+    if hybrid:
+        cls, cfg = Mamba2HybridForCausalLM, Mamba2HybridConfig(
+            **kw, num_hidden_layers=4, attn_num_heads=4, attn_head_dim=16, attn_key_value_heads=2, mlp_hidden_size=128,
+            hybrid_attention_ratio=0.25, hybrid_mlp_ratio=0.25)
+    else:
+        cls, cfg = Mamba2ForCausalLM, Mamba2Config(**kw, num_hidden_layers=2)
+    m = cls(cfg).eval()
+    with tempfile.TemporaryDirectory() as d:
+        m.save_pretrained(d)
+        again = cls.from_pretrained(d).eval()
+    a, b = m.state_dict(), again.state_dict()
+    assert a.keys() == b.keys()
+    for k in a:
+        assert a[k].dtype == b[k].dtype and torch.equal(a[k], b[k]), k
+    assert any(v.dtype == torch.float32 for v in b.values()) and any(v.dtype == torch.bfloat16 for v in b.values())
