@@ -1,14 +1,18 @@
-// bf16 GEMM for sm_100a: TMA -> 128B-swizzled shared memory -> tcgen05.mma with fp32 accumulators in
-// TMEM -> epilogue.  Persistent, warp-specialised:
-//     warp 0      TMA producer (one lane)            ring of STAGES {A,B} k-blocks, full/empty mbarriers
-//     warp 1      TMEM allocator + MMA issuer (lane 0), two accumulator buffers (2 x BN columns)
-//     warps 2..5  epilogue: tcgen05.ld -> (+bias, GELU) -> bf16 -> swizzled smem -> TMA store,
-//                 or fp32 direct store / fp32 red.add (gradient accumulation)
+// bf16 GEMM for sm_100a: TMA (no multicast) -> 128B-swizzled smem ring -> tcgen05.mma with fp32 accumulators in
+// TMEM -> epilogue.  Persistent, warp-specialised, 7 warps:
+//     warp 0      TMA producer (one elected thread): the A loads of every stage (all loads in the fused variants)
+//     warp 1      MMA issuer (one elected thread), owns the TMEM allocation
+//     warps 2..5  epilogue: tcgen05.ld -> bf16 (plain, or +bias / GELU) -> swizzled smem -> TMA store,
+//                 or fp32 TMA store / TMA reduce-add for gradient outputs (optionally adding sum(C^2) to a scalar),
+//                 or TMA stores into the peers' landing zones (reduce-scatter)
+//     warp 6      second TMA producer: the B loads of every stage (plain GEMMs)
+// Two accumulator stages in TMEM let the epilogue of tile i overlap the main loop of tile i+1.
+// Tiles 128 x {256, 192, 128} x 64, chosen per problem by wave count.
 // C[M,N] = A * B with A given as [M,K] row-major ("K-major") or [K,M] row-major ("MN-major") and B as
 // [N,K] row-major (K-major) or [K,N] row-major (MN-major); the MN-major forms serve the transposed products
 // of the backward pass (dX = dY W, dW = dY^T X) without any explicit transpose.
-// This is the GEMM behind every Linear layer (the reference leaves those to the XLA compiler:
-// mamba2/mamba2_mixer.py:228,233; mamba2/modeling_mamba2.py:498).
+// Replaces the XLA-compiled `dot` of every Linear layer of the reference (mamba2/mamba2_mixer.py:228,233,
+// mamba2/modeling_mamba2.py:498, mamba2hybrid/mamba2hybrid_attn.py:411-413,463, mamba2hybrid/mamba2hybrid_mlp.py:121,134).
 #include "common.cuh"
 #include <stdlib.h>
 #include <string.h>
