@@ -8,6 +8,11 @@
 //                                      that landed in this rank's landing zone (fp32 accumulate) -> bf16
 //   small all-reduce                   packed fp32 vector (cross-entropy statistics, norm-weight grads):
 //                                      every rank writes its vector into every rank's slot, waits, sums
+//   ZeRO-1                             peer reduce of the owned gradient shard fused with scaling and the norm
+//                                      partial; AdamW on the shard fused with the push of the new bf16 parameters
+//   one-shot bf16 all-reduce           decode-time sum of a [batch, d_model] activation over the TP group
+//   vocabulary-parallel embedding      the rank that holds a token's row stores it into the sequence owner's
+//                                      buffer; backward scatter-adds gathered output gradients in fp32
 // Flag waits are bounded (SSM_WAIT_NS); on time-out the status word is set and the kernel returns.
 // The collectives the reference triggers implicitly through neuronx-distributed are listed with their call
 // sites in mamba2/mamba2_mixer.py:228,233 and mamba2/modeling_mamba2.py:276,300-301,498-510.
