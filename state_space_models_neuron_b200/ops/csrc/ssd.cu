@@ -359,7 +359,7 @@ ssd_chunk_scan_fwd_kernel(const __grid_constant__ CUtensorMap tm_xbc, const __gr
 }
 
 // =====================================================================================
-// backward chunk scan.  grid (nc, G * splits, B), 128 threads, 1 CTA / SM; the CTA walks `hpc` head slices
+// backward chunk scan.  grid (nc, G * splits, B), 256 threads (two warpgroups), 1 CTA / SM; the CTA walks `hpc` head slices
 // of one group.  Given dY and, per chunk, S_in (state entering the chunk) and dS_out (gradient of the state
 // leaving the chunk):
 //   CB = C B^T ; dM = dY X^T ; M0 = CB o Lambda ; dCB = dM o Lambda o dt_j
