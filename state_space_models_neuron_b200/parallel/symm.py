@@ -88,21 +88,30 @@ class SymmWorkspace:
     def fits(self, rows: int, cols: int) -> bool:
         return rows * cols <= self.rows_total * self.cols
 
-    STEP_STRIDE = 1 << 16    # even and larger than the number of fused calls in one training step
+    STEP_STRIDE = 1 << 16    # host positions stay below this; the base is advanced before they reach it
 
     def next_seq(self) -> int:
-        """Position of the next fused call inside the current step (parity selects the double buffers)."""
+        """Position of the next fused call since the last advance (parity selects the double buffers).  Long runs
+        of calls without an optimizer step (gradient accumulation over many micro-steps) advance the base on their
+        own; every rank makes the same calls in the same order, so all ranks do this at the same call."""
+        if self.seq + 1 >= self.STEP_STRIDE - 2:
+            self.advance_step()
         self.seq += 1
-        if self.seq >= self.STEP_STRIDE:
-            raise RuntimeError("too many fused collective calls without advance_step()")
         return self.seq
 
     def advance_step(self) -> None:
-        """Start a new step: bump the device-side base (a kernel on the current stream, so it is captured into
-        CUDA graphs) and restart the host-side position."""
+        """Start a new block of sequence numbers: bump the device-side base by STEP_STRIDE (a kernel on the current
+        stream, so it is captured into CUDA graphs) and restart the host-side position.  The numbers are 31-bit:
+        32767 advances (optimizer steps, plus one per ~65k fused calls under gradient accumulation) fit before
+        they would wrap; a wrap-safe comparison in the waiting kernels is the planned follow-up."""
         from ..ops.cuda_ops import _P, _run, _st
         _run("ssm_advance_counter", _P(self.seq_base), self.STEP_STRIDE, _st())
         self.seq = 0
+        self.advances = getattr(self, "advances", 0) + 1
+        if self.advances == 30000:
+            import warnings
+            warnings.warn("fused-collective sequence numbers are close to their 31-bit limit; restart the job from a "
+                          "checkpoint before ~32000 advances")
 
     def counter_ptr(self, index: int) -> int:
         return self.counters.data_ptr() + 4 * index

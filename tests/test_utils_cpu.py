@@ -96,3 +96,20 @@ def test_ncu_command_always_leaves_clocks_alone():
     assert "regex:gemm_bf16" in cmd and cmd[cmd.index("-c") + 1] == "2" and cmd[cmd.index("-s") + 1] == "1"
     light = ncu_command(["python", "x.py"], None, full=False)
     assert "gpu__time_duration.sum" in light and "--set" not in light
+
+
+def test_fused_sequence_numbers_advance_on_their_own(monkeypatch):
+    """Gradient accumulation makes far more than 65536 fused collective calls between optimizer steps: the
+    workspace starts a new block of sequence numbers by itself instead of failing, at the same call on every rank."""
+    from state_space_models_neuron_b200.ops import cuda_ops
+    from state_space_models_neuron_b200.parallel import symm
+    launched = []
+    monkeypatch.setattr(cuda_ops, "_run", lambda name, *a: launched.append((name, a[1])))
+    monkeypatch.setattr(cuda_ops, "_st", lambda: None)
+    ws = symm.SymmWorkspace.__new__(symm.SymmWorkspace)
+    ws.seq, ws.seq_base = 0, torch.zeros(1, dtype=torch.int32)
+    positions = [ws.next_seq() for _ in range(150000)]
+    assert min(positions) == 1 and max(positions) < symm.SymmWorkspace.STEP_STRIDE
+    assert [n for n, _ in launched] == ["ssm_advance_counter"] * 2 and all(s == symm.SymmWorkspace.STEP_STRIDE for _, s in launched)
+    ws.advance_step()
+    assert ws.seq == 0 and ws.next_seq() == 1
