@@ -65,6 +65,83 @@ class GraphedTrainStep:
         return self.static_loss
 
 
+class GraphedAccumulationStep:
+    """Gradient accumulation with CUDA graphs: three graphs instead of one.
+
+        first    forward + backward of a micro-step right after `zero_grad()` (wgrad GEMMs store)
+        next     forward + backward of every further micro-step (wgrad GEMMs accumulate)
+        update   gradient reduction, clipping, AdamW, `zero_grad()`
+
+    `micro_step(batch)` replays `first` or `next` and returns the micro-step's loss divided by the number of
+    micro-steps (device tensor, overwritten by the next call); after `grad_accum_usteps` micro-steps it replays
+    `update`.  The reference accumulates the same way with eager XLA steps (train.py:178-232).
+    Status: built from the pieces that `GraphedTrainStep` uses and checked for its bookkeeping on the host; it has
+    not been run on a GPU yet."""
+
+    def __init__(self, model, optimizer, example_batch: Dict[str, torch.Tensor], grad_accum_usteps: int,
+                 loss_fn: Optional[Callable] = None, warmup: int = 1):
+        if grad_accum_usteps < 2:
+            raise ValueError("use GraphedTrainStep for grad_accum_usteps == 1")
+        self.model, self.optimizer, self.accum = model, optimizer, grad_accum_usteps
+        self.static = {k: v.clone() for k, v in example_batch.items()}
+        self.loss_fn = loss_fn or (lambda m, b: m(input_ids=b["input_ids"], labels=b["labels"], return_logits=False).loss)
+        self.micro_index = 0
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(warmup):              # real optimizer steps on the example batch (allocator, workspaces)
+                for _ in range(self.accum):
+                    self._micro()
+                self._update()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
+        self.optimizer.upload_learning_rates()
+        pool = torch.cuda.graph_pool_handle()
+        self.g_first, self.g_next, self.g_update = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+        # capture in the order of a real step so that the host-side store/accumulate flags seen by each graph are
+        # the ones it will meet at replay: first (gradients stale) -> next (accumulating) -> update
+        with torch.cuda.graph(self.g_first, pool=pool):
+            self.loss_first = self._micro()
+        with torch.cuda.graph(self.g_next, pool=pool):
+            self.loss_next = self._micro()
+        with torch.cuda.graph(self.g_update, pool=pool):
+            self._update()
+        self.optimizer.step_count -= 1           # capturing recorded an optimizer step without executing it
+        self.eager_steps = warmup
+
+    def _micro(self):
+        loss = self.loss_fn(self.model, self.static) / self.accum
+        loss.backward()
+        # every replay of a micro-step graph must publish fresh sequence numbers for its fused collectives: the
+        # graph ends with a bump of the device-side base by the number of calls it made
+        from . import symm
+        symm.advance_step(compact=True)
+        return loss.detach()
+
+    def _update(self):
+        self.optimizer.step()
+        self.optimizer.zero_grad()
+
+    def micro_step(self, batch: Dict[str, torch.Tensor]) -> torch.Tensor:
+        for k, v in batch.items():
+            self.static[k].copy_(v, non_blocking=True)
+        first = self.micro_index == 0
+        (self.g_first if first else self.g_next).replay()
+        self.micro_index += 1
+        if self.micro_index == self.accum:
+            self.optimizer.upload_learning_rates()
+            self.g_update.replay()
+            self.optimizer.step_count += 1
+            self.micro_index = 0
+        return self.loss_first if first else self.loss_next
+
+    @property
+    def at_step_boundary(self) -> bool:
+        """True right after the micro-step that completed an optimizer step."""
+        return self.micro_index == 0
+
+
 class GraphedDecodeStep:
     """One autoregressive decode step (all layers, LM head, greedy argmax) captured as a CUDA graph.
 

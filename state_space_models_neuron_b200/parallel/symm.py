@@ -99,13 +99,16 @@ class SymmWorkspace:
         self.seq += 1
         return self.seq
 
-    def advance_step(self) -> None:
+    def advance_step(self, compact: bool = False) -> None:
         """Start a new block of sequence numbers: bump the device-side base by STEP_STRIDE (a kernel on the current
         stream, so it is captured into CUDA graphs) and restart the host-side position.  The numbers are 31-bit:
         32767 advances (optimizer steps, plus one per ~65k fused calls under gradient accumulation) fit before
-        they would wrap; a wrap-safe comparison in the waiting kernels is the planned follow-up."""
+        they would wrap; a wrap-safe comparison in the waiting kernels is the planned follow-up.
+        `compact` advances by the number of calls actually made (rounded up to even) instead: for callers that
+        advance very often (one graph replay per micro-step)."""
         from ..ops.cuda_ops import _P, _run, _st
-        _run("ssm_advance_counter", _P(self.seq_base), self.STEP_STRIDE, _st())
+        amount = (self.seq + 2) // 2 * 2 if compact else self.STEP_STRIDE
+        _run("ssm_advance_counter", _P(self.seq_base), amount, _st())
         self.seq = 0
         self.advances = getattr(self, "advances", 0) + 1
         if self.advances == 30000:
@@ -134,9 +137,9 @@ def get_workspace(rows_total: int, cols: int, device) -> Optional[SymmWorkspace]
     return _WS
 
 
-def advance_step() -> None:
+def advance_step(compact: bool = False) -> None:
     if _WS is not None:
-        _WS.advance_step()
+        _WS.advance_step(compact)
 
 
 def reset_workspace() -> None:

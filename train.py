@@ -119,8 +119,8 @@ def run(args):
 
     graphed = None
     if args.cuda_graph:
-        if not use_cuda or args.grad_accum_usteps != 1:
-            raise SystemExit("--cuda_graph needs a CUDA device and --grad_accum_usteps 1")
+        if not use_cuda:
+            raise SystemExit("--cuda_graph needs a CUDA device")
     done = global_step >= args.max_steps
     # a resumed run continues with the batch that the interrupted run would have seen next
     skip_batches = global_step * args.grad_accum_usteps if args.resume else 0
@@ -132,12 +132,20 @@ def run(args):
             training_step += 1
             if args.cuda_graph:
                 if graphed is None:
-                    from state_space_models_neuron_b200.parallel.graph import GraphedTrainStep
-                    graphed = GraphedTrainStep(model, optimizer, data, warmup=2)
+                    from state_space_models_neuron_b200.parallel.graph import GraphedAccumulationStep, GraphedTrainStep
+                    if args.grad_accum_usteps == 1:
+                        graphed = GraphedTrainStep(model, optimizer, data, warmup=2)
+                    else:       # one graph per kind of micro-step plus one for the update
+                        graphed = GraphedAccumulationStep(model, optimizer, data, args.grad_accum_usteps, warmup=1)
                     global_step += graphed.eager_steps
                     for _ in range(graphed.eager_steps):
                         scheduler.step()
-                running_loss += graphed(data)
+                if args.grad_accum_usteps == 1:
+                    running_loss += graphed(data)
+                else:
+                    running_loss += graphed.micro_step(data)
+                    if not graphed.at_step_boundary:
+                        continue
                 reduced = running_loss / dp_size
                 if dp_size > 1:
                     dist.all_reduce(reduced, group=ps.get_data_parallel_group())
@@ -244,7 +252,9 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--resume", action="store_true", help="also restore optimizer, scheduler and step")
     p.add_argument("--profile", action="store_true")
     p.add_argument("--cuda_graph", action="store_true",
-                   help="capture the whole optimizer step (fwd+bwd+collectives+AdamW) in one CUDA graph and replay it")
+                   help="capture the whole optimizer step (fwd+bwd+collectives+AdamW) in one CUDA graph and replay it; "
+                        "with --grad_accum_usteps > 1: one graph per kind of micro-step plus one for the update "
+                        "(that variant has not been run on a GPU yet)")
     p.add_argument("--device", default=None)
     return p
 
