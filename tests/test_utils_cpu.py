@@ -113,3 +113,29 @@ def test_fused_sequence_numbers_advance_on_their_own(monkeypatch):
     assert [n for n, _ in launched] == ["ssm_advance_counter"] * 2 and all(s == symm.SymmWorkspace.STEP_STRIDE for _, s in launched)
     ws.advance_step()
     assert ws.seq == 0 and ws.next_seq() == 1
+
+
+def test_symmetric_workspace_regions_do_not_overlap():
+    """Byte layout of the peer-mapped workspace: flags, 2 gather buffers, 2 landing zones, small all-reduce slots and
+    2 embedding buffers are disjoint, ordered and inside the allocation, for several TP sizes."""
+    from state_space_models_neuron_b200.parallel import symm
+    for nranks, rows, cols in [(2, 2048, 4096), (8, 2048, 4096), (4, 4096, 4096), (8, 64 * 8, 2560)]:
+        ws = symm.SymmWorkspace.__new__(symm.SymmWorkspace)
+        ws.nranks, ws.rows_total, ws.cols = nranks, rows, cols
+        elems = rows * cols
+        ws.gather_bytes, ws.flags_bytes = elems * 2, 4096
+        ws.slots_bytes = 2 * symm.MAX_RANKS * symm.SMALL_N_MAX * 4
+        ws.embed_bytes = (-(-elems // nranks) * 2 + 255) // 256 * 256
+        total = ws.flags_bytes + 4 * ws.gather_bytes + ws.slots_bytes + 2 * ws.embed_bytes
+        regions = [(0, ws.flags_bytes)]
+        regions += [(ws.gather_offset(p), ws.gather_bytes) for p in (0, 1)]
+        regions += [(ws.land_offset(p), ws.gather_bytes) for p in (0, 1)]
+        regions += [(ws.slots_offset(p), symm.MAX_RANKS * symm.SMALL_N_MAX * 4) for p in (0, 1)]
+        regions += [(ws.embed_offset(p), ws.embed_bytes) for p in (0, 1)]
+        end = 0
+        for off, size in regions:
+            assert off >= end and off % 16 == 0, (nranks, off, end)
+            end = off + size
+        assert end <= total
+        # flag words of the four kinds x two parities x eight sources fit in the flag page
+        assert (symm.KIND_EMB * 2 + 1) * symm.MAX_RANKS + symm.MAX_RANKS <= ws.flags_bytes // 4
