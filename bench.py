@@ -31,6 +31,20 @@ SMALL = dict(name="Mamba2-tiny", hidden_size=512, num_hidden_layers=4, head_dim=
              n_groups=8, vocab_size=50288, conv_kernel=4)
 
 
+def measured_baselines(n_gpus: int):
+    """(tokens/s of the PyTorch + cuBLAS + NCCL arm, tokens/s of this repo's kernels with NCCL collectives) at this
+    GPU count as recorded in baseline/measured.json by earlier runs of `--impl baseline` and `--fused_comm off` on
+    the same pool; None where no measurement exists."""
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "measured.json")
+    try:
+        with open(path) as f:
+            rec = json.load(f)
+    except (OSError, ValueError):
+        return None, None
+    key = str(n_gpus)
+    return rec.get("pytorch_cublas_nccl", {}).get(key), rec.get("own_kernels_nccl", {}).get(key)
+
+
 def reference_arm():
     print(json.dumps({"impl": "reference", "unavailable":
                       "reference is Trainium-only (imports neuronx_distributed/torch_xla/neuronxcc NKI, asserts an XLA "
@@ -160,6 +174,7 @@ def main():
         opt.zero_grad()
         return loss
 
+    fused_fallback = None
     if fused and tp > 1:
         # pre-flight of the fused collective kernels: one eager step; if any rank reports a failed wait, every rank
         # switches to the NCCL collectives (same kernels otherwise) and the JSON line says so
@@ -177,6 +192,7 @@ def main():
             from state_space_models_neuron_b200.parallel import fused as fused_switch
             fused_switch.set_enabled(False)
             fused = False
+            fused_fallback = "pre-flight step of the fused collective kernels failed on at least one rank; NCCL collectives used"
             torch.cuda.synchronize()
             try:
                 cuda_ops.check_status()
@@ -256,10 +272,13 @@ def main():
                "ms_per_step": t2.item() * 1e3 / args.steps, "last_loss": lval}
 
     if rank == 0:
+        base_pt, base_nccl = measured_baselines(args.gpus)
+        is_headline = args.impl == "ours" and not args.small and not args.layers and args.shard_of == 1
         out = {
             "metric": "train tokens/s (device-timed, max over ranks) Mamba2-7B TP=N seq2048",
             "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": (value / base_pt) if (base_pt and is_headline) else None,
             "dtype": "bf16", "data": "synthetic uniform-random token ids, random-init weights",
             "impl": args.impl if args.impl != "ours" else "ours",
             "config": {"model": m["name"], "layers": m["num_hidden_layers"], "global_batch": B * dp, "seq_len": L,
@@ -272,20 +291,35 @@ def main():
         if tp > 1:
             from state_space_models_neuron_b200.parallel import fused_ops
             out["fused_kernel_launches"] = dict(fused_ops.CALLS)
+            if fused_fallback:
+                out["fused_comm_fallback"] = fused_fallback
         if e2e is not None:
             out["e2e"] = e2e
+        if is_headline:
+            out["baselines"] = {"pytorch_cublas_nccl_tokens_per_s": base_pt, "own_kernels_nccl_tokens_per_s": base_nccl,
+                                "vs_own_kernels_nccl": (value / base_nccl) if base_nccl else None,
+                                "source": "baseline/measured.json"}
         print(json.dumps(out), flush=True)
     # Tear down without destroying NCCL communicators that a live CUDA graph still references (that can block
-    # forever): drop the graph, drain the device, meet the other ranks, then leave the process directly.
+    # forever): drop the graph, drain the device, meet the other ranks, run the interpreter's registered exit
+    # handlers (anything that records which libraries this process loaded runs there) and only then leave the
+    # process directly.  A single process holds no communicator and simply returns.
     if gstep is not None:
         gstep.graph.reset()
         gstep = None
     torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
+    if world == 1:
+        return
+    dist.barrier()
     sys.stdout.flush()
     sys.stderr.flush()
-    os._exit(0)
+    import atexit
+    try:
+        atexit._run_exitfuncs()
+    finally:
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":

@@ -22,21 +22,29 @@ from state_space_models_neuron_b200.parallel.layers import set_init_seed
 
 
 def print_stats(name, a, b, atol=1e-3, rtol=3e-2, low_precision=False) -> bool:
-    """fp32 models must satisfy allclose(atol, rtol) (the reference's criterion,
-    mamba2_inference_no_tp.py:22-43); bf16 models accumulate rounding over all layers, so they pass when the
-    mean error stays below 3 % of the logits' standard deviation."""
+    """Two bounds, stated with the result:
+      * fp32 models: `allclose(atol=1e-3, rtol=3e-2)` on every logit, the reference's criterion
+        (mamba2_inference_no_tp.py:22-43).
+      * bf16 models: both paths round every activation of every layer to 8 mantissa bits in a different order, so
+        single logits differ by a few bf16 ulps of the logit scale and an element-wise bound at atol 1e-3 cannot
+        hold by construction.  Enforced instead: mean |error| <= 3 % of the standard deviation of the reference
+        logits AND max |error| <= one standard deviation (greedy-token agreement is printed for information: with
+        random weights many logits are near ties)."""
     a, b = a.float(), b.float()
     err = (a - b).abs()
     rel = err / (b.abs() + 1e-6)
     ok = bool(torch.allclose(a, b, atol=atol, rtol=rtol))
-    if True:
-        # low-precision runs: also report the error relative to the spread of the reference values
-        print(f"{name}: reference std {b.std().item():.3e}, error/std mean {(err.mean() / b.std()).item():.3e}")
     print(f"{name}: max abs {err.max().item():.3e}  mean abs {err.mean().item():.3e}  max rel {rel.max().item():.3e}"
           f"  mean rel {rel.mean().item():.3e}  allclose(atol={atol}, rtol={rtol})={ok}")
-    if low_precision:
-        return bool((err.mean() / b.std()).item() < 3e-2)
-    return ok
+    if not low_precision:
+        return ok
+    std = b.std().item()
+    mean_ratio, max_ratio = err.mean().item() / std, err.max().item() / std
+    agree = (a.argmax(-1) == b.argmax(-1)).float().mean().item()
+    ok_lp = mean_ratio <= 3e-2 and max_ratio <= 1.0
+    print(f"{name}: bf16 bound: reference std {std:.3e}, mean error / std {mean_ratio:.3e} (<= 3e-2), max error / std "
+          f"{max_ratio:.3e} (<= 1.0) -> {ok_lp}; greedy-token agreement {agree:.4f}")
+    return ok_lp
 
 
 def build(args, device):
@@ -144,10 +152,26 @@ def main(argv=None):
     ps.initialize_model_parallel(args.tp)
     device = torch.device(args.device) if args.device else (
         torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu"))
+    def device_status_ok() -> bool:
+        """False if a bounded device-side wait ran out during the run (results would be garbage)."""
+        if device.type != "cuda":
+            return True
+        from state_space_models_neuron_b200.ops import cuda_ops
+        torch.cuda.synchronize()
+        try:
+            cuda_ops.check_status()
+        except RuntimeError as e:
+            print(f"device status check failed: {e}", file=sys.stderr)
+            return False
+        return True
+
     if args.mode == "check":
         ok = check(args, device)
+        ok = device_status_ok() and ok
         sys.exit(0 if ok else 1)
     bench(args, device)
+    if not device_status_ok():
+        sys.exit(2)
 
 
 if __name__ == "__main__":

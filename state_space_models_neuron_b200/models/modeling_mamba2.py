@@ -245,10 +245,11 @@ class Mamba2ForCausalLM(Mamba2PreTrainedModel, GenerationMixin):
     def loss_from_hidden(self, hidden, labels):
         """Loss without materialising fp32 logits for the caller: labels are shifted instead of
         the logits (position L-1 is ignored), the mean runs over the B*(L-1) real targets."""
-        logits = self.lm_head(hidden)
         shifted = torch.full_like(labels, -100)
         shifted[:, :-1] = labels[:, 1:]
-        per_tok = parallel_cross_entropy(logits, shifted.to(logits.device))
+        shifted = shifted.to(hidden.device)
+        logits, stats = self.lm_head(hidden, ce_labels=shifted)
+        per_tok = parallel_cross_entropy(logits, shifted, stats=stats)
         return per_tok.sum() / (labels.shape[0] * (labels.shape[1] - 1))
 
     @torch.no_grad()

@@ -4,8 +4,8 @@
 //
 //   push (all-gather building block)   copy a local [rows, cols] bf16 shard into every rank's gather buffer at
 //                                      this rank's row offset, then publish flag[src = me] = seq on every rank
-//   reduce (reduce-scatter consumer)   wait until all T sources have published, then sum the T partial tiles
-//                                      that landed in this rank's landing zone (fp32 accumulate) -> bf16
+//                                      (the all-gather and reduce-scatter of the linear layers live inside the GEMM
+//                                      kernel, gemm.cu; this stand-alone push serves the embedding backward)
 //   small all-reduce                   packed fp32 vector (cross-entropy statistics, norm-weight grads):
 //                                      every rank writes its vector into every rank's slot, waits, sums
 //   ZeRO-1                             peer reduce of the owned gradient shard fused with scaling and the norm
@@ -34,12 +34,20 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
   asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-// Bounded wait until *flag >= seq.
+// Sequence numbers wrap around: "flag has reached seq" is a signed distance, valid while the two are less than 2^31
+// apart (advance_counter_kernel keeps idle flags within that distance).
+__device__ __forceinline__ bool seq_reached(int flag, int seq) {
+  return (int)((unsigned)flag - (unsigned)seq) >= 0;
+}
+__device__ __forceinline__ int seq_add(int off, const int* base) {
+  return (int)((unsigned)off + (base != nullptr ? (unsigned)*base : 0u));
+}
+// Bounded wait until *flag has reached seq.
 __device__ __forceinline__ bool wait_flag_ge(const int* flag, int seq, int* status) {
-  if (ld_acquire_sys(flag) >= seq) return true;
+  if (seq_reached(ld_acquire_sys(flag), seq)) return true;
   const uint64_t t0 = global_timer_ns();
   for (uint32_t i = 1;; ++i) {
-    if (ld_acquire_sys(flag) >= seq) return true;
+    if (seq_reached(ld_acquire_sys(flag), seq)) return true;
     if ((i & 63u) == 0u) {
       if (status != nullptr && *((volatile int*)status) != 0) return false;
       if (global_timer_ns() - t0 > SSM_WAIT_NS) break;
@@ -58,7 +66,7 @@ __global__ void __launch_bounds__(256)
 push_shard_kernel(const __nv_bfloat16* __restrict__ src, long long src_ld, PeerPtrs dst, long long dst_ld,
                   long long row_off, int rows, int cols, int nranks, int me, PeerPtrs flags, int flag_base, int seq_off,
                   const int* seq_base, int* counter) {
-  const int seq = seq_off + (seq_base ? *seq_base : 0);
+  const int seq = seq_add(seq_off, seq_base);
   const int vec_per_row = cols / 8;
   const long long total = (long long)rows * vec_per_row;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -85,41 +93,6 @@ push_shard_kernel(const __nv_bfloat16* __restrict__ src, long long src_ld, PeerP
 }
 
 // ---------------------------------------------------------------------------------------------------
-// reduce: out[r, c] = sum_s land[s][r][c]  after flags[flag_base + s] >= seq for all s.
-// land: local landing zone [nranks][rows][ld] bf16.  grid: any; block 256.
-// ---------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256)
-reduce_partials_kernel(const __nv_bfloat16* __restrict__ land, long long ld, long long slot_stride,
-                       __nv_bfloat16* __restrict__ out, long long out_ld, int rows, int cols, int nranks,
-                       const int* flags, int flag_base, int seq_off, const int* seq_base, int* status) {
-  const int seq = seq_off + (seq_base ? *seq_base : 0);
-  __shared__ int s_ok;
-  if (threadIdx.x == 0) s_ok = 1;
-  __syncthreads();
-  if (threadIdx.x < nranks) {
-    if (!wait_flag_ge(flags + flag_base + threadIdx.x, seq, status)) s_ok = 0;
-  }
-  __syncthreads();
-  if (!s_ok) return;
-  const int vec_per_row = cols / 8;
-  const long long total = (long long)rows * vec_per_row;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const long long r = i / vec_per_row;
-    const int c = (int)(i % vec_per_row) * 8;
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int s = 0; s < nranks; ++s) {
-      const uint4 u = *reinterpret_cast<const uint4*>(land + s * slot_stride + r * ld + c);
-      acc[0] += bf16_lo(u.x); acc[1] += bf16_hi(u.x); acc[2] += bf16_lo(u.y); acc[3] += bf16_hi(u.y);
-      acc[4] += bf16_lo(u.z); acc[5] += bf16_hi(u.z); acc[6] += bf16_lo(u.w); acc[7] += bf16_hi(u.w);
-    }
-    uint4 o;
-    o.x = pack_bf16(acc[0], acc[1]); o.y = pack_bf16(acc[2], acc[3]);
-    o.z = pack_bf16(acc[4], acc[5]); o.w = pack_bf16(acc[6], acc[7]);
-    *reinterpret_cast<uint4*>(out + r * out_ld + c) = o;
-  }
-}
-
-// ---------------------------------------------------------------------------------------------------
 // small all-reduce (sum or max) of n fp32 values, n <= a few thousand.  Every rank writes its vector into
 // slot[me] of every rank, publishes, waits for all, reduces.  slots[t] -> rank t's slot array [nranks][n_max].
 // One block.  op: 0 sum, 1 max.
@@ -127,7 +100,7 @@ reduce_partials_kernel(const __nv_bfloat16* __restrict__ land, long long ld, lon
 __global__ void __launch_bounds__(256)
 small_allreduce_kernel(float* __restrict__ data, int n, int n_max, PeerPtrs slots, PeerPtrs flags, int flag_base,
                        int nranks, int me, int seq_off, const int* seq_base, int op, int* status) {
-  const int seq = seq_off + (seq_base ? *seq_base : 0);
+  const int seq = seq_add(seq_off, seq_base);
   __shared__ int s_ok;
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     const float v = data[i];
@@ -156,9 +129,27 @@ small_allreduce_kernel(float* __restrict__ data, int n, int n_max, PeerPtrs slot
   }
 }
 
-// *base += stride  (one thread); launched once per training step so that sequence numbers grow across replays of
-// a captured CUDA graph although every kernel node keeps its fixed offset
-__global__ void advance_counter_kernel(int* base, int stride) { *base += stride; }
+// *base += stride (modulo 2^32); launched once per training step so that sequence numbers grow across replays of a
+// captured CUDA graph although every kernel node keeps its fixed offset.  The waits compare by signed distance,
+// which is only meaningful within 2^31: whenever the base crosses a multiple of 2^29, every local flag that has
+// fallen more than 2^29 behind (a collective kind that has not run for a long time) is pulled up to the new base,
+// which no wait of the new block can mistake for "arrived" (their sequence numbers are base + position, position
+// >= 1).  A flag that a peer stores to at the same moment keeps the peer's (newer) value: the update is a
+// compare-and-swap against the stale value.
+__global__ void advance_counter_kernel(int* base, int stride, int* flags, int nflags) {
+  __shared__ unsigned s_old, s_new;
+  if (threadIdx.x == 0) {
+    s_old = (unsigned)*base;
+    s_new = s_old + (unsigned)stride;
+    *base = (int)s_new;
+  }
+  __syncthreads();
+  if (flags == nullptr || (s_old >> 29) == (s_new >> 29)) return;
+  for (int i = threadIdx.x; i < nflags; i += blockDim.x) {
+    const int f = *((volatile int*)(flags + i));
+    if ((int)(s_new - (unsigned)f) > (1 << 29)) atomicCAS(flags + i, f, (int)s_new);
+  }
+}
 
 }  // namespace ssm
 
@@ -182,16 +173,6 @@ extern "C" int ssm_push_shard(const void* src, long long src_ld, const void* con
   return (int)cudaGetLastError();
 }
 
-extern "C" int ssm_reduce_partials(const void* land, long long ld, long long slot_stride, void* out, long long out_ld,
-                                   int rows, int cols, int nranks, const void* flags, int flag_base, int seq,
-                                   const int* seq_base, int* status, int blocks, cudaStream_t st) {
-  if (cols % 8 || ld % 8 || out_ld % 8 || slot_stride % 8 || nranks > MAX_RANKS) return -SSM_ERR_BAD_ARG;
-  reduce_partials_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(land), ld, slot_stride,
-                                                 reinterpret_cast<__nv_bfloat16*>(out), out_ld, rows, cols, nranks,
-                                                 reinterpret_cast<const int*>(flags), flag_base, seq, seq_base, status);
-  return (int)cudaGetLastError();
-}
-
 extern "C" int ssm_small_allreduce(void* data, int n, int n_max, const void* const* slot_ptrs,
                                    const void* const* flag_ptrs, int flag_base, int nranks, int me, int seq,
                                    const int* seq_base, int op, int* status, cudaStream_t st) {
@@ -201,8 +182,9 @@ extern "C" int ssm_small_allreduce(void* data, int n, int n_max, const void* con
   return (int)cudaGetLastError();
 }
 
-extern "C" int ssm_advance_counter(int* base, int stride, cudaStream_t st) {
-  advance_counter_kernel<<<1, 1, 0, st>>>(base, stride);
+// flags / nflags: this rank's flag array that belongs to the counter (may be null: no refresh of idle flags)
+extern "C" int ssm_advance_counter(int* base, int stride, int* flags, int nflags, cudaStream_t st) {
+  advance_counter_kernel<<<1, 128, 0, st>>>(base, stride, flags, nflags);
   return (int)cudaGetLastError();
 }
 
@@ -225,7 +207,7 @@ __global__ void __launch_bounds__(256)
 zero1_reduce_kernel(PeerPtrs grads, float* __restrict__ shard_out, long long shard_start, long long n4, int nranks,
                     int me, float scale, float* __restrict__ sumsq, PeerPtrs flags, int flag_base, int seq_off,
                     const int* seq_base, int* status) {
-  const int seq = seq_off + (seq_base ? *seq_base : 0);
+  const int seq = seq_add(seq_off, seq_base);
   __shared__ int s_ok;
   __shared__ float red[8];
   if (threadIdx.x == 0) s_ok = 1;
@@ -269,13 +251,16 @@ zero1_adamw_push_kernel(float* __restrict__ master, float* __restrict__ m, float
                         int me, const float* __restrict__ clip, float lr, float b1, float b2, float eps, float wd,
                         const float* __restrict__ lr_dev, const int* __restrict__ step_dev, int step, PeerPtrs flags,
                         int flag_base, int seq_off, const int* seq_base, int* counter, int publish) {
-  const int seq = seq_off + (seq_base ? *seq_base : 0);
+  const int seq = seq_add(seq_off, seq_base);
   const float c = clip ? *clip : 1.f;
   if (lr_dev != nullptr) lr = *lr_dev;
   const float st = step_dev != nullptr ? (float)(*step_dev) : (float)step;
   const float ib1 = 1.f / (1.f - powf(b1, st)), ib2 = 1.f / (1.f - powf(b2, st));
   const float decay = 1.f - lr * wd;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+  // a negative or NaN clip coefficient means "skip this step" (non-finite gradients): nothing is updated or pushed,
+  // the parameters every rank holds stay valid, and the completion flag is still published
+  const long long n_eff = (c >= 0.f) ? n4 : 0;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_eff; i += (long long)gridDim.x * blockDim.x) {
     const float4 gi = *reinterpret_cast<const float4*>(g + i * 4);
     float4 mi = *reinterpret_cast<const float4*>(m + i * 4);
     float4 vi = *reinterpret_cast<const float4*>(v + i * 4);
@@ -313,7 +298,7 @@ zero1_adamw_push_kernel(float* __restrict__ master, float* __restrict__ m, float
 
 __global__ void zero1_wait_kernel(const int* flags, int flag_base, int nranks, int seq_off, const int* seq_base,
                                   int* status) {
-  const int seq = seq_off + (seq_base ? *seq_base : 0);
+  const int seq = seq_add(seq_off, seq_base);
   if ((int)threadIdx.x < nranks) wait_flag_ge(flags + flag_base + threadIdx.x, seq, status);
 }
 
@@ -366,7 +351,7 @@ __global__ void __launch_bounds__(256)
 oneshot_allreduce_bf16_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, long long nvec,
                               PeerPtrs slots, long long slot_stride, int nranks, int me, PeerPtrs flags,
                               int flag_base, int seq_off, const int* seq_base, int* counter, int* status) {
-  const int seq = seq_off + (seq_base ? *seq_base : 0);
+  const int seq = seq_add(seq_off, seq_base);
   const long long step = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += step) {
     const uint4 v = reinterpret_cast<const uint4*>(in)[i];
@@ -439,7 +424,7 @@ __global__ void __launch_bounds__(256)
 vocab_embed_push_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ weight,
                         long long vocab_start, long long vloc, PeerPtrs dst, int B, int L, int Ls, int D, int nranks,
                         int me, PeerPtrs flags, int flag_base, int seq_off, const int* seq_base, int* counter) {
-  const int seq = seq_off + (seq_base ? *seq_base : 0);
+  const int seq = seq_add(seq_off, seq_base);
   const int vec = D / 8;
   const long long ntok = (long long)B * L;
   for (long long t = blockIdx.x; t < ntok; t += gridDim.x) {
@@ -467,7 +452,7 @@ vocab_embed_push_kernel(const long long* __restrict__ ids, const __nv_bfloat16* 
 __global__ void __launch_bounds__(256)
 embed_wait_copy_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ out, long long nvec,
                        int nranks, const int* flags, int flag_base, int seq_off, const int* seq_base, int* status) {
-  const int seq = seq_off + (seq_base ? *seq_base : 0);
+  const int seq = seq_add(seq_off, seq_base);
   __shared__ int s_ok;
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
@@ -485,7 +470,7 @@ embed_bwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restr
                  float* __restrict__ grad32, long long vocab_start, long long vloc, int B, int L, int Ls, int D,
                  int nranks, const int* flags, int flag_base, int seq_off, const int* seq_base, int* status) {
   if (nranks > 1) {
-    const int seq = seq_off + (seq_base ? *seq_base : 0);
+    const int seq = seq_add(seq_off, seq_base);
     __shared__ int s_ok;
     if (threadIdx.x == 0) s_ok = 1;
     __syncthreads();

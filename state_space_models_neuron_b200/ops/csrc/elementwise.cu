@@ -538,6 +538,21 @@ ce_backward_kernel(const T* __restrict__ logits, long long ld, const long long* 
   }
 }
 
+// Row statistics that a GEMM epilogue produced per column tile -> one (max, sum exp(x - max)) per row.
+// tmax / tsum: [tiles][rows].
+__global__ void __launch_bounds__(256)
+ce_merge_tiles_kernel(const float* __restrict__ tmax, const float* __restrict__ tsum, int tiles, long long rows,
+                      float* __restrict__ omax, float* __restrict__ osum) {
+  const long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  float m = -INFINITY;
+  for (int t = 0; t < tiles; ++t) m = fmaxf(m, tmax[(long long)t * rows + r]);
+  float s = 0.f;
+  for (int t = 0; t < tiles; ++t) s += tsum[(long long)t * rows + r] * __expf(tmax[(long long)t * rows + r] - m);
+  omax[r] = m;
+  osum[r] = s;
+}
+
 // =====================================================================================
 // AdamW on a flat fp32 master shard + low-precision copy; sum of squares
 // =====================================================================================
@@ -560,6 +575,7 @@ adamw_kernel(float* __restrict__ master, float* __restrict__ m, float* __restric
              long long n4, const float* __restrict__ clip, float lr, float b1, float b2, float eps,
              float wd, float bc1, float bc2, const float* __restrict__ lr_dev, const int* __restrict__ step_dev) {
   const float c = clip ? *clip : 1.f;
+  if (!(c >= 0.f)) return;                               // negative or NaN coefficient: the optimizer skips this step
   if (lr_dev != nullptr) lr = *lr_dev;                   // device-resident hyper-parameters: a captured graph
   if (step_dev != nullptr) {                             // replays with the current learning rate and step
     const float st = (float)(*step_dev);
@@ -860,6 +876,14 @@ extern "C" int ssm_ce_partials(const void* logits, long long ld, int is_fp32, co
   else ce_partials_kernel<__nv_bfloat16><<<(unsigned)rows, 256, 0, st>>>(BF(logits), ld, lb, V, vocab_start, a, b, c);
   return (int)cudaGetLastError();
 }
+extern "C" int ssm_ce_merge_tiles(const void* tmax, const void* tsum, int tiles, long long rows, void* omax, void* osum,
+                                  cudaStream_t st) {
+  if (tiles < 1 || rows < 1) return -SSM_ERR_BAD_ARG;
+  ce_merge_tiles_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(
+      reinterpret_cast<const float*>(tmax), reinterpret_cast<const float*>(tsum), tiles, rows,
+      reinterpret_cast<float*>(omax), reinterpret_cast<float*>(osum));
+  return (int)cudaGetLastError();
+}
 extern "C" int ssm_ce_backward(const void* logits, long long ld, int is_fp32, const void* labels, long long rows, int V,
                                int vocab_start, long long ignore_index, const void* gmax, const void* gsum,
                                const void* grow, void* grad, long long gld, cudaStream_t st) {
@@ -944,6 +968,11 @@ extern "C" int ssm_add_rmsnorm_bwd_noalloc(const void* res, const void* w, const
   int mv = 1;
   const int t = norm_threads(D, &mv);
   if (D <= 0 || D % 8 || t < 0 || rows < 1 || !res || !w || !dout || !dsum || !dw) return -SSM_NOALLOC_ERR_BAD_ARG;
+  // the kernels move rows with 16-byte vector loads and stores: a misaligned base would fault on the device
+  const uintptr_t vec16 = reinterpret_cast<uintptr_t>(res) | reinterpret_cast<uintptr_t>(w) |
+                          reinterpret_cast<uintptr_t>(dout) | reinterpret_cast<uintptr_t>(dres_out) |
+                          reinterpret_cast<uintptr_t>(dsum);
+  if ((vec16 & 15) || (reinterpret_cast<uintptr_t>(dw) & 3)) return -SSM_NOALLOC_ERR_BAD_ARG;
   int err = 0;
   float* scratch = noalloc_scratch_for_current_device(&err);
   if (scratch == nullptr) return err;

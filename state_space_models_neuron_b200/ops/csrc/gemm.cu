@@ -1,13 +1,26 @@
 // bf16 GEMM for sm_100a: TMA (no multicast) -> 128B-swizzled smem ring -> tcgen05.mma with fp32 accumulators in
-// TMEM -> epilogue.  Persistent, warp-specialised, 7 warps:
-//     warp 0      TMA producer (one elected thread): the A loads of every stage (all loads in the fused variants)
+// TMEM -> epilogue.  Persistent, warp-specialised, 7 warps per CTA:
+//     warp 0      TMA producer (one elected thread): the A loads of every stage
 //     warp 1      MMA issuer (one elected thread), owns the TMEM allocation
 //     warps 2..5  epilogue: tcgen05.ld -> bf16 (plain, or +bias / GELU) -> swizzled smem -> TMA store,
 //                 or fp32 TMA store / TMA reduce-add for gradient outputs (optionally adding sum(C^2) to a scalar),
-//                 or TMA stores into the peers' landing zones (reduce-scatter)
-//     warp 6      second TMA producer: the B loads of every stage (plain GEMMs)
+//                 or TMA stores into the peers' landing zones (reduce-scatter);
+//                 in the all-gather variant the same warps first push this rank's shard to the peers
+//     warp 6      second TMA producer: the B loads of every stage
 // Two accumulator stages in TMEM let the epilogue of tile i overlap the main loop of tile i+1.
-// Tiles 128 x {256, 192, 128} x 64, chosen per problem by wave count.
+//
+// Two tile families:
+//   * one CTA per tile, 128 x {256, 192, 128} x 64 (cta_group::1)
+//   * a CTA pair per tile, 256 x {256, 128} x 64 (cta_group::2, clusters of two CTAs): every CTA loads its own 128
+//     rows of A and its own half of the B rows, the even CTA issues MMAs that read both CTAs' shared memory and
+//     write 128 accumulator rows into each CTA's TMEM.  Per FLOP a CTA then pulls 2/3 of the operand bytes of
+//     a 128 x 256 tile through its L2 port, which is what bounds the single-CTA main loop.
+// Scheduling: whole tiles round-robin over the CTAs (or pairs) for as many full waves as there are; the tiles of
+// the last, partial wave are split along K over the idle units (at most 4 slices, 8 for accumulating outputs).
+// Slices of a tile leave their fp32 partial sums in a scratch buffer; whichever slice finishes last sums all of them
+// in slice order (the result does not depend on the arrival order) and runs the epilogue; no slice ever waits for
+// another one.
+//
 // C[M,N] = A * B with A given as [M,K] row-major ("K-major") or [K,M] row-major ("MN-major") and B as
 // [N,K] row-major (K-major) or [K,N] row-major (MN-major); the MN-major forms serve the transposed products
 // of the backward pass (dX = dY W, dW = dY^T X) without any explicit transpose.
@@ -19,16 +32,19 @@
 
 namespace ssm {
 
-constexpr int GEMM_BM = 128;
+constexpr int GEMM_BM = 128;                             // accumulator rows per CTA
 constexpr int GEMM_BK = 64;
-constexpr int GEMM_THREADS = 224;                       // warp 0: TMA (A), 1: MMA, 2-5: epilogue, 6: TMA (B) when dual
+constexpr int GEMM_THREADS = 224;                       // warp 0: TMA (A), 1: MMA, 2-5: epilogue, 6: TMA (B)
 constexpr int EPI_BLOCK_COLS = 64;                       // bf16 columns per TMA store block (128 bytes)
 constexpr int EPI_BUF_BYTES = GEMM_BM * EPI_BLOCK_COLS * 2;  // 16 KiB
+constexpr int MAX_SPLIT = 8;                             // K slices of a tail tile (upper bound of GemmParams::split)
+constexpr int MAX_UNITS = 160;                           // scheduling units (CTAs or pairs) the scratch is sized for
+constexpr int AG_MAX_GROUPS = 4;                         // row groups of a shard with a ready flag of their own
 
 struct GemmParams {
   int M, N, K;
   int a_mn, b_mn;        // operand majorness
-  int mode;              // 0: bf16 via TMA store, 1: fp32 store, 2: fp32 accumulate (red.add)
+  int mode;              // 0: bf16 via TMA store, 1: fp32 store, 2: fp32 accumulate (red.add), 3: reduce-scatter push
   int act;               // 0 none, 1 GELU (mode 0 only)
   const __nv_bfloat16* bias;  // [N] or null (mode 0 only)
   float* c32;            // modes 1, 2
@@ -37,12 +53,22 @@ struct GemmParams {
   long long ldc16;
   float* sumsq;          // mode 1 only: += sum of squares of every stored element (gradient-norm contribution)
   int dual;              // 1: two producer warps, one issues the A loads and one the B loads of every stage
-  int prefetch;          // k-blocks that the TMA producer prefetches into L2 ahead of its loads (0 = off)
   unsigned long long* trace;   // optional [grid][16] timestamps (ns) for pipeline analysis, else null
   int direct;            // 1: epilogue warps store their rows straight from registers (no smem staging / TMA store)
   int* status;
   int tiles_m, tiles_n;
-  int gemm_ctas;         // CTAs that run GEMM tiles (the grid may hold extra communication CTAs)
+  // schedule: `units` CTAs (or CTA pairs) take whole tiles [0, full_tiles) round-robin; the `rem` tiles after them
+  // are cut into `split` K slices each, one slice per unit
+  int units, full_tiles, rem, split;
+  float* ws;             // scratch for partial sums of split tiles: [rem][split][CTAs per unit][128 x BN] fp32
+  int* ws_counters;      // [rem][CTAs per unit] arrival counters (zero between launches)
+  // cross-entropy statistics of the rows of C (mode 0, LM head): per n-tile (max, sum exp(x - max)) of the bf16-rounded
+  // logits and the logit at the row's label
+  const long long* ce_labels;   // [M] global ids, negative = ignored; null = off
+  long long ce_vocab_start;
+  float* ce_max;         // [tiles_n][M]
+  float* ce_sum;         // [tiles_n][M]
+  float* ce_tgt;         // [M], written only for rows whose label lies in [vocab_start, vocab_start + N)
 };
 
 constexpr int MAX_RANKS = 8;
@@ -50,26 +76,32 @@ struct PeerPtrs { void* p[MAX_RANKS]; };
 
 // Fusion of the GEMM with the tensor-parallel collectives over peer memory.
 //  * all-gather side (ag): the A operand is a gather buffer [nranks * rows_per_shard, K] in local memory that
-//    every rank fills by pushing its shard into all ranks' buffers.  The last `comm_ctas` CTAs of this grid do
-//    this rank's push (P2P stores) and publish flag[me] = seq on every rank; the TMA producer of the GEMM CTAs
-//    waits (bounded) for flag[shard] before the first load of a shard's rows and visits the local shard first.
+//    every rank fills by pushing its shard into all ranks' buffers.  The epilogue warps of every CTA push a slice
+//    of each row group of the local shard (P2P stores) before they turn to their tiles; the CTA that completes a
+//    group publishes flag[me][group] = seq on every rank.  Meanwhile the producer and MMA warps already work: tiles
+//    of the local shard read the shard itself (second tensor map), tiles of a remote shard wait (bounded) for the
+//    flag of exactly the row group they read, so a remote group is consumed as soon as its bytes have landed.
 //  * reduce-scatter side (rs, epilogue mode 3): output rows belong to owner = row / rows_per_owner; each tile is
 //    TMA-stored into the owner's landing slot for this rank (one tensor map per owner, peer memory), remote
 //    owners first; when all of this rank's tiles for an owner have landed, flag[me] = seq is published there.
+//    With rs_out set the kernel also finishes the collective: after its tiles every CTA waits (bounded) for the
+//    flags of all sources and sums a slice of the landing slots into rs_out (fp32 accumulate, bf16 result).
 struct GemmComm {
   int nranks, me, seq;          // sequence number of this call = *seq_base + seq (seq_base may be null)
   const int* seq_base;          // device counter advanced once per training step (keeps CUDA-graph replays unique)
   // all-gather side
-  int ag, rows_per_shard, comm_ctas, ag_flag_base, ag_cols;
+  int ag, rows_per_shard, ag_group_rows, ag_flag_base, ag_cols;
   const int* ag_flags;                 // local flag array
   const __nv_bfloat16* ag_src; long long ag_src_ld;
   PeerPtrs ag_dst; long long ag_dst_ld;
   PeerPtrs flag_ptrs;                  // every rank's flag array
-  int* ag_counter;
+  int* ag_counter;                     // local [AG_MAX_GROUPS], zero between launches
   // reduce-scatter side
   int rs, rows_per_owner, rs_flag_base;
   int* rs_counters;                    // local [nranks]
   PeerPtrs rs_land; long long rs_land_ld;   // landing slots as plain pointers (direct-store epilogue)
+  const __nv_bfloat16* rs_land_local; long long rs_slot_stride;   // this rank's landing zone [nranks][rows][ld]
+  __nv_bfloat16* rs_out; long long rs_out_ld;                     // reduced block [rows_per_owner, N] or null
 };
 struct RsMaps { CUtensorMap m[MAX_RANKS]; };
 
@@ -81,11 +113,16 @@ __device__ __forceinline__ int ld_acquire_sys_s32(const int* p) {
   asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+// Sequence numbers wrap around: "flag has reached seq" is a signed distance, valid while the two are less than
+// 2^31 apart.
+__device__ __forceinline__ bool seq_reached(int flag, int seq) {
+  return (int)((unsigned)flag - (unsigned)seq) >= 0;
+}
 __device__ __forceinline__ bool wait_flag(const int* flag, int seq, int* status) {
-  if (ld_acquire_sys_s32(flag) >= seq) return true;
+  if (seq_reached(ld_acquire_sys_s32(flag), seq)) return true;
   const uint64_t t0 = global_timer_ns();
   for (uint32_t i = 1;; ++i) {
-    if (ld_acquire_sys_s32(flag) >= seq) return true;
+    if (seq_reached(ld_acquire_sys_s32(flag), seq)) return true;
     if ((i & 63u) == 0u) {
       if (status != nullptr && *((volatile int*)status) != 0) return false;
       if (global_timer_ns() - t0 > SSM_WAIT_NS) break;
@@ -94,9 +131,9 @@ __device__ __forceinline__ bool wait_flag(const int* flag, int seq, int* status)
   if (status != nullptr) atomicCAS(status, 0, SSM_ERR_TIMEOUT_FLAG);
   return false;
 }
-// m-tile visiting order: rotate so that `first_block` (a shard / owner index) comes first
-__device__ __forceinline__ int rotate_m(int tm, int tiles_m, int tiles_per_block, int first_block) {
-  int v = tm + first_block * tiles_per_block;
+// m-tile visiting order: rotate so that tile `first` comes first
+__device__ __forceinline__ int rotate_m(int tm, int tiles_m, int first) {
+  int v = tm + first;
   return v >= tiles_m ? v - tiles_m : v;
 }
 
@@ -104,10 +141,11 @@ __device__ __forceinline__ void trace_mark(const GemmParams& p, int slot) {
   if (p.trace != nullptr) p.trace[(size_t)blockIdx.x * 16 + slot] = global_timer_ns();
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool PAIR>
 struct GemmSmem {
+  static constexpr int B_ROWS = PAIR ? BN / 2 : BN;       // rows of B that this CTA loads
   static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;   // 16 KiB
-  static constexpr int B_BYTES = BN * GEMM_BK * 2;
+  static constexpr int B_BYTES = B_ROWS * GEMM_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int EPI_OFF = STAGES * STAGE_BYTES;
   static constexpr int BAR_OFF = EPI_OFF + 2 * EPI_BUF_BYTES;
@@ -118,12 +156,42 @@ __device__ __forceinline__ float gelu_f(float x) {
   return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
 }
 
-template <int BN, int STAGES>
+struct Work { int tile, kb0, kb1, slice, nslices, tail; };
+
+__device__ __forceinline__ bool get_work(const GemmParams& p, int unit, int it, int kblocks, Work& w) {
+  const int idx = unit + it * p.units;
+  if (idx < p.full_tiles) {
+    w.tile = idx; w.kb0 = 0; w.kb1 = kblocks; w.slice = 0; w.nslices = 1; w.tail = 0;
+    return true;
+  }
+  if (it != p.full_tiles / p.units || unit >= p.rem * p.split) return false;
+  w.tail = unit / p.split;
+  w.tile = p.full_tiles + w.tail;
+  w.slice = unit - w.tail * p.split;
+  w.nslices = p.split;
+  w.kb0 = (int)((long long)w.slice * kblocks / p.split);
+  w.kb1 = (int)((long long)(w.slice + 1) * kblocks / p.split);
+  return true;
+}
+
+// (first row of this CTA's 128 accumulator rows, first column of the tile)
+template <int BN, bool PAIR>
+__device__ __forceinline__ void tile_origin(const GemmParams& p, const GemmComm& cm, int tile, int cta_rank, int& m0, int& n0) {
+  constexpr int TILE_M = PAIR ? 256 : 128;
+  int tm = tile % p.tiles_m;
+  if (cm.ag) tm = rotate_m(tm, p.tiles_m, (cm.me * cm.rows_per_shard) / TILE_M);
+  if (cm.rs) tm = rotate_m(tm, p.tiles_m, ((cm.me + 1) % cm.nranks) * cm.rows_per_owner / TILE_M);
+  m0 = tm * TILE_M + cta_rank * GEMM_BM;
+  n0 = (tile / p.tiles_m) * BN;
+}
+
+template <int BN, int STAGES, bool PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                  const __grid_constant__ CUtensorMap tmap_c, const GemmParams p, const GemmComm cm,
-                  const __grid_constant__ RsMaps rsm) {
-  using L = GemmSmem<BN, STAGES>;
+                  const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_a_local,
+                  const GemmParams p, const GemmComm cm, const __grid_constant__ RsMaps rsm) {
+  using L = GemmSmem<BN, STAGES, PAIR>;
+  constexpr int CTAS_PER_UNIT = PAIR ? 2 : 1;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
@@ -131,209 +199,172 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   uint64_t* tfull_bar = empty_bar + STAGES;
   uint64_t* tempty_bar = tfull_bar + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  int* epi_flag = reinterpret_cast<int*>(tmem_slot + 1);      // epilogue warps: "this slice arrived last"
+  int* tail_ok = epi_flag + 1;                                 // reduce-scatter tail: all flags arrived
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int cta_rank = PAIR ? (int)cluster_ctarank() : 0;
+  const int unit = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const bool leader = cta_rank == 0;
   const int kblocks = (p.K + GEMM_BK - 1) / GEMM_BK;
-  const int nctas = p.gemm_ctas;
-  const int seqv = cm.seq + (cm.seq_base != nullptr ? *cm.seq_base : 0);
-
-  if (cm.ag && cm.comm_ctas == 0) {
-    // ------------------------------------------------------------------ cooperative all-gather push
-    // Every CTA first moves a slice of the local shard into all ranks' gather buffers (P2P stores), the last one
-    // to finish publishes this rank's flag everywhere; only then do the CTAs turn to their tiles.  The tiles of
-    // remote shards could not start before the data has crossed NVLink anyway, and all SMs storing together get
-    // the shard out several times faster than a few dedicated CTAs.
-    const int vec_per_row = cm.ag_cols / 8;
-    const long long total = (long long)cm.rows_per_shard * vec_per_row;
-    const long long row_off = (long long)cm.me * cm.rows_per_shard;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-      const long long r = i / vec_per_row;
-      const int c = (int)(i % vec_per_row) * 8;
-      const uint4 v = *reinterpret_cast<const uint4*>(cm.ag_src + r * cm.ag_src_ld + c);
-      #pragma unroll
-      for (int k = 0; k < MAX_RANKS; ++k) {
-        const int t = (cm.me + k) % MAX_RANKS;
-        if (t < cm.nranks)
-          *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(cm.ag_dst.p[t]) + (row_off + r) * cm.ag_dst_ld + c) = v;
-      }
-    }
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      const int done = atomicAdd(cm.ag_counter, 1) + 1;
-      if (done == (int)gridDim.x) {
-        __threadfence_system();
-        for (int t = 0; t < cm.nranks; ++t)
-          st_release_sys_s32(reinterpret_cast<int*>(cm.flag_ptrs.p[t]) + cm.ag_flag_base + cm.me, seqv);
-        *cm.ag_counter = 0;
-      }
-    }
-  }
-  if ((int)blockIdx.x >= nctas) {
-    // ------------------------------------------------------------------ communication CTA (all-gather push)
-    const int ci = blockIdx.x - nctas;
-    const int vec_per_row = cm.ag_cols / 8;
-    const long long total = (long long)cm.rows_per_shard * vec_per_row;
-    const long long row_off = (long long)cm.me * cm.rows_per_shard;
-    for (long long i = (long long)ci * blockDim.x + threadIdx.x; i < total; i += (long long)cm.comm_ctas * blockDim.x) {
-      const long long r = i / vec_per_row;
-      const int c = (int)(i % vec_per_row) * 8;
-      const uint4 v = *reinterpret_cast<const uint4*>(cm.ag_src + r * cm.ag_src_ld + c);
-      #pragma unroll
-      for (int k = 0; k < MAX_RANKS; ++k) {
-        const int t = (cm.me + k) % MAX_RANKS;
-        if (t < cm.nranks)
-          *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(cm.ag_dst.p[t]) + (row_off + r) * cm.ag_dst_ld + c) = v;
-      }
-    }
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      const int done = atomicAdd(cm.ag_counter, 1) + 1;
-      if (done == cm.comm_ctas) {
-        __threadfence_system();
-        for (int t = 0; t < cm.nranks; ++t)
-          st_release_sys_s32(reinterpret_cast<int*>(cm.flag_ptrs.p[t]) + cm.ag_flag_base + cm.me, seqv);
-        *cm.ag_counter = 0;
-      }
-    }
-    return;
-  }
+  const int seqv = (int)((unsigned)cm.seq + (cm.seq_base != nullptr ? (unsigned)*cm.seq_base : 0u));
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], p.dual ? 2 : 1); mbar_init(&empty_bar[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], 4); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], 4 * CTAS_PER_UNIT); }
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
     if (p.mode != 3) tma_prefetch_desc(&tmap_c);
     if (p.mode == 3) for (int t = 0; t < cm.nranks; ++t) tma_prefetch_desc(&rsm.m[t]);
+    if (cm.ag) tma_prefetch_desc(&tmap_a_local);
+    *tail_ok = 1;
   }
   constexpr int TMEM_COLS = 2 * BN <= 256 ? 256 : 512;      // allocation sizes are powers of two
-  if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  if (warp == 1) {
+    if (PAIR) { tmem_alloc_pair(tmem_slot, TMEM_COLS); tmem_relinquish_pair(); }
+    else { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  }
   tc_fence_before_sync();
-  __syncthreads();
+  if (PAIR) cluster_sync_all(); else __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   if (threadIdx.x == 0) trace_mark(p, 0);
 
   if (warp == 0 || (warp == 6 && p.dual)) {
     // ------------------------------------------------------------------ TMA producer(s)
-    // One thread issuing every load of a stage is a bottleneck of its own: a tensor-map copy takes that thread a few
-    // hundred cycles to issue, and a stage needs 2 (K-major operands) to 6 (MN-major) of them.  With `dual` warp 0
-    // issues the A loads and warp 6 the B loads; both arm the same full barrier (two arrivals) with their byte counts.
+    // A tensor-map copy takes the issuing thread a few hundred cycles, and a stage needs 2 (K-major operands) to 6
+    // (MN-major) of them: warp 0 issues the A loads and warp 6 the B loads; both arm the same full barrier.  In a
+    // pair both CTAs' loads complete on the leader's barrier, which its producers arm with the bytes of both CTAs.
     const bool do_a = warp == 0, do_b = warp == 6 || !p.dual;
-    const uint32_t tx_bytes = (do_a ? L::A_BYTES : 0) + (do_b ? L::B_BYTES : 0);
+    const uint32_t tx_bytes = ((do_a ? L::A_BYTES : 0) + (do_b ? L::B_BYTES : 0)) * CTAS_PER_UNIT;
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0;
       int armed[STAGES];
       #pragma unroll
       for (int s = 0; s < STAGES; ++s) armed[s] = -1;
       bool ok = true;
-      uint32_t shard_seen = 0;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += nctas) {
-        int tm = tile % p.tiles_m;
-        if (cm.ag) tm = rotate_m(tm, p.tiles_m, cm.rows_per_shard / GEMM_BM, cm.me);
-        if (cm.rs) tm = rotate_m(tm, p.tiles_m, cm.rows_per_owner / GEMM_BM, (cm.me + 1) % cm.nranks);
-        const int m0 = tm * GEMM_BM;
-        const int n0 = (tile / p.tiles_m) * BN;
+      uint32_t group_seen = 0;
+      Work w;
+      for (int it = 0; ok && get_work(p, unit, it, kblocks, w); ++it) {
+        int m0, n0;
+        tile_origin<BN, PAIR>(p, cm, w.tile, cta_rank, m0, n0);
+        const int nb0 = n0 + cta_rank * L::B_ROWS;         // first B row (= output column) this CTA loads
+        const CUtensorMap* ta = &tmap_a;
+        int am0 = m0;
         if (cm.ag) {
           const int shard = m0 / cm.rows_per_shard;
-          if (!(shard_seen & (1u << shard))) {
-            if (!wait_flag(cm.ag_flags + cm.ag_flag_base + shard, seqv, p.status)) { ok = false; break; }
-            fence_proxy_async_all();      // rows were written by generic-proxy stores (local or peer SMs)
-            shard_seen |= 1u << shard;
-          }
-        }
-        for (int kb = 0; kb < kblocks; ++kb) {
-          if (p.prefetch > 0 && !p.dual) {
-            // L2 prefetch of the operand tiles this CTA will load `prefetch` k-blocks from now (possibly in its next
-            // tile): the ring of STAGES loads then completes at L2 latency instead of HBM latency
-            int pk = kb + p.prefetch, ptile = tile;
-            while (pk >= kblocks) { pk -= kblocks; ptile += nctas; }
-            if (ptile < num_tiles) {
-              int ptm = ptile % p.tiles_m;
-              if (cm.ag) ptm = rotate_m(ptm, p.tiles_m, cm.rows_per_shard / GEMM_BM, cm.me);
-              if (cm.rs) ptm = rotate_m(ptm, p.tiles_m, cm.rows_per_owner / GEMM_BM, (cm.me + 1) % cm.nranks);
-              const int pm0 = ptm * GEMM_BM, pn0 = (ptile / p.tiles_m) * BN, pk0 = pk * GEMM_BK;
-              if (!cm.ag) {                       // gathered rows may not have arrived yet: weights only in that case
-                if (!p.a_mn) tma_prefetch_l2_2d(&tmap_a, pk0, pm0);
-                else { tma_prefetch_l2_2d(&tmap_a, pm0, pk0); tma_prefetch_l2_2d(&tmap_a, pm0 + 64, pk0); }
-              }
-              if (!p.b_mn) tma_prefetch_l2_2d(&tmap_b, pk0, pn0);
-              else {
-                #pragma unroll
-                for (int j = 0; j < BN / 64; ++j) tma_prefetch_l2_2d(&tmap_b, pn0 + 64 * j, pk0);
-              }
+          if (shard == cm.me) {
+            ta = &tmap_a_local;                            // the local shard is read in place
+            am0 = m0 - shard * cm.rows_per_shard;
+          } else if (m0 < p.M) {
+            const int grp = (m0 - shard * cm.rows_per_shard) / cm.ag_group_rows;
+            const uint32_t bit = 1u << (shard * AG_MAX_GROUPS + grp);
+            if (!(group_seen & bit)) {
+              if (!wait_flag(cm.ag_flags + cm.ag_flag_base + shard * AG_MAX_GROUPS + grp, seqv, p.status)) { ok = false; break; }
+              fence_proxy_async_all();      // rows were written by generic-proxy stores of peer SMs
+              group_seen |= bit;
             }
           }
+        }
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status)) { ok = false; break; }
           uint8_t* sa = smem + stage * L::STAGE_BYTES;
           uint8_t* sb = sa + L::A_BYTES;
-          mbar_expect_tx(&full_bar[stage], tx_bytes);
+          if (leader) mbar_expect_tx(&full_bar[stage], tx_bytes);
           armed[stage] = (int)phase;
           const int k0 = kb * GEMM_BK;
-          if (do_a) {
-            if (!p.a_mn) {
-              tma_load_2d(sa, &tmap_a, k0, m0, &full_bar[stage]);                 // box {64 k, 128 m}
-            } else {
-              tma_load_2d(sa, &tmap_a, m0, k0, &full_bar[stage]);                 // box {64 m, 64 k} x 2
-              tma_load_2d(sa + 8192, &tmap_a, m0 + 64, k0, &full_bar[stage]);
+          if (!PAIR) {
+            if (do_a) {
+              if (!p.a_mn) {
+                tma_load_2d(sa, ta, k0, am0, &full_bar[stage]);                 // box {64 k, 128 m}
+              } else {
+                tma_load_2d(sa, ta, am0, k0, &full_bar[stage]);                 // box {64 m, 64 k} x 2
+                tma_load_2d(sa + 8192, ta, am0 + 64, k0, &full_bar[stage]);
+              }
             }
-          }
-          if (do_b) {
-            if (!p.b_mn) {
-              tma_load_2d(sb, &tmap_b, k0, n0, &full_bar[stage]);                 // box {64 k, BN n}
-            } else {
-              #pragma unroll
-              for (int j = 0; j < BN / 64; ++j)
-                tma_load_2d(sb + j * 8192, &tmap_b, n0 + 64 * j, k0, &full_bar[stage]);  // box {64 n, 64 k}
+            if (do_b) {
+              if (!p.b_mn) {
+                tma_load_2d(sb, &tmap_b, k0, nb0, &full_bar[stage]);            // box {64 k, BN n}
+              } else {
+                #pragma unroll
+                for (int j = 0; j < L::B_ROWS / 64; ++j)
+                  tma_load_2d(sb + j * 8192, &tmap_b, nb0 + 64 * j, k0, &full_bar[stage]);  // box {64 n, 64 k}
+              }
+            }
+          } else {
+            const uint32_t bar = smem_u32(&full_bar[stage]) & PAIR_LEADER_MASK;
+            if (do_a) {
+              if (!p.a_mn) {
+                tma_load_2d_pair(sa, ta, k0, am0, bar);
+              } else {
+                tma_load_2d_pair(sa, ta, am0, k0, bar);
+                tma_load_2d_pair(sa + 8192, ta, am0 + 64, k0, bar);
+              }
+            }
+            if (do_b) {
+              if (!p.b_mn) {
+                tma_load_2d_pair(sb, &tmap_b, k0, nb0, bar);                    // box {64 k, BN/2 n}
+              } else {
+                #pragma unroll
+                for (int j = 0; j < L::B_ROWS / 64; ++j)
+                  tma_load_2d_pair(sb + j * 8192, &tmap_b, nb0 + 64 * j, k0, bar);
+              }
             }
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
-          if (do_a && tile == (int)blockIdx.x && kb == 0) trace_mark(p, 8);
+          if (do_a && it == 0 && kb == w.kb0) trace_mark(p, 8);
         }
       }
       if (do_a) trace_mark(p, 9);
       if (!ok) {
         // error path: let copies that are still in flight land before the CTA's shared memory goes away
-        #pragma unroll
-        for (int s = 0; s < STAGES; ++s)
-          if (armed[s] >= 0) mbar_wait(&full_bar[s], (uint32_t)armed[s], nullptr);
+        if (leader) {
+          #pragma unroll
+          for (int s = 0; s < STAGES; ++s)
+            if (armed[s] >= 0) mbar_wait(&full_bar[s], (uint32_t)armed[s], nullptr);
+        } else {
+          const uint64_t t0 = global_timer_ns();           // the peer's copies complete on the leader's barriers
+          while (global_timer_ns() - t0 < 50000ull) { }
+        }
       }
     }
     __syncwarp();
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      const uint32_t idesc = make_idesc_bf16(GEMM_BM, BN, p.a_mn, p.b_mn);
+    // ------------------------------------------------------------------ MMA issuer (even CTA of a pair only)
+    if (lane == 0 && leader) {
+      const uint32_t idesc = make_idesc_bf16(PAIR ? 256 : 128, BN, p.a_mn, p.b_mn);
       const uint32_t a_step = p.a_mn ? (16 * 128) >> 4 : 32 >> 4;  // descriptor start-address step per UMMA_K=16
       const uint32_t b_step = p.b_mn ? (16 * 128) >> 4 : 32 >> 4;
       const uint32_t a_lbo = p.a_mn ? 8192u : 16u, b_lbo = p.b_mn ? 8192u : 16u;
       int stage = 0; uint32_t phase = 0;
       int acc = 0; uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += nctas) {
+      Work w;
+      for (int it = 0; ok && get_work(p, unit, it, kblocks, w); ++it) {
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, p.status)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < kblocks; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, p.status)) { ok = false; break; }
           tc_fence_after_sync();
-          if (tile == (int)blockIdx.x && kb == 0) trace_mark(p, 1);
+          if (it == 0 && kb == w.kb0) trace_mark(p, 1);
           const uint32_t sa = smem_u32(smem + stage * L::STAGE_BYTES);
           const uint32_t sb = sa + L::A_BYTES;
           const uint64_t da = make_smem_desc_sw128(sa, a_lbo, 1024);
           const uint64_t db = make_smem_desc_sw128(sb, b_lbo, 1024);
           #pragma unroll
-          for (int kk = 0; kk < GEMM_BK / 16; ++kk)
-            umma_bf16(d_tmem, da + (uint64_t)(kk * a_step), db + (uint64_t)(kk * b_step), idesc, (kb | kk) != 0);
-          umma_commit(&empty_bar[stage]);          // frees the smem stage once these MMAs have read it
+          for (int kk = 0; kk < GEMM_BK / 16; ++kk) {
+            const uint32_t accum = (kb != w.kb0 || kk != 0) ? 1u : 0u;
+            if (PAIR) umma_bf16_pair(d_tmem, da + (uint64_t)(kk * a_step), db + (uint64_t)(kk * b_step), idesc, accum);
+            else umma_bf16(d_tmem, da + (uint64_t)(kk * a_step), db + (uint64_t)(kk * b_step), idesc, accum);
+          }
+          // frees the smem stage (in both CTAs of a pair) once these MMAs have read it
+          if (PAIR) umma_commit_pair(&empty_bar[stage]); else umma_commit(&empty_bar[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
-        if (ok) umma_commit(&tfull_bar[acc]);      // accumulator complete
-        trace_mark(p, tile == (int)blockIdx.x ? 2 : 3);
+        if (ok) { if (PAIR) umma_commit_pair(&tfull_bar[acc]); else umma_commit(&tfull_bar[acc]); }   // accumulator complete
+        trace_mark(p, it == 0 ? 2 : 3);
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
     }
@@ -344,6 +375,53 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     const int epi_tid = threadIdx.x - 64;          // 0..127
     const int row = q * 32 + lane;                 // row of the tile held by this thread
     uint8_t* epi_buf = smem + L::EPI_OFF;
+
+    if (cm.ag) {
+      // -------- all-gather push: this CTA's slice of every row group of the local shard, to all ranks
+      const int vec_per_row = cm.ag_cols / 8;
+      const int ngroups = cm.rows_per_shard / cm.ag_group_rows;
+      const long long vec_per_group = (long long)cm.ag_group_rows * vec_per_row;
+      const long long row_off = (long long)cm.me * cm.rows_per_shard;
+      const long long lo = vec_per_group * blockIdx.x / gridDim.x, hi = vec_per_group * (blockIdx.x + 1) / gridDim.x;
+      for (int g = 0; g < ngroups; ++g) {
+        for (long long i0 = lo + epi_tid; i0 < hi; i0 += 128 * 4) {
+          uint4 v[4];
+          long long off[4];
+          #pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const long long i = i0 + u * 128;
+            if (i < hi) {
+              const long long r = (long long)g * cm.ag_group_rows + i / vec_per_row;
+              const int c = (int)(i % vec_per_row) * 8;
+              v[u] = *reinterpret_cast<const uint4*>(cm.ag_src + r * cm.ag_src_ld + c);
+              off[u] = (row_off + r) * cm.ag_dst_ld + c;
+            }
+          }
+          #pragma unroll
+          for (int k = 1; k <= MAX_RANKS; ++k) {           // peers first (ring order), the local copy last
+            const int t = (cm.me + k) % MAX_RANKS;
+            if (t < cm.nranks) {
+              #pragma unroll
+              for (int u = 0; u < 4; ++u)
+                if (i0 + u * 128 < hi)
+                  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(cm.ag_dst.p[t]) + off[u]) = v[u];
+            }
+          }
+        }
+        __threadfence_system();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (epi_tid == 0) {
+          const int done = atomicAdd(cm.ag_counter + g, 1) + 1;
+          if (done == (int)gridDim.x) {
+            cm.ag_counter[g] = 0;
+            __threadfence_system();
+            for (int t = 0; t < cm.nranks; ++t)
+              st_release_sys_s32(reinterpret_cast<int*>(cm.flag_ptrs.p[t]) + cm.ag_flag_base + cm.me * AG_MAX_GROUPS + g, seqv);
+          }
+        }
+      }
+    }
+
     int acc = 0; uint32_t acc_phase = 0;
     bool ok = true;
     int stores_issued = 0;
@@ -351,17 +429,11 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     int rs_count[MAX_RANKS];
     #pragma unroll
     for (int t = 0; t < MAX_RANKS; ++t) rs_count[t] = 0;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += nctas) {
-      int tm = tile % p.tiles_m;
-      if (cm.ag) tm = rotate_m(tm, p.tiles_m, cm.rows_per_shard / GEMM_BM, cm.me);
-      if (cm.rs) tm = rotate_m(tm, p.tiles_m, cm.rows_per_owner / GEMM_BM, (cm.me + 1) % cm.nranks);
-      const int m0 = tm * GEMM_BM;
-      const int n0 = (tile / p.tiles_m) * BN;
+    Work w;
+    for (int it = 0; ok && get_work(p, unit, it, kblocks, w); ++it) {
+      int m0, n0;
+      tile_origin<BN, PAIR>(p, cm, w.tile, cta_rank, m0, n0);
       const int owner = cm.rs ? m0 / cm.rows_per_owner : 0;
-      if (cm.rs && ok) {
-        #pragma unroll
-        for (int t = 0; t < MAX_RANKS; ++t) if (t == owner) rs_count[t] += 1;
-      }
       if (!mbar_wait(&tfull_bar[acc], acc_phase, p.status)) { ok = false; }
       {
         // the four epilogue warps must agree on the outcome before they meet at named barriers
@@ -377,16 +449,80 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         ok = all != 0;
       }
       tc_fence_after_sync();
-      if (epi_tid == 0) trace_mark(p, tile == (int)blockIdx.x ? 4 : 6);
-      if (ok) {
+      if (epi_tid == 0) trace_mark(p, it == 0 ? 4 : 6);
+      // ---- tail tiles cut along K: exchange partial sums, the slice that arrives last runs the epilogue
+      bool run_epilogue = ok && m0 < p.M;
+      const float* others = nullptr;       // partial sums of the other slices (this CTA's rows), null: none
+      if (ok && w.nslices > 1 && p.mode != 2) {
+        float* mine = p.ws + ((size_t)(w.tail * MAX_SPLIT + w.slice) * CTAS_PER_UNIT + cta_rank) * (GEMM_BM * BN);
+        #pragma unroll 1
+        for (int j = 0; j < BN / 32; ++j) {
+          if (n0 + j * 32 >= p.N) break;
+          uint32_t v[32];
+          tmem_ld32(tmem_addr(tmem_base, q * 32, acc * BN + j * 32), v);
+          tmem_ld_wait();
+          #pragma unroll
+          for (int c = 0; c < 8; ++c)           // layout [BN / 4][128 rows][4]: a warp writes 512 contiguous bytes
+            *reinterpret_cast<uint4*>(mine + ((size_t)(j * 8 + c) * GEMM_BM + row) * 4) =
+                make_uint4(v[c * 4], v[c * 4 + 1], v[c * 4 + 2], v[c * 4 + 3]);
+        }
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (epi_tid == 0) {
+          int* ctr = p.ws_counters + w.tail * CTAS_PER_UNIT + cta_rank;
+          const int ticket = atomicAdd(ctr, 1);
+          const int last = ticket == w.nslices - 1;
+          if (last) { *ctr = 0; __threadfence(); }
+          *epi_flag = last;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        run_epilogue = run_epilogue && (*epi_flag != 0);
+        others = p.ws + ((size_t)(w.tail * MAX_SPLIT) * CTAS_PER_UNIT + cta_rank) * (GEMM_BM * BN);
+      }
+      if (run_epilogue && cm.rs) {
+        #pragma unroll
+        for (int t = 0; t < MAX_RANKS; ++t) if (t == owner) rs_count[t] += 1;
+      }
+      float ce_m = -INFINITY, ce_s = 0.f;
+      long long ce_lbl = -1;
+      if (p.ce_labels != nullptr && run_epilogue && m0 + row < p.M) {
+        const long long lb = p.ce_labels[m0 + row];
+        ce_lbl = lb >= 0 ? lb - p.ce_vocab_start : -1;
+      }
+      if (run_epilogue) {
         #pragma unroll 1
         for (int j = 0; j < BN / EPI_BLOCK_COLS; ++j) {
           const int nb = n0 + j * EPI_BLOCK_COLS;
           if (nb >= p.N) break;
           uint32_t v[2][32];
-          tmem_ld32(tmem_addr(tmem_base, q * 32, acc * BN + j * 64), v[0]);
-          tmem_ld32(tmem_addr(tmem_base, q * 32, acc * BN + j * 64 + 32), v[1]);
-          tmem_ld_wait();
+          if (others == nullptr) {
+            tmem_ld32(tmem_addr(tmem_base, q * 32, acc * BN + j * 64), v[0]);
+            tmem_ld32(tmem_addr(tmem_base, q * 32, acc * BN + j * 64 + 32), v[1]);
+            tmem_ld_wait();
+          } else {
+            // sum of all slices in slice order (this CTA's own partial is read back like the others), so the result
+            // does not depend on which slice happened to arrive last
+            #pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              #pragma unroll
+              for (int e = 0; e < 32; ++e) v[h][e] = 0u;
+            }
+            for (int s = 0; s < w.nslices; ++s) {
+              const float* src = others + (size_t)s * CTAS_PER_UNIT * (GEMM_BM * BN);
+              #pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                if (nb + h * 32 >= p.N) break;
+                #pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                  const float4 o = __ldcg(reinterpret_cast<const float4*>(src + ((size_t)(j * 16 + h * 8 + c) * GEMM_BM + row) * 4));
+                  v[h][c * 4 + 0] = __float_as_uint(__uint_as_float(v[h][c * 4 + 0]) + o.x);
+                  v[h][c * 4 + 1] = __float_as_uint(__uint_as_float(v[h][c * 4 + 1]) + o.y);
+                  v[h][c * 4 + 2] = __float_as_uint(__uint_as_float(v[h][c * 4 + 2]) + o.z);
+                  v[h][c * 4 + 3] = __float_as_uint(__uint_as_float(v[h][c * 4 + 3]) + o.w);
+                }
+              }
+            }
+          }
           if (p.direct && p.mode == 3) {
             // reduce-scatter: the row goes straight into the owner's landing slot (peer memory, P2P stores)
             __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(cm.rs_land.p[owner]) +
@@ -475,6 +611,27 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                   o.z = pack_bf16(__uint_as_float(v[h][c * 8 + 4]), __uint_as_float(v[h][c * 8 + 5]));
                   o.w = pack_bf16(__uint_as_float(v[h][c * 8 + 6]), __uint_as_float(v[h][c * 8 + 7]));
                   *reinterpret_cast<uint4*>(buf + sw128_offset(row, h * 4 + c)) = o;
+                  if (p.ce_labels != nullptr) {
+                    // statistics of the values the consumer of C will read: the bf16-rounded logits
+                    const uint32_t pk[4] = {o.x, o.y, o.z, o.w};
+                    float mx = ce_m;
+                    #pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                      const int col = nb + h * 32 + c * 8 + e;
+                      const float x = (e & 1) ? bf16_hi(pk[e >> 1]) : bf16_lo(pk[e >> 1]);
+                      if (col < p.N) mx = fmaxf(mx, x);
+                    }
+                    if (mx > ce_m) { ce_s *= __expf(ce_m - mx); ce_m = mx; }
+                    #pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                      const int col = nb + h * 32 + c * 8 + e;
+                      const float x = (e & 1) ? bf16_hi(pk[e >> 1]) : bf16_lo(pk[e >> 1]);
+                      if (col < p.N) {
+                        ce_s += __expf(x - ce_m);
+                        if ((long long)col == ce_lbl) p.ce_tgt[m0 + row] = x;
+                      }
+                    }
+                  }
                 }
               }
             } else {
@@ -538,11 +695,19 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             }
           }
         }
+        if (p.ce_labels != nullptr && m0 + row < p.M) {
+          const size_t o = (size_t)(n0 / BN) * p.M + (m0 + row);
+          p.ce_max[o] = ce_m;
+          p.ce_sum[o] = ce_s;
+        }
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (epi_tid == 0) trace_mark(p, tile == (int)blockIdx.x ? 5 : 7);
-      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      if (epi_tid == 0) trace_mark(p, it == 0 ? 5 : 7);
+      if (lane == 0) {
+        if (PAIR) mbar_arrive_cluster(smem_u32(&tempty_bar[acc]) & PAIR_LEADER_MASK);
+        else mbar_arrive(&tempty_bar[acc]);
+      }
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
     if (p.sumsq != nullptr && p.mode == 1) {
@@ -579,39 +744,62 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (cm.rs && cm.rs_out != nullptr) {
+    // ------------------------------------------------------------------ reduce-scatter tail
+    // every CTA sums a slice of the T partial blocks that the sources stored into this rank's landing zone; the
+    // wait is for the peers' flags only (they do not depend on this kernel), never for another CTA of this grid
+    if ((int)threadIdx.x < cm.nranks) {
+      const int* flags = reinterpret_cast<const int*>(cm.flag_ptrs.p[cm.me]);
+      if (!wait_flag(flags + cm.rs_flag_base + threadIdx.x, seqv, p.status)) *tail_ok = 0;
+    }
+    __syncthreads();
+    if (*tail_ok) {
+      const int vec_per_row = p.N / 8;
+      const long long total = (long long)cm.rows_per_owner * vec_per_row;
+      for (long long i = (long long)blockIdx.x * GEMM_THREADS + threadIdx.x; i < total; i += (long long)gridDim.x * GEMM_THREADS) {
+        const long long r = i / vec_per_row;
+        const int c = (int)(i % vec_per_row) * 8;
+        float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        #pragma unroll 4
+        for (int s = 0; s < cm.nranks; ++s) {
+          const uint4 u = *reinterpret_cast<const uint4*>(cm.rs_land_local + s * cm.rs_slot_stride + r * cm.rs_land_ld + c);
+          a[0] += bf16_lo(u.x); a[1] += bf16_hi(u.x); a[2] += bf16_lo(u.y); a[3] += bf16_hi(u.y);
+          a[4] += bf16_lo(u.z); a[5] += bf16_hi(u.z); a[6] += bf16_lo(u.w); a[7] += bf16_hi(u.w);
+        }
+        uint4 o;
+        o.x = pack_bf16(a[0], a[1]); o.y = pack_bf16(a[2], a[3]);
+        o.z = pack_bf16(a[4], a[5]); o.w = pack_bf16(a[6], a[7]);
+        *reinterpret_cast<uint4*>(cm.rs_out + r * cm.rs_out_ld + c) = o;
+      }
+    }
+  }
   if (threadIdx.x == 0) trace_mark(p, 10);
-  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (PAIR) {
+    // neither CTA may leave (or free TMEM) while its partner can still signal its barriers or read its shared memory
+    tc_fence_before_sync();
+    cluster_sync_all();
+    if (warp == 1) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  } else {
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+  }
 }
 
 // ------------------------------------------------------------------------------------ host
 static int g_num_sms = 0;
-
-// SSM_GEMM_EPI=direct makes the epilogue warps store their rows straight from registers instead of staging them in
-// shared memory for a TMA store (measured slower: each lane then writes its own 128-byte row segment, which costs
-// most for the fp32 gradient outputs; kept for experiments).
 static unsigned long long* g_trace = nullptr;
 
+static int env_int(const char* name, int dflt) {
+  const char* e = getenv(name);
+  return e ? atoi(e) : dflt;
+}
 // SSM_GEMM_DUAL=0 goes back to one producer thread for all loads of a stage.
 static int gemm_dual_producers() {
   static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("SSM_GEMM_DUAL");
-    v = (e && atoi(e) == 0) ? 0 : 1;
-  }
+  if (v < 0) v = env_int("SSM_GEMM_DUAL", 1) ? 1 : 0;
   return v;
 }
-
-// SSM_GEMM_PREFETCH=n: the producer prefetches operand tiles n k-blocks ahead into L2 (0 = off).
-static int gemm_prefetch_distance() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("SSM_GEMM_PREFETCH");
-    v = e ? atoi(e) : 0;
-    if (v < 0) v = 0;
-  }
-  return v;
-}
-
+// SSM_GEMM_EPI=direct makes the epilogue warps store their rows straight from registers instead of staging them in
+// shared memory for a TMA store (measured slower; kept for experiments).
 static int epilogue_direct() {
   static int v = -1;
   if (v < 0) {
@@ -620,75 +808,176 @@ static int epilogue_direct() {
   }
   return v;
 }
+// SSM_GEMM_PAIR=0 never uses CTA pairs; SSM_GEMM_SPLIT=0 never cuts tail tiles along K.
+static int gemm_pairs_enabled() {
+  static int v = -1;
+  if (v < 0) v = env_int("SSM_GEMM_PAIR", 1) ? 1 : 0;
+  return v;
+}
+static int gemm_split_enabled() {
+  static int v = -1;
+  if (v < 0) v = env_int("SSM_GEMM_SPLIT", 1) ? 1 : 0;
+  return v;
+}
 
-// Tile width.  128x256 tiles have the best operand reuse; 128x192 and 128x128 tiles fill the SMs better when the
-// 256-wide tiling leaves the last wave mostly empty (the per-rank shapes of tensor parallelism).  Compare the
-// SM-time of the tilings: waves x relative tile cost (measured: a 128-wide tile costs 0.8 of a 256-wide one, a
-// 192-wide one is taken as 0.8 = 0.75 / 0.94); a narrower tiling must win by 10 % to be chosen.
-// SSM_GEMM_FORCE_BN=128|192|256 overrides the choice (experiments).
-static int pick_tile_n(int M, int N) {
-  static int forced = -1;
-  if (forced < 0) {
-    const char* e = getenv("SSM_GEMM_FORCE_BN");
-    forced = e ? atoi(e) : 0;
+// Scratch for the split tail (allocated once per device, on first use): partial sums and arrival counters.
+struct Scratch { float* ws; int* counters; };
+static Scratch g_scratch[16] = {};
+static int scratch_for_current_device(Scratch* out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return -1;
+  if (g_scratch[dev].ws == nullptr) {
+    const size_t ws_bytes = (size_t)MAX_UNITS * 2 * GEMM_BM * 256 * sizeof(float);   // one slice per CTA and launch
+    void* a = nullptr; void* b = nullptr;
+    if (cudaMalloc(&a, ws_bytes) != cudaSuccess) return -1;
+    if (cudaMalloc(&b, MAX_UNITS * 2 * sizeof(int)) != cudaSuccess) { cudaFree(a); return -1; }
+    if (cudaMemset(b, 0, MAX_UNITS * 2 * sizeof(int)) != cudaSuccess) { cudaFree(a); cudaFree(b); return -1; }
+    g_scratch[dev].ws = reinterpret_cast<float*>(a);
+    g_scratch[dev].counters = reinterpret_cast<int*>(b);
   }
-  if (N <= 128) return 128;
-  if (forced == 128 || forced == 192 || forced == 256) return forced;
+  *out = g_scratch[dev];
+  return 0;
+}
+
+struct TileChoice { int bn; int pair; };
+
+// Tile shape.  The cost of a tiling is (full waves + the split tail) x time of one tile; tile times relative to a
+// 128 x 256 single-CTA tile are measured values (a CTA's main loop is bound by the operand bytes it pulls per
+// k-block: 48 KB for 128x256, 32 KB for a 128x128 tile or for its half of a 256x256 pair tile, 24 KB for its half
+// of a 256x128 pair tile).  SSM_GEMM_FORCE_BN=128|192|256 and SSM_GEMM_PAIR=0|1|2 (2 = always) override.
+static TileChoice pick_tile(int M, int N, int K, int b_mn, int allow_pair) {
+  static int forced_bn = -1, forced_pair = -1;
+  if (forced_bn < 0) { forced_bn = env_int("SSM_GEMM_FORCE_BN", 0); forced_pair = env_int("SSM_GEMM_PAIR", 1); }
   const int sms = g_num_sms > 0 ? g_num_sms : 148;
-  const long long tm = (M + GEMM_BM - 1) / GEMM_BM;
-  auto cost = [&](int bn, double tile_cost) {
-    const long long t = tm * ((N + bn - 1) / bn);
-    return (double)((t + sms - 1) / sms) * tile_cost;
-  };
-  // fewer 128-wide tiles than SMs (decode-time GEMMs with a handful of rows, thin per-rank projections): every CTA
-  // is bound by its own operand stream, so the tiling with the most CTAs wins
-  if (tm * ((N + 127) / 128) <= sms) return 128;
-  const double c256 = cost(256, 1.0), c192 = cost(192, 0.8), c128 = cost(128, 0.8);
-  int best = 256;
-  double cb = c256;
-  if (c192 < 0.9 * cb) { best = 192; cb = c192; }
-  if (c128 < 0.9 * c256 && c128 < cb) best = 128;
+  const int kblocks = (K + GEMM_BK - 1) / GEMM_BK;
+  struct Cand { int bn, pair; double cost; };
+  // cost of one tile per k-block, relative
+  const Cand cands[5] = {{256, 0, 1.00}, {192, 0, 0.80}, {128, 0, 0.80}, {256, 1, 0.68}, {128, 1, 0.52}};
+  TileChoice best = {256, 0};
+  double best_t = 1e30;
+  for (const Cand& c : cands) {
+    if (c.pair && (!allow_pair || forced_pair == 0 || M <= 128)) continue;
+    if (!c.pair && forced_pair == 2 && allow_pair && M > 128) continue;
+    if (forced_bn && c.bn != forced_bn) continue;
+    if (c.bn > 128 && N <= 128) continue;
+    const int tile_m = c.pair ? 256 : 128;
+    const int units = c.pair ? sms / 2 : sms;
+    const long long tiles = (long long)((M + tile_m - 1) / tile_m) * ((N + c.bn - 1) / c.bn);
+    const long long full = tiles / units, rem = tiles % units;
+    double waves = (double)full;
+    if (rem) {
+      int split = (int)(units / rem);
+      if (split > 4) split = 4;
+      if (split > kblocks / 4) split = kblocks / 4 > 0 ? kblocks / 4 : 1;
+      waves += 1.0 / split + (split > 1 ? 0.08 : 0.0);       // exchange of partial sums
+    }
+    // per-tile fixed cost (pipeline fill, epilogue tail) in k-block units
+    const double t = waves * (kblocks * c.cost + 6.0);
+    if (t < best_t) { best_t = t; best = {c.bn, c.pair}; }
+  }
+  (void)b_mn;
   return best;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool PAIR>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, GemmParams p,
-                       cudaStream_t stream, const GemmComm* comm = nullptr, const RsMaps* maps = nullptr) {
-  using L = GemmSmem<BN, STAGES>;
+                       cudaStream_t stream, const GemmComm* comm = nullptr, const RsMaps* maps = nullptr,
+                       const CUtensorMap* ta_local = nullptr) {
+  using L = GemmSmem<BN, STAGES, PAIR>;
   static bool configured = false;
-  auto kern = gemm_bf16_tcgen05<BN, STAGES>;
+  auto kern = gemm_bf16_tcgen05<BN, STAGES, PAIR>;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  p.tiles_m = (p.M + GEMM_BM - 1) / GEMM_BM;
+  constexpr int TILE_M = PAIR ? 256 : 128;
+  p.tiles_m = (p.M + TILE_M - 1) / TILE_M;
   p.tiles_n = (p.N + BN - 1) / BN;
   const int tiles = p.tiles_m * p.tiles_n;
   static GemmComm no_comm;       // zero-initialised: no fusion
   static RsMaps no_maps;
   GemmComm cm = comm ? *comm : no_comm;
-  int extra = (comm && cm.ag) ? cm.comm_ctas : 0;
-  const int avail = g_num_sms - extra;
-  p.gemm_ctas = tiles < avail ? tiles : avail;
-  kern<<<p.gemm_ctas + extra, GEMM_THREADS, L::TOTAL, stream>>>(ta, tb, tc, p, cm, maps ? *maps : no_maps);
+  int max_units = PAIR ? g_num_sms / 2 : g_num_sms;
+  if (PAIR) {
+    // every CTA of the grid must be resident at once (CTAs of different ranks wait for one another's pushes)
+    static int max_clusters = -1;
+    if (max_clusters < 0) {
+      cudaLaunchConfig_t q = {};
+      q.gridDim = dim3((unsigned)g_num_sms, 1, 1);
+      q.blockDim = dim3(GEMM_THREADS, 1, 1);
+      q.dynamicSmemBytes = L::TOTAL;
+      cudaLaunchAttribute qa[1];
+      qa[0].id = cudaLaunchAttributeClusterDimension;
+      qa[0].val.clusterDim.x = 2; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
+      q.attrs = qa; q.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kern, &q) != cudaSuccess || n < 1) n = g_num_sms / 2;
+      max_clusters = n;
+    }
+    if (max_units > max_clusters) max_units = max_clusters;
+  }
+  if (max_units > MAX_UNITS) max_units = MAX_UNITS;
+  const int kblocks = (p.K + GEMM_BK - 1) / GEMM_BK;
+  int units = tiles < max_units ? tiles : max_units;
+  p.full_tiles = (tiles / units) * units;
+  p.rem = tiles - p.full_tiles;
+  p.split = 1;
+  p.ws = nullptr; p.ws_counters = nullptr;
+  if (gemm_split_enabled() && (p.rem > 0 || tiles < max_units)) {
+    // fewer tiles than units: everything is tail (full_tiles = 0) and the idle units take K slices
+    if (tiles < max_units) { units = max_units; p.full_tiles = 0; p.rem = tiles; }
+    int split = units / p.rem;
+    const int cap = p.mode == 2 ? MAX_SPLIT : 4;
+    if (split > cap) split = cap;
+    if (split > kblocks / 4) split = kblocks / 4;
+    if (split < 1) split = 1;
+    p.split = split;
+    if (split > 1 && p.mode != 2) {
+      Scratch s;
+      if (scratch_for_current_device(&s) != 0) p.split = 1;
+      else { p.ws = s.ws; p.ws_counters = s.counters; }
+    }
+    if (tiles < max_units) units = p.rem * p.split;          // launch only the units that have work
+  }
+  p.units = units;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(units * (PAIR ? 2 : 1)), 1, 1);
+  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = L::TOTAL;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = PAIR ? 2 : 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, ta_local ? *ta_local : ta, p, cm, maps ? *maps : no_maps);
+  if (e != cudaSuccess) return (int)e;
   return (int)cudaGetLastError();
 }
 
 }  // namespace ssm
 
+struct GemmExtra {                     // optional outputs of ssm_gemm_bf16_ex2
+  const void* ce_labels; long long ce_vocab_start; void* ce_max; void* ce_sum; void* ce_tgt;
+};
+
+static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                          long long ldc, int a_mn, int b_mn, int mode, const void* bias, int act, int* status,
+                          cudaStream_t stream, float* sumsq, const GemmExtra* extra, const ssm::GemmComm* comm,
+                          const void* const* land_ptrs, long long land_ld, int* tiles_n_out);
+
 // C[M,N] = A * B.  a_mn = 0: A is [M,K] with row stride lda; a_mn = 1: A is [K,M] with row stride lda.
 // b_mn = 0: B is [N,K] with row stride ldb; b_mn = 1: B is [K,N] with row stride ldb.
 // mode 0: C bf16 [M, ldc] (ldc * 2 bytes must be a multiple of 16); 1: C fp32 store; 2: C fp32 += .
 // All leading dimensions in elements; operand bases 16-byte aligned, operand row strides multiples of 8.
-static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
-                          long long ldc, int a_mn, int b_mn, int mode, const void* bias, int act, int* status,
-                          cudaStream_t stream, float* sumsq);
-
 extern "C" int ssm_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
                              long long ldb, long long ldc, int a_mn, int b_mn, int mode, const void* bias, int act,
                              int* status, cudaStream_t stream) {
-  return gemm_bf16_impl(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, mode, bias, act, status, stream, nullptr);
+  return gemm_bf16_impl(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, mode, bias, act, status, stream, nullptr, nullptr,
+                        nullptr, nullptr, 0, nullptr);
 }
 
 // Same, and with mode 1 (fp32 store) the sum of squares of the stored matrix is added to *sumsq (fp32, device):
@@ -698,12 +987,38 @@ extern "C" int ssm_gemm_bf16_ex(const void* A, const void* B, void* C, int M, in
                                 int* status, cudaStream_t stream, void* sumsq) {
   if (sumsq != nullptr && mode != 1) return -SSM_ERR_BAD_ARG;
   return gemm_bf16_impl(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, mode, bias, act, status, stream,
-                        reinterpret_cast<float*>(sumsq));
+                        reinterpret_cast<float*>(sumsq), nullptr, nullptr, nullptr, 0, nullptr);
+}
+
+// Number of column tiles the kernel will use for an [M, N] x K product with K-major operands: the leading extent of
+// the per-tile cross-entropy statistics that ssm_gemm_bf16_ce / the fused variant write.
+extern "C" int ssm_gemm_ce_tiles(int M, int N, int K, int fused) {
+  using namespace ssm;
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  (void)fused;
+  const TileChoice c = pick_tile(M, N, K, 0, gemm_pairs_enabled());
+  return (N + c.bn - 1) / c.bn;
+}
+
+// bf16 GEMM (mode 0, no bias / activation) whose epilogue also emits cross-entropy statistics of the rows of C:
+// ce_max / ce_sum [tiles_n][M] (maximum and sum of exp(x - max) over the tile's columns, from the bf16-rounded
+// values) and ce_tgt[row] = C[row, labels[row] - vocab_start] where that column exists (other rows untouched).
+extern "C" int ssm_gemm_bf16_ce(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                                long long ldb, long long ldc, int* status, cudaStream_t stream, const void* labels,
+                                long long vocab_start, void* ce_max, void* ce_sum, void* ce_tgt) {
+  GemmExtra ex = {labels, vocab_start, ce_max, ce_sum, ce_tgt};
+  return gemm_bf16_impl(A, B, C, M, N, K, lda, ldb, ldc, 0, 0, 0, nullptr, 0, status, stream, nullptr, &ex, nullptr,
+                        nullptr, 0, nullptr);
 }
 
 static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                           long long ldc, int a_mn, int b_mn, int mode, const void* bias, int act, int* status,
-                          cudaStream_t stream, float* sumsq) {
+                          cudaStream_t stream, float* sumsq, const GemmExtra* extra, const ssm::GemmComm* comm,
+                          const void* const* land_ptrs, long long land_ld, int* tiles_n_out) {
   using namespace ssm;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
@@ -714,73 +1029,17 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
   }
-  const int BN = pick_tile_n(M, N);
-  CUtensorMap ta, tb, tc;
+  const TileChoice tcw = pick_tile(M, N, K, b_mn, gemm_pairs_enabled());
+  const int BN = tcw.bn;
+  const bool pair = tcw.pair != 0;
+  if (tiles_n_out) *tiles_n_out = (N + BN - 1) / BN;
+  const uint32_t b_rows = pair ? BN / 2 : BN;
+  CUtensorMap ta, tb, tc, ta_local;
   int r;
   if (!a_mn) r = make_tmap_2d_bf16(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, 64, 128);
   else       r = make_tmap_2d_bf16(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, 64, 64);
   if (r) return -100 - r;
-  if (!b_mn) r = make_tmap_2d_bf16(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, 64, BN);
-  else       r = make_tmap_2d_bf16(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, 64);
-  if (r) return -200 - r;
-  if (mode == 0) {
-    r = make_tmap_2d_bf16(&tc, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc * 2, 64, 128);
-    if (r) return -300 - r;
-  } else {
-    if ((ldc % 4) || (reinterpret_cast<uintptr_t>(C) & 15)) return -SSM_ERR_BAD_ARG;
-    r = make_tmap_2d(&tc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc * 4, 32, 128);
-    if (r) return -300 - r;
-  }
-  GemmParams p;
-  p.M = M; p.N = N; p.K = K; p.a_mn = a_mn; p.b_mn = b_mn; p.mode = mode; p.act = act;
-  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
-  p.c32 = mode == 0 ? nullptr : reinterpret_cast<float*>(C);
-  p.ldc32 = ldc; p.status = status; p.tiles_m = 0; p.tiles_n = 0; p.gemm_ctas = 0;
-  p.c16 = mode == 0 ? reinterpret_cast<__nv_bfloat16*>(C) : nullptr;
-  p.ldc16 = ldc; p.direct = epilogue_direct(); p.trace = g_trace; p.prefetch = gemm_prefetch_distance(); p.sumsq = sumsq;
-  p.dual = gemm_dual_producers();
-  if (sumsq != nullptr) p.direct = 0;      // the sum of squares is formed in the staged (TMA-store) epilogue
-  if (BN == 256) return launch_gemm<256, 4>(ta, tb, tc, p, stream);
-  if (BN == 192) return launch_gemm<192, 4>(ta, tb, tc, p, stream);
-  return launch_gemm<128, 6>(ta, tb, tc, p, stream);
-}
-
-// GEMM fused with a tensor-parallel collective over peer memory (see GemmComm).
-//   ag = 1: A must be this rank's gather buffer [nranks * rows_per_shard, K] (= ag_dst_ptrs[me], row stride
-//           ag_dst_ld); ag_src is the local shard [rows_per_shard, K]; flag_ptrs[t] is rank t's flag array.
-//   rs = 1: mode is forced to 3; land_ptrs[o] is the base of the [rows_per_owner, N] slot this rank owns inside
-//           rank o's landing zone (row stride land_ld); C is ignored.
-// rows_per_shard / rows_per_owner must be multiples of 128 and M = nranks * rows.
-extern "C" int ssm_gemm_bf16_fused(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
-                                   long long ldb, long long ldc, int a_mn, int b_mn, int mode, const void* bias,
-                                   int act, int* status, cudaStream_t stream, int nranks, int me, int seq,
-                                   const int* seq_base, const void* const* flag_ptrs, int ag, int rows_per_shard, int comm_ctas,
-                                   int ag_flag_base, const void* ag_src, long long ag_src_ld,
-                                   const void* const* ag_dst_ptrs, long long ag_dst_ld, int* ag_counter, int rs,
-                                   int rows_per_owner, int rs_flag_base, const void* const* land_ptrs,
-                                   long long land_ld, int* rs_counters) {
-  using namespace ssm;
-  if (M <= 0 || N <= 0 || K <= 0 || nranks < 1 || nranks > MAX_RANKS || me < 0 || me >= nranks) return -SSM_ERR_BAD_ARG;
-  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
-    return -SSM_ERR_BAD_ARG;
-  if (ag && (a_mn || rows_per_shard % GEMM_BM || (long long)rows_per_shard * nranks != M || K % 8 || comm_ctas < 0 ||
-             ag_src_ld % 8 || ag_dst_ld % 8))
-    return -SSM_ERR_BAD_ARG;
-  if (rs && (rows_per_owner % GEMM_BM || (long long)rows_per_owner * nranks != M || land_ld % 8)) return -SSM_ERR_BAD_ARG;
-  if (rs) mode = 3;
-  if (mode == 0 && ((ldc % 8) || (reinterpret_cast<uintptr_t>(C) & 15))) return -SSM_ERR_BAD_ARG;
-  if (g_num_sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
-  }
-  const int BN = pick_tile_n(M, N);
-  CUtensorMap ta, tb, tc;
-  int r;
-  if (!a_mn) r = make_tmap_2d_bf16(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, 64, 128);
-  else       r = make_tmap_2d_bf16(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, 64, 64);
-  if (r) return -100 - r;
-  if (!b_mn) r = make_tmap_2d_bf16(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, 64, BN);
+  if (!b_mn) r = make_tmap_2d_bf16(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, 64, b_rows);
   else       r = make_tmap_2d_bf16(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, 64);
   if (r) return -200 - r;
   if (mode == 0) {
@@ -793,14 +1052,88 @@ extern "C" int ssm_gemm_bf16_fused(const void* A, const void* B, void* C, int M,
   } else {
     tc = ta;
   }
+  ta_local = ta;
   RsMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  if (comm != nullptr && comm->ag) {
+    r = make_tmap_2d_bf16(&ta_local, comm->ag_src, (uint64_t)K, (uint64_t)comm->rows_per_shard,
+                          (uint64_t)comm->ag_src_ld * 2, 64, 128);
+    if (r) return -500 - r;
+  }
+  if (comm != nullptr && comm->rs) {
+    for (int t = 0; t < comm->nranks; ++t) {
+      r = make_tmap_2d_bf16(&maps.m[t], land_ptrs[t], (uint64_t)N, (uint64_t)comm->rows_per_owner, (uint64_t)land_ld * 2, 64, 128);
+      if (r) return -400 - r;
+    }
+  }
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = M; p.N = N; p.K = K; p.a_mn = a_mn; p.b_mn = b_mn; p.mode = mode; p.act = act;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.c32 = (mode == 1 || mode == 2) ? reinterpret_cast<float*>(C) : nullptr;
+  p.ldc32 = ldc; p.status = status;
+  p.c16 = mode == 0 ? reinterpret_cast<__nv_bfloat16*>(C) : nullptr;
+  p.ldc16 = ldc; p.direct = epilogue_direct(); p.trace = g_trace; p.sumsq = sumsq;
+  p.dual = gemm_dual_producers();
+  if (sumsq != nullptr) p.direct = 0;      // the sum of squares is formed in the staged (TMA-store) epilogue
+  if (extra != nullptr && extra->ce_labels != nullptr) {
+    if (mode != 0 || bias != nullptr || act != 0) return -SSM_ERR_BAD_ARG;
+    p.direct = 0;
+    p.ce_labels = reinterpret_cast<const long long*>(extra->ce_labels);
+    p.ce_vocab_start = extra->ce_vocab_start;
+    p.ce_max = reinterpret_cast<float*>(extra->ce_max);
+    p.ce_sum = reinterpret_cast<float*>(extra->ce_sum);
+    p.ce_tgt = reinterpret_cast<float*>(extra->ce_tgt);
+  }
+  const RsMaps* mp = (comm != nullptr && comm->rs) ? &maps : nullptr;
+  if (pair) {
+    if (BN == 256) return launch_gemm<256, 6, true>(ta, tb, tc, p, stream, comm, mp, &ta_local);
+    return launch_gemm<128, 8, true>(ta, tb, tc, p, stream, comm, mp, &ta_local);
+  }
+  if (BN == 256) return launch_gemm<256, 4, false>(ta, tb, tc, p, stream, comm, mp, &ta_local);
+  if (BN == 192) return launch_gemm<192, 4, false>(ta, tb, tc, p, stream, comm, mp, &ta_local);
+  return launch_gemm<128, 6, false>(ta, tb, tc, p, stream, comm, mp, &ta_local);
+}
+
+// GEMM fused with a tensor-parallel collective over peer memory (see GemmComm).
+//   ag = 1: A must be this rank's gather buffer [nranks * rows_per_shard, K] (= ag_dst_ptrs[me], row stride
+//           ag_dst_ld); ag_src is the local shard [rows_per_shard, K]; flag_ptrs[t] is rank t's flag array; the
+//           ready flags of this call are flag_ptrs[t][ag_flag_base + source * 4 + row group]; ag_counter points at
+//           4 local ints that are zero between launches.
+//   rs = 1: mode is forced to 3; land_ptrs[o] is the base of the [rows_per_owner, N] slot this rank owns inside
+//           rank o's landing zone (row stride land_ld); C is ignored.  With rs_out the kernel also reduces this
+//           rank's landing zone (rs_land_local: [nranks] slots, rs_slot_stride elements apart) into
+//           rs_out [rows_per_owner, N] (row stride rs_out_ld) once all sources have published; N % 8 == 0 then.
+//   ce_labels: as in ssm_gemm_bf16_ce (all-gather + LM head).
+// rows_per_shard / rows_per_owner must be multiples of 128 and M = nranks * rows.
+extern "C" int ssm_gemm_bf16_fused(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                                   long long ldb, long long ldc, int a_mn, int b_mn, int mode, const void* bias,
+                                   int act, int* status, cudaStream_t stream, int nranks, int me, int seq,
+                                   const int* seq_base, const void* const* flag_ptrs, int ag, int rows_per_shard,
+                                   int ag_flag_base, const void* ag_src, long long ag_src_ld,
+                                   const void* const* ag_dst_ptrs, long long ag_dst_ld, int* ag_counter, int rs,
+                                   int rows_per_owner, int rs_flag_base, const void* const* land_ptrs,
+                                   long long land_ld, int* rs_counters, const void* rs_land_local,
+                                   long long rs_slot_stride, void* rs_out, long long rs_out_ld, const void* ce_labels,
+                                   long long ce_vocab_start, void* ce_max, void* ce_sum, void* ce_tgt) {
+  using namespace ssm;
+  if (M <= 0 || N <= 0 || K <= 0 || nranks < 1 || nranks > MAX_RANKS || me < 0 || me >= nranks) return -SSM_ERR_BAD_ARG;
+  if (ag && (a_mn || rows_per_shard % GEMM_BM || (long long)rows_per_shard * nranks != M || K % 8 ||
+             ag_src_ld % 8 || ag_dst_ld % 8 || (reinterpret_cast<uintptr_t>(ag_src) & 15)))
+    return -SSM_ERR_BAD_ARG;
+  if (rs && (rows_per_owner % GEMM_BM || (long long)rows_per_owner * nranks != M || land_ld % 8)) return -SSM_ERR_BAD_ARG;
+  if (rs && rs_out != nullptr && (N % 8 || rs_out_ld % 8 || rs_slot_stride % 8)) return -SSM_ERR_BAD_ARG;
+  if (rs) mode = 3;
   GemmComm cm;
   memset(&cm, 0, sizeof(cm));
-  memset(&maps, 0, sizeof(maps));
   cm.nranks = nranks; cm.me = me; cm.seq = seq; cm.seq_base = seq_base;
   for (int t = 0; t < MAX_RANKS; ++t) cm.flag_ptrs.p[t] = t < nranks ? const_cast<void*>(flag_ptrs[t]) : nullptr;
   if (ag) {
-    cm.ag = 1; cm.rows_per_shard = rows_per_shard; cm.comm_ctas = comm_ctas; cm.ag_flag_base = ag_flag_base;
+    cm.ag = 1; cm.rows_per_shard = rows_per_shard; cm.ag_flag_base = ag_flag_base;
+    // at most AG_MAX_GROUPS row groups per shard, each a multiple of 128 rows
+    int group = GEMM_BM;
+    while (rows_per_shard / group > AG_MAX_GROUPS || rows_per_shard % group) group += GEMM_BM;
+    cm.ag_group_rows = group;
     cm.ag_cols = K; cm.ag_flags = reinterpret_cast<const int*>(flag_ptrs[me]);
     cm.ag_src = reinterpret_cast<const __nv_bfloat16*>(ag_src); cm.ag_src_ld = ag_src_ld;
     for (int t = 0; t < MAX_RANKS; ++t) cm.ag_dst.p[t] = t < nranks ? const_cast<void*>(ag_dst_ptrs[t]) : nullptr;
@@ -810,22 +1143,13 @@ extern "C" int ssm_gemm_bf16_fused(const void* A, const void* B, void* C, int M,
     cm.rs = 1; cm.rows_per_owner = rows_per_owner; cm.rs_flag_base = rs_flag_base; cm.rs_counters = rs_counters;
     cm.rs_land_ld = land_ld;
     for (int t = 0; t < nranks; ++t) cm.rs_land.p[t] = const_cast<void*>(land_ptrs[t]);
-    for (int t = 0; t < nranks; ++t) {
-      r = make_tmap_2d_bf16(&maps.m[t], land_ptrs[t], (uint64_t)N, (uint64_t)rows_per_owner, (uint64_t)land_ld * 2, 64, 128);
-      if (r) return -400 - r;
-    }
+    cm.rs_land_local = reinterpret_cast<const __nv_bfloat16*>(rs_land_local);
+    cm.rs_slot_stride = rs_slot_stride;
+    cm.rs_out = reinterpret_cast<__nv_bfloat16*>(rs_out); cm.rs_out_ld = rs_out_ld;
   }
-  GemmParams p;
-  p.M = M; p.N = N; p.K = K; p.a_mn = a_mn; p.b_mn = b_mn; p.mode = mode; p.act = act;
-  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
-  p.c32 = (mode == 1 || mode == 2) ? reinterpret_cast<float*>(C) : nullptr;
-  p.ldc32 = ldc; p.status = status; p.tiles_m = 0; p.tiles_n = 0; p.gemm_ctas = 0;
-  p.c16 = mode == 0 ? reinterpret_cast<__nv_bfloat16*>(C) : nullptr;
-  p.ldc16 = ldc; p.direct = epilogue_direct(); p.trace = g_trace; p.prefetch = gemm_prefetch_distance(); p.sumsq = nullptr;
-  p.dual = 0;      // the fused variants keep the single producer that their flag protocol was validated with
-  if (BN == 256) return launch_gemm<256, 4>(ta, tb, tc, p, stream, &cm, &maps);
-  if (BN == 192) return launch_gemm<192, 4>(ta, tb, tc, p, stream, &cm, &maps);
-  return launch_gemm<128, 6>(ta, tb, tc, p, stream, &cm, &maps);
+  GemmExtra ex = {ce_labels, ce_vocab_start, ce_max, ce_sum, ce_tgt};
+  return gemm_bf16_impl(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, mode, bias, act, status, stream, nullptr,
+                        ce_labels != nullptr ? &ex : nullptr, &cm, land_ptrs, land_ld, nullptr);
 }
 
 // Pipeline analysis: buf = device array of gridDim * 16 uint64 (or null to switch tracing off).  Slots (ns, global

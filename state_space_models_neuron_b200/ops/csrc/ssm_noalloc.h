@@ -17,6 +17,9 @@
 // Limits and rules
 //   * D must be a multiple of 8 and at most SSM_NOALLOC_MAX_D (8192); larger sizes are rejected with
 //     -SSM_NOALLOC_ERR_TOO_LARGE and nothing is launched.  rows >= 1.
+//   * res, w, dout, dres_out and dsum must be 16-byte aligned (the kernels use 16-byte vector accesses; rows are
+//     then aligned too because D is a multiple of 8) and dw 4-byte aligned; a sub-tensor that starts at an odd
+//     offset is rejected with -SSM_NOALLOC_ERR_BAD_ARG before anything is launched.
 //   * The library holds SSM_NOALLOC_SLICES * SSM_NOALLOC_MAX_D floats (2 MiB) of device memory per GPU that
 //     loads it, from load until the process exits.
 //   * The first call on each device looks up the device address of that array (cudaGetSymbolAddress, with
@@ -26,7 +29,8 @@
 //     overwrite every entry they later read, so nothing needs clearing between calls.  Two calls that may
 //     overlap on the GPU (different streams without an ordering between them) race on it: serialise them.
 //   * Returns 0 on success, a negative SSM_NOALLOC_ERR_* code for rejected arguments, a positive cudaError_t
-//     otherwise.
+//     otherwise (the value of cudaGetLastError() after the launches, so an error left pending by earlier work on
+//     the same thread is reported here too).
 #pragma once
 #include <cuda_runtime.h>
 

@@ -145,6 +145,46 @@ def gemm(a: torch.Tensor, b: torch.Tensor, a_mn: bool = False, b_mn: bool = Fals
     return out
 
 
+def ce_epilogue_buffers(M: int, N: int, K: int, labels: torch.Tensor, vocab_start: int):
+    """Buffers for a GEMM whose epilogue emits cross-entropy statistics of its [M, N] output (the LM head):
+    (arguments for the kernel, number of column tiles).  `labels` [M] int64 global ids, negative = ignored."""
+    fn = _lib().ssm_gemm_ce_tiles
+    fn.restype = _c.c_int
+    tiles = int(fn(int(M), int(N), int(K), 0))
+    dev = labels.device
+    lab = labels.reshape(-1).contiguous()
+    if lab.numel() != M or lab.dtype != torch.int64:
+        raise ValueError("labels must be int64 with one entry per output row")
+    return dict(labels=lab, vocab_start=int(vocab_start),
+                tmax=torch.empty(tiles, M, dtype=torch.float32, device=dev),
+                tsum=torch.empty(tiles, M, dtype=torch.float32, device=dev),
+                tgt=torch.zeros(M, dtype=torch.float32, device=dev)), tiles
+
+
+def ce_merge(ced, tiles: int):
+    """Per-tile statistics -> (row max, row sum of exp(x - max), target logit or 0) for this vocabulary shard."""
+    M = ced["tgt"].numel()
+    m = torch.empty(M, dtype=torch.float32, device=ced["tgt"].device)
+    s = torch.empty_like(m)
+    _run("ssm_ce_merge_tiles", _p(ced["tmax"]), _p(ced["tsum"]), int(tiles), _ll(M), _p(m), _p(s), _st())
+    return m, s, ced["tgt"]
+
+
+def gemm_ce(a: torch.Tensor, b: torch.Tensor, labels: torch.Tensor, vocab_start: int):
+    """y = a b^T (bf16, [M, N]) together with the cross-entropy statistics of its rows, produced by the GEMM
+    epilogue (no second pass over the logits): returns (y, (max, sumexp, target))."""
+    _require_bf16(a, b)
+    a, b = _as_operand(a), _as_operand(b)
+    M, K = a.shape
+    N = b.shape[0]
+    out = torch.empty(M, _ceil8(N), dtype=torch.bfloat16, device=a.device)[:, :N]
+    ced, tiles = ce_epilogue_buffers(M, N, K, labels, vocab_start)
+    _run("ssm_gemm_bf16_ce", _p(a), _p(b), _p(out), M, N, K, _ll(a.stride(0)), _ll(b.stride(0)), _ll(out.stride(0)),
+         _p(status_tensor(a.device)), _st(), _p(ced["labels"]), _ll(ced["vocab_start"]), _p(ced["tmax"]),
+         _p(ced["tsum"]), _p(ced["tgt"]))
+    return out, ce_merge(ced, tiles)
+
+
 def wgrad_to_main_grad(dy2: torch.Tensor, x2: torch.Tensor, w) -> bool:
     """dW = dY^T X written straight into the optimizer's fp32 `w.main_grad`: stored on the first contribution of a
     step (lazy zeroing), added afterwards.  When the optimizer has given the weight a norm accumulator (`w.norm_acc`)
@@ -174,17 +214,21 @@ def untrack_norm(w) -> None:
 
 class _Linear(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, bias):
+    def forward(ctx, x, w, bias, ce_labels=None, ce_vocab_start=0):
         K = x.shape[-1]
         x2 = x.reshape(-1, K)
-        y = gemm(x2, w, bias=bias)
         ctx.save_for_backward(x2, w)
         ctx.has_bias = bias is not None
         ctx.xshape = x.shape
+        if ce_labels is not None:
+            y, stats = gemm_ce(x2, w, ce_labels, ce_vocab_start)
+            ctx.mark_non_differentiable(*stats)
+            return (y.reshape(*x.shape[:-1], w.shape[0]),) + tuple(stats)
+        y = gemm(x2, w, bias=bias)
         return y.reshape(*x.shape[:-1], w.shape[0])
 
     @staticmethod
-    def backward(ctx, dy):
+    def backward(ctx, dy, *unused):
         x2, w = ctx.saved_tensors
         N = w.shape[0]
         dy2 = dy.reshape(-1, N)
@@ -198,12 +242,20 @@ class _Linear(torch.autograd.Function):
                     dw = dw.contiguous()
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = dy2.float().sum(0).to(dy.dtype)
-        return dx, dw, db
+        return dx, dw, db, None, None
 
 
 def linear(x, w, bias=None):
     _require_bf16(x, w)
     return _Linear.apply(x, w, bias)
+
+
+def linear_ce(x, w, labels, vocab_start: int = 0):
+    """(x w^T, (row max, row sum-exp, target logit)): the LM head with the cross-entropy statistics taken in the
+    GEMM epilogue (mamba2/modeling_mamba2.py:498-510 computes them in separate passes over fp32 logits)."""
+    _require_bf16(x, w)
+    out = _Linear.apply(x, w, None, labels, int(vocab_start))
+    return out[0], tuple(out[1:])
 
 
 # ======================================================================================

@@ -36,6 +36,15 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     return F.linear(x, weight, bias)
 
 
+def linear_ce(x: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor, vocab_start: int = 0):
+    """(x @ weight^T, statistics): on the GPU path the GEMM epilogue also delivers the per-row cross-entropy
+    statistics (max, sum-exp, target logit) of this vocabulary shard; elsewhere statistics is None and the
+    cross entropy computes them itself."""
+    if _native(x) and x.dtype == torch.bfloat16:
+        return _cuda().linear_ce(x, weight, labels, vocab_start)
+    return F.linear(x, weight), None
+
+
 # ---- conv ---------------------------------------------------------------------------------
 def causal_conv1d_silu(x, weight, bias, initial_state=None):
     """Depthwise causal conv (taps = weight.shape[-1]) + SiLU on channels-last x [B,L,C]."""

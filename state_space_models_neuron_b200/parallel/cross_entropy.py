@@ -17,13 +17,16 @@ from .. import ops
 
 class _ParallelCrossEntropy(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, logits, labels, vocab_start, ignore_index):
+    def forward(ctx, logits, labels, vocab_start, ignore_index, m=None, s=None, tgt=None):
         shape = logits.shape
         V = shape[-1]
-        lg = logits.reshape(-1, V)
+        lg = logits.reshape(-1, V) if logits.dim() != 2 else logits
+        if lg.dim() == 2 and lg.stride(1) != 1:
+            lg = lg.contiguous()
         lb = labels.reshape(-1)
         tp, grp = ps.get_tensor_model_parallel_size(), ps.get_tensor_model_parallel_group()
-        m, s, tgt = ops.ce_partials(lg, lb, vocab_start)
+        if m is None:          # statistics not delivered by the producer of the logits: one pass over them here
+            m, s, tgt = ops.ce_partials(lg, lb, vocab_start)
         if tp > 1:
             from . import fused
             gm = m.clone()
@@ -43,13 +46,18 @@ class _ParallelCrossEntropy(torch.autograd.Function):
     def backward(ctx, g):
         lg, lb, m, s = ctx.saved_tensors
         grad = ops.ce_backward(lg, lb, m, s, g.reshape(-1), ctx.vocab_start, ctx.ignore_index)
-        return grad.reshape(ctx.shape), None, None, None
+        return grad.reshape(ctx.shape), None, None, None, None, None, None
 
 
-def parallel_cross_entropy(logits: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100) -> torch.Tensor:
-    """Per-token loss (no reduction) for vocab-sharded logits and global label ids."""
+def parallel_cross_entropy(logits: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100,
+                           stats=None) -> torch.Tensor:
+    """Per-token loss (no reduction) for vocab-sharded logits and global label ids.  `stats` = (row max, row
+    sum of exp(x - max), target logit or 0) of the local shard when the GEMM that produced the logits already
+    computed them (`ColumnParallelLinear.forward(..., ce_labels=...)`); labels must then be the ones given there."""
     tp, r = ps.get_tensor_model_parallel_size(), ps.get_tensor_model_parallel_rank()
     vocab_start = r * logits.shape[-1] if tp > 1 else 0
+    if stats is not None:
+        return _ParallelCrossEntropy.apply(logits, labels, vocab_start, ignore_index, *stats)
     return _ParallelCrossEntropy.apply(logits, labels, vocab_start, ignore_index)
 
 

@@ -35,8 +35,9 @@ def enabled_for(x) -> bool:
     return bool(_IMPL[0].ready_for(x))
 
 
-def all_gather_linear(x, weight, bias=None):
-    return _IMPL[0].all_gather_linear(x, weight, bias)
+def all_gather_linear(x, weight, bias=None, ce=None):
+    """`ce` = (labels, vocab_start): also return the cross-entropy statistics of the output rows, `(y, stats)`."""
+    return _IMPL[0].all_gather_linear(x, weight, bias, ce)
 
 
 def all_gather_multi_linear(x, weights):

@@ -1,11 +1,13 @@
 """Column-/row-parallel linear layers whose sequence-parallel collective runs inside the GEMM kernel.
 
-    all_gather_linear      y = all_gather_seq(x_shard) W^T     one kernel: P2P push of the shard into every
-                           rank's gather buffer by dedicated CTAs + tcgen05 GEMM whose TMA producer waits per shard
-                           backward: dX = reduce_scatter_seq(dY W) as GEMM -> peer landing zones -> reduce;
+    all_gather_linear      y = all_gather_seq(x_shard) W^T     one kernel: the epilogue warps of every CTA push a
+                           slice of the shard into every rank's gather buffer (P2P stores, ready flag per row group)
+                           while the TMA / MMA warps already compute: local rows first, remote rows as they land
+                           backward: dX = reduce_scatter_seq(dY W) (GEMM -> peer landing zones -> in-kernel sum);
                                      dW += dY^T x_gathered
-    linear_reduce_scatter  y_shard = reduce_scatter_seq(x W^T)  GEMM whose epilogue TMA-stores every tile into the
-                           owning rank's landing zone + a reduce kernel that waits for the T sources
+    linear_reduce_scatter  y_shard = reduce_scatter_seq(x W^T)  one kernel: the GEMM epilogue TMA-stores every tile
+                           into the owning rank's landing zone; after its tiles every CTA sums a slice of the T
+                           partial blocks that arrived for this rank
                            backward: dX = all_gather_seq(dY_shard) W (same fused kernel), dW += dY_full^T x
 
 These replace the pairs (all-gather, GEMM) and (GEMM, reduce-scatter) that the reference leaves to
@@ -17,7 +19,6 @@ multiple of 128).
 from __future__ import annotations
 
 import ctypes
-import os
 
 import torch
 
@@ -26,9 +27,6 @@ from . import symm
 from ..ops import cuda_ops
 from ..ops.cuda_ops import _P, _ceil8, _ll, _run, _st, status_tensor
 
-# CTAs of the all-gather GEMM that only push the local shard to the peers.  0 (default): every CTA pushes a slice
-# first and then computes tiles; N > 0: N dedicated CTAs push while the others start on the local shard's tiles.
-COMM_CTAS = int(os.environ.get("SSM_AG_COMM_CTAS", "0"))
 CALLS = {"ag_gemm": 0, "gemm_rs": 0}     # how many fused kernels this process has launched
 _c = ctypes
 
@@ -44,34 +42,45 @@ def ready_for(x: torch.Tensor) -> bool:
     return x.shape[0] == 1
 
 
-def _fused_gemm(a, b, out, M, N, K, lda, ldb, ldc, a_mn, b_mn, mode, bias, ws, seq, ag=None, rs=None):
+def _fused_gemm(a, b, out, M, N, K, lda, ldb, ldc, a_mn, b_mn, mode, bias, act, ws, seq, ag=None, rs=None, ce=None):
     null = symm._ptr_array([])
     ag = ag or dict(on=0, rows=0, base=0, src=None, src_ld=0, dst=null, dst_ld=0, counter=0)
-    rs = rs or dict(on=0, rows=0, base=0, land=null, ld=0, counters=0)
+    rs = rs or dict(on=0, rows=0, base=0, land=null, ld=0, counters=0, local=0, slot_stride=0, out=None, out_ld=0)
+    ce = ce or dict(labels=None, vocab_start=0, tmax=None, tsum=None, tgt=None)
     _run("ssm_gemm_bf16_fused", _P(a), _P(b), _P(out), M, N, K, _ll(lda), _ll(ldb), _ll(ldc), int(a_mn), int(b_mn), mode,
-         _P(bias), 0, _P(status_tensor(ws.device)), _st(), ws.nranks, ws.me, seq, _P(ws.seq_base), ws.flag_ptr_array,
-         ag["on"], ag["rows"], COMM_CTAS, ag["base"], _P(ag["src"]), _ll(ag["src_ld"]), ag["dst"], _ll(ag["dst_ld"]),
-         _c.c_void_p(ag["counter"]), rs["on"], rs["rows"], rs["base"], rs["land"], _ll(rs["ld"]),
-         _c.c_void_p(rs["counters"]))
+         _P(bias), int(act), _P(status_tensor(ws.device)), _st(), ws.nranks, ws.me, seq, _P(ws.seq_base),
+         ws.flag_ptr_array,
+         ag["on"], ag["rows"], ag["base"], _P(ag["src"]), _ll(ag["src_ld"]), ag["dst"], _ll(ag["dst_ld"]),
+         _c.c_void_p(ag["counter"]),
+         rs["on"], rs["rows"], rs["base"], rs["land"], _ll(rs["ld"]), _c.c_void_p(rs["counters"]),
+         _c.c_void_p(rs["local"]), _ll(rs["slot_stride"]), _P(rs["out"]), _ll(rs["out_ld"]),
+         _P(ce["labels"]), _ll(ce["vocab_start"]), _P(ce["tmax"]), _P(ce["tsum"]), _P(ce["tgt"]))
 
 
-def _ag_gemm(x_shard2, w, b_mn, bias, ws):
-    """gathered [T*Ls, K] (view of the workspace) and y = gathered @ (w^T or w)."""
+def _ag_gemm(x_shard2, w, b_mn, bias, ws, act=0, ce=None):
+    """gathered [T*Ls, K] (view of the workspace) and y = gathered @ (w^T or w).  `ce` = (labels [T*Ls] int64,
+    vocab_start): the epilogue also produces the cross-entropy statistics of the rows of y; returns
+    (gathered, y, (row max, row sum-exp, target logit)) then."""
     Ls, K = x_shard2.shape
     T = ws.nranks
     M = T * Ls
     N = w.shape[1] if b_mn else w.shape[0]
     CALLS["ag_gemm"] += 1
-    seq = ws.next_seq()
-    par = seq & 1
+    seq, par = ws.next_seq(symm.KIND_AG)
     off = ws.gather_offset(par)
     gathered = ws.local_view(off, M, K)
     y = torch.empty(M, _ceil8(N), dtype=torch.bfloat16, device=x_shard2.device)[:, :N]
-    if x_shard2.stride(1) != 1 or x_shard2.stride(0) % 8:
+    if x_shard2.stride(1) != 1 or x_shard2.stride(0) % 8 or x_shard2.data_ptr() % 16:
         x_shard2 = x_shard2.contiguous()
-    _fused_gemm(gathered, w, y, M, N, K, K, w.stride(0), y.stride(0), False, b_mn, 0, bias, ws, seq,
+    ced, stats = None, None
+    if ce is not None:
+        labels, vocab_start = ce
+        ced, stats = cuda_ops.ce_epilogue_buffers(M, N, K, labels, vocab_start)
+    _fused_gemm(gathered, w, y, M, N, K, K, w.stride(0), y.stride(0), False, b_mn, 0, bias, act, ws, seq,
                 ag=dict(on=1, rows=Ls, base=ws.flag_base(symm.KIND_AG, par), src=x_shard2, src_ld=x_shard2.stride(0),
-                        dst=ws.peer_ptrs(off), dst_ld=K, counter=ws.counter_ptr(0)))
+                        dst=ws.peer_ptrs(off), dst_ld=K, counter=ws.counter_ptr(0)), ce=ced)
+    if ce is not None:
+        return gathered, y, cuda_ops.ce_merge(ced, stats)
     return gathered, y
 
 
@@ -82,22 +91,16 @@ def _gemm_rs(a2, w, b_mn, ws):
     Ls = M // T
     N = w.shape[1] if b_mn else w.shape[0]
     CALLS["gemm_rs"] += 1
-    seq = ws.next_seq()
-    par = seq & 1
+    seq, par = ws.next_seq(symm.KIND_RS)
     off = ws.land_offset(par)
     slot_bytes = Ls * N * 2
     land = symm._ptr_array([p + off + ws.me * slot_bytes for p in ws.base_ptrs])
-    if a2.stride(1) != 1 or a2.stride(0) % 8:
-        a2 = a2.contiguous()
-    _fused_gemm(a2, w, None, M, N, K, a2.stride(0), w.stride(0), 0, False, b_mn, 3, None, ws, seq,
-                rs=dict(on=1, rows=Ls, base=ws.flag_base(symm.KIND_RS, par), land=land, ld=N,
-                        counters=ws.counter_ptr(8)))
+    if a2.stride(1) != 1 or a2.stride(0) % 8 or a2.data_ptr() % 16:
+        a2 = cuda_ops._as_operand(a2)
     out = torch.empty(Ls, N, dtype=torch.bfloat16, device=a2.device)
-    local_land = ws.local_view(off, T * Ls, N)
-    _run("ssm_reduce_partials", _P(local_land), _ll(N), _ll(Ls * N), _P(out), _ll(N), Ls, N, T,
-         _c.c_void_p(ws.base_ptrs[ws.me]), ws.flag_base(symm.KIND_RS, par), seq, _P(ws.seq_base),
-         _P(status_tensor(ws.device)),
-         min(148, max(1, Ls * N // 8 // 256)), _st())
+    _fused_gemm(a2, w, None, M, N, K, a2.stride(0), w.stride(0), 0, False, b_mn, 3, None, 0, ws, seq,
+                rs=dict(on=1, rows=Ls, base=ws.flag_base(symm.KIND_RS, par), land=land, ld=N,
+                        counters=ws.counter_ptr(8), local=ws.local_ptr(off), slot_stride=Ls * N, out=out, out_ld=N))
     return out
 
 
@@ -113,8 +116,7 @@ def small_allreduce(data: torch.Tensor, op: str = "sum") -> bool:
             or data.dtype != torch.float32 or not data.is_contiguous() or data.numel() > symm.SMALL_N_MAX):
         return False
     CALLS["small_allreduce"] = CALLS.get("small_allreduce", 0) + 1
-    seq = ws.next_seq()
-    par = seq & 1
+    seq, par = ws.next_seq(symm.KIND_AR)
     _run("ssm_small_allreduce", _P(data), data.numel(), symm.SMALL_N_MAX, ws.peer_ptrs(ws.slots_offset(par)),
          ws.flag_ptr_array, ws.flag_base(symm.KIND_AR, par), ws.nranks, ws.me, seq, _P(ws.seq_base),
          0 if op == "sum" else 1, _P(status_tensor(ws.device)), _st())
@@ -136,8 +138,7 @@ def allreduce_bf16(x: torch.Tensor):
     xc = x.contiguous()
     out = torch.empty_like(xc)
     CALLS["allreduce_bf16"] = CALLS.get("allreduce_bf16", 0) + 1
-    seq = ws.next_seq()
-    par = seq & 1
+    seq, par = ws.next_seq(symm.KIND_AG)
     stride = ws.gather_bytes // 2 // T // 8 * 8
     _run("ssm_allreduce_bf16", _P(xc), _P(out), _ll(n), ws.peer_ptrs(ws.gather_offset(par)), _ll(stride), T, ws.me,
          ws.flag_ptr_array, ws.flag_base(symm.KIND_AG, par), seq, _P(ws.seq_base), _c.c_void_p(ws.counter_ptr(34)),
@@ -159,8 +160,7 @@ class _VocabEmbedScatter(torch.autograd.Function):
         Ls = L // T
         ids_c = ids.contiguous()
         CALLS["vocab_embed"] = CALLS.get("vocab_embed", 0) + 1
-        seq = ws.next_seq()
-        par = seq & 1
+        seq, par = ws.next_seq(symm.KIND_EMB)
         off = ws.embed_offset(par)
         base = ws.flag_base(symm.KIND_EMB, par)
         _run("ssm_vocab_embed_push", _P(ids_c), _P(w), _ll(vocab_start), _ll(w.shape[0]), ws.peer_ptrs(off), B, L, Ls, D,
@@ -181,8 +181,7 @@ class _VocabEmbedScatter(torch.autograd.Function):
         g2 = g.reshape(B * Ls, D)
         if g2.stride(1) != 1 or g2.stride(0) % 8:
             g2 = g2.contiguous()
-        seq = ws.next_seq()
-        par = seq & 1
+        seq, par = ws.next_seq(symm.KIND_AG)
         off = ws.gather_offset(par)
         base = ws.flag_base(symm.KIND_AG, par)
         _run("ssm_push_shard", _P(g2), _ll(g2.stride(0)), ws.peer_ptrs(off), _ll(D), _ll(ws.me * B * Ls), B * Ls, D, T,
@@ -209,25 +208,34 @@ def vocab_embed_scatter(ids, w, vocab_start):
 
 
 def _shape_ok(Ls, K, N, ws):
-    return Ls % 128 == 0 and K % 8 == 0 and N % 8 == 0 and ws is not None
+    """Shard rows in whole 128-row tiles; K (the gathered / reduced inner extent that is moved in 16-byte vectors)
+    a multiple of 8.  N (output features of an all-gather GEMM) is free: edge tiles are masked, rows are padded to
+    a multiple of 8 elements by the callers."""
+    return Ls % 128 == 0 and K % 8 == 0 and N >= 1 and ws is not None
 
 
 class _AllGatherLinear(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, bias, ws):
+    def forward(ctx, x, w, bias, ws, ce_labels=None, ce_vocab_start=0):
         Ls, K = x.shape[1], x.shape[2]
-        gathered, y = _ag_gemm(x.reshape(Ls, K), w, False, bias, ws)
+        ce = None if ce_labels is None else (ce_labels, ce_vocab_start)
+        res = _ag_gemm(x.reshape(Ls, K), w, False, bias, ws, ce=ce)
+        gathered, y = res[0], res[1]
         xg = gathered.clone()                      # kept for dW; the workspace buffer is reused two calls later
         ctx.save_for_backward(xg, w)
         ctx.ws, ctx.has_bias = ws, bias is not None
-        return y.reshape(1, y.shape[0], w.shape[0])
+        y3 = y.as_strided((1, y.shape[0], w.shape[0]), (y.shape[0] * y.stride(0), y.stride(0), 1))
+        if ce is not None:
+            ctx.mark_non_differentiable(*res[2])
+            return (y3,) + tuple(res[2])
+        return y3
 
     @staticmethod
-    def backward(ctx, dy):
+    def backward(ctx, dy, *unused):
         xg, w = ctx.saved_tensors
         ws = ctx.ws
         N = w.shape[0]
-        dy2 = dy.reshape(-1, N)
+        dy2 = dy.reshape(-1, N) if dy.dim() != 2 else dy
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
             dx = _gemm_rs(dy2, w, True, ws)         # reduce_scatter(dY W)
@@ -237,7 +245,7 @@ class _AllGatherLinear(torch.autograd.Function):
                 dw = cuda_ops.gemm(dy2, xg, a_mn=True, b_mn=True).contiguous()
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = dy2.float().sum(0).to(dy.dtype)
-        return dx, dw, db, None
+        return dx, dw, db, None, None, None
 
 
 class _AllGatherMultiLinear(torch.autograd.Function):
@@ -309,14 +317,20 @@ class _Impl:
         return ready_for(x)
 
     @staticmethod
-    def all_gather_linear(x, w, bias=None):
+    def all_gather_linear(x, w, bias=None, ce=None):
         T = ps.get_tensor_model_parallel_size()
         Ls, K = x.shape[1], x.shape[2]
         ws = _ws_for(T * Ls, K, x.device)
         if not _shape_ok(Ls, K, w.shape[0], ws) or not ws.fits(T * Ls, K):
             from . import mappings as mp
             from .. import ops
-            return ops.linear(mp.gather_from_sequence_parallel_region(x, True), w, bias)
+            xg = mp.gather_from_sequence_parallel_region(x, True)
+            if ce is not None:
+                return ops.linear_ce(xg, w, ce[0], ce[1])
+            return ops.linear(xg, w, bias)
+        if ce is not None:
+            out = _AllGatherLinear.apply(x, w, bias, ws, ce[0], int(ce[1]))
+            return out[0], tuple(out[1:])
         return _AllGatherLinear.apply(x, w, bias, ws)
 
     @staticmethod

@@ -38,9 +38,13 @@ class GraphedTrainStep:
         self.optimizer.upload_learning_rates()
         from ..ops import cuda_ops
         before = cuda_ops.launch_count()
+        from . import symm
+        symm.start_recording()
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
             self.static_loss = self._eager_step()
+        rec = symm.stop_recording()
+        symm.check_replay_safe(rec + rec)          # double-buffer parities must survive back-to-back replays
         self.native_launches_per_step = cuda_ops.launch_count() - before   # native kernel nodes in the graph
         self.replays = 0
         self.optimizer.step_count -= 1     # capturing recorded a step without executing it
@@ -74,9 +78,7 @@ class GraphedAccumulationStep:
 
     `micro_step(batch)` replays `first` or `next` and returns the micro-step's loss divided by the number of
     micro-steps (device tensor, overwritten by the next call); after `grad_accum_usteps` micro-steps it replays
-    `update`.  The reference accumulates the same way with eager XLA steps (train.py:178-232).
-    Status: built from the pieces that `GraphedTrainStep` uses and checked for its bookkeeping on the host; it has
-    not been run on a GPU yet."""
+    `update`.  The reference accumulates the same way with eager XLA steps (train.py:178-232)."""
 
     def __init__(self, model, optimizer, example_batch: Dict[str, torch.Tensor], grad_accum_usteps: int,
                  loss_fn: Optional[Callable] = None, warmup: int = 1):
@@ -101,12 +103,20 @@ class GraphedAccumulationStep:
         self.g_first, self.g_next, self.g_update = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
         # capture in the order of a real step so that the host-side store/accumulate flags seen by each graph are
         # the ones it will meet at replay: first (gradients stale) -> next (accumulating) -> update
-        with torch.cuda.graph(self.g_first, pool=pool):
-            self.loss_first = self._micro()
-        with torch.cuda.graph(self.g_next, pool=pool):
-            self.loss_next = self._micro()
-        with torch.cuda.graph(self.g_update, pool=pool):
-            self._update()
+        from . import symm
+        kinds = []
+        for graph, body, name in ((self.g_first, self._micro, "loss_first"), (self.g_next, self._micro, "loss_next"),
+                                  (self.g_update, self._update, None)):
+            symm.start_recording()
+            with torch.cuda.graph(graph, pool=pool):
+                out = body()
+            kinds.append(symm.stop_recording())
+            if name:
+                setattr(self, name, out)
+        # replay order: first, next x (accum - 1), update, first, ...: the buffer parities fixed at capture must be
+        # safe for every succession that occurs, in particular `next` replayed back to back
+        first, nxt, upd = kinds
+        symm.check_replay_safe(first + nxt + nxt + upd + first + nxt + upd + first)
         self.optimizer.step_count -= 1           # capturing recorded an optimizer step without executing it
         self.eager_steps = warmup
 

@@ -129,7 +129,22 @@ class ColumnParallelLinear(nn.Module):
         else:
             self.register_parameter("bias", None)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, ce_labels: Optional[torch.Tensor] = None):
+        """`ce_labels` (global ids, one per output row of the full sequence; negative = ignored) turns the layer into
+        an LM head that also returns the cross-entropy statistics of its logits, taken in the GEMM epilogue where
+        the kernels support it: the result is then `(y, statistics or None)`."""
+        if ce_labels is not None:
+            if self.bias is not None or self.gather_output:
+                raise ValueError("cross-entropy statistics need a bias-free layer without gathered output")
+            vocab_start = ps.get_tensor_model_parallel_rank() * self.output_size_per_partition
+            if self.sequence_parallel_enabled:
+                from . import fused
+                if fused.enabled_for(x):
+                    return fused.all_gather_linear(x, self.weight, None, ce=(ce_labels, vocab_start))
+                xg = mp.gather_from_sequence_parallel_region(x, True)
+            else:
+                xg = mp.copy_to_tensor_parallel_region(x)
+            return ops.linear_ce(xg, self.weight, ce_labels, vocab_start)
         if self.sequence_parallel_enabled:
             from . import fused
             if fused.enabled_for(x):

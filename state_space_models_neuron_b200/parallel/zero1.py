@@ -10,7 +10,10 @@ Replaces what the reference obtains from `nxd.initialize_parallel_optimizer(...)
   * with `shard=False` the same code is plain data parallelism (all-reduce, full state everywhere).
 The flat layout orders parameters as [TP-sharded | TP-replicated] x [decay | no decay] so that every
 rank's shard is a handful of homogeneous segments; the AdamW update and the norm run as one fused
-kernel per segment on GPUs (`ops/csrc/optim.cu`) and as torch ops on CPU.
+kernel per segment on GPUs (`adamw_kernel` / `sumsq_kernel` in `ops/csrc/elementwise.cu`, the peer-memory
+variants `zero1_*` in `ops/csrc/comm.cu`) and as torch ops on CPU.
+A step whose gradient norm is not finite is skipped on the device (no host synchronisation): the clip coefficient
+becomes negative, the AdamW kernels leave parameters and moments untouched, and `skipped_steps()` counts it.
 """
 from __future__ import annotations
 
@@ -136,6 +139,7 @@ class Zero1Optimizer(torch.optim.Optimizer):
         # device-resident step counter and per-group learning rates (read by the fused AdamW kernel, so a captured
         # CUDA graph of the step keeps working when the scheduler changes the rate)
         self._dev_step = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._dev_skipped = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._dev_lr = torch.zeros(max(1, len(self.param_groups)), dtype=torch.float32, device=self.device)
         self._host_lr = torch.zeros(max(1, len(self.param_groups)), dtype=torch.float32,
                                     pin_memory=self.device.type == "cuda")
@@ -315,15 +319,14 @@ class Zero1Optimizer(torch.optim.Optimizer):
         self._finish_lazy_zero()
         self._allreduce_sequence_parallel_grads()
         self.step_count += 1
-        self._dev_step.add_(1)
         if self._fused_dp:
             return self._fused_step()
         g = self._reduce_gradients()
-        clip = torch.ones(1, dtype=torch.float32, device=self.device)
-        if self.max_grad_norm is not None:
-            norm = torch.sqrt(self._grad_norm_sq(g))
-            self.last_grad_norm = norm
-            clip = torch.clamp(self.max_grad_norm / (norm + 1e-6), max=1.0)
+        clip = self._clip_coefficient(lambda: self._grad_norm_sq(g))
+        from ..ops.functional import _native
+        if not _native(self.master) and float(clip) < 0:
+            self.step_count -= 1             # non-finite gradients: skip the update (decided on the host here)
+            return None
         s = self.shard_start
         out = self.flat_params[s:s + self.shard_size]
         for lo, hi, gi, rep in self.segments:
@@ -339,6 +342,25 @@ class Zero1Optimizer(torch.optim.Optimizer):
             from . import symm
             symm.advance_step()
         return None
+
+    def _clip_coefficient(self, norm_sq_fn) -> torch.Tensor:
+        """Clip coefficient min(1, max_norm / norm) as a device scalar; -1 when the norm is not finite, which makes
+        the AdamW kernels skip the step.  Also advances the device-side step counter (only for steps that are
+        applied, so the bias correction stays exact) and the skipped-step counter."""
+        if self.max_grad_norm is None:
+            self._dev_step.add_(1)
+            return torch.ones(1, dtype=torch.float32, device=self.device)
+        norm = torch.sqrt(norm_sq_fn()).reshape(1)
+        self.last_grad_norm = norm
+        finite = torch.isfinite(norm)
+        clip = torch.where(finite, torch.clamp(self.max_grad_norm / (norm + 1e-6), max=1.0), -torch.ones_like(norm))
+        self._dev_step.add_(finite.to(torch.int32))
+        self._dev_skipped.add_((~finite).to(torch.int32))
+        return clip
+
+    def skipped_steps(self) -> int:
+        """Optimizer steps skipped so far because the gradient norm was not finite (reads the device counter)."""
+        return int(self._dev_skipped.item())
 
     def _fused_step(self):
         """reduce-scatter(+1/dp, +norm partial) -> clip -> AdamW(+push of bf16 params to every rank) -> wait."""
@@ -357,16 +379,13 @@ class Zero1Optimizer(torch.optim.Optimizer):
         _run("ssm_zero1_reduce", arr(self._peer_grads), _P(g), _ll(self.shard_start), _ll(self.shard_size), self.dp_size,
              self.dp_rank, ctypes.c_float(1.0 / self.dp_size), _P(total if fused_norm else None), arr(self._peer_flags),
              0, 1, _P(self._zseq_base), _P(st), _st())
-        clip = torch.ones(1, dtype=torch.float32, device=self.device)
-        if self.max_grad_norm is not None:
+        def norm_sq():
             if fused_norm:
                 dist.all_reduce(total, group=self.dp_group)
-            else:
-                total = self._grad_norm_sq(g)
-            norm = torch.sqrt(total)
-            self.last_grad_norm = norm
-            clip = torch.clamp(self.max_grad_norm / (norm + 1e-6), max=1.0)
-        else:
+                return total
+            return self._grad_norm_sq(g)
+        clip = self._clip_coefficient(norm_sq)
+        if self.max_grad_norm is None:
             dist.barrier(group=self.dp_group)     # peers must finish reading gradients before the next backward
         for k, (lo, hi, gi, rep) in enumerate(self.segments):
             grp = self.param_groups[gi]
@@ -380,7 +399,7 @@ class Zero1Optimizer(torch.optim.Optimizer):
                  _P(self._zcounter), int(last), _st())
         _run("ssm_zero1_wait", ctypes.c_void_p(self._peer_flags[self.dp_rank]), 16, self.dp_size, 2,
              _P(self._zseq_base), _P(st), _st())
-        _run("ssm_advance_counter", _P(self._zseq_base), 4, _st())
+        _run("ssm_advance_counter", _P(self._zseq_base), 4, ctypes.c_void_p(self._peer_flags[self.dp_rank]), 64, _st())
         if self.tp_size > 1:
             from . import symm
             symm.advance_step()

@@ -7,8 +7,9 @@ simulator its tests use, tests/mamba2_kernel_test_no_tp.py:48):
     protocol races and uninitialised reads show up as run-to-run differences.
   * `check_finite`: NaN/Inf check with a named error (the reference's decode script does this by hand,
     mamba2_inference_no_tp.py:104-106).
-  * `tile_schedule_is_permutation`: host-side check of the GEMM tile visiting order used by the fused
-    collectives (every tile visited exactly once for every rank rotation).
+  * `tile_schedule_is_permutation`, `gemm_schedule_covers_once`: host-side models of the GEMM's tile visiting
+    order under the fused collectives' rotations and of its full-wave / K-split tail work distribution, for
+    property tests of the index arithmetic (every tile and k-block computed exactly once).
 """
 from __future__ import annotations
 
@@ -51,19 +52,74 @@ def check_finite(t: torch.Tensor, name: str = "tensor") -> None:
         raise FloatingPointError(f"{name} has {bad} non-finite values")
 
 
-def rotate_m(tm: int, tiles_m: int, tiles_per_block: int, first_block: int) -> int:
-    """Host copy of the device tile rotation (ops/csrc/gemm.cu `rotate_m`)."""
-    v = tm + first_block * tiles_per_block
+def rotate_m(tm: int, tiles_m: int, first: int) -> int:
+    """Host copy of the device tile rotation (ops/csrc/gemm.cu `rotate_m`): m-tile `first` is visited first."""
+    v = tm + first
     return v - tiles_m if v >= tiles_m else v
 
 
+def gemm_schedule(tiles: int, max_units: int, kblocks: int, accumulate: bool = False, split_enabled: bool = True):
+    """Host copy of the GEMM's work distribution (ops/csrc/gemm.cu `launch_gemm` + `get_work`): returns
+    (units, [(unit, tile, kb0, kb1, slice, nslices)]).  Whole tiles go round-robin over the units for as many full
+    waves as there are; the tiles of the last partial wave are cut into K slices, one per otherwise idle unit."""
+    units = min(tiles, max_units)
+    full = (tiles // units) * units
+    rem = tiles - full
+    split = 1
+    if split_enabled and (rem > 0 or tiles < max_units):
+        if tiles < max_units:
+            units, full, rem = max_units, 0, tiles
+        split = units // rem
+        split = min(split, 8 if accumulate else 4, kblocks // 4)
+        split = max(split, 1)
+        if tiles < max_units:
+            units = rem * split
+    work = []
+    for unit in range(units):
+        it = 0
+        while True:
+            idx = unit + it * units
+            if idx < full:
+                work.append((unit, idx, 0, kblocks, 0, 1))
+            elif it == full // units and unit < rem * split:
+                tail = unit // split
+                sl = unit - tail * split
+                work.append((unit, full + tail, sl * kblocks // split, (sl + 1) * kblocks // split, sl, split))
+            else:
+                break
+            it += 1
+    return units, work
+
+
+def gemm_schedule_covers_once(tiles: int, max_units: int, kblocks: int, accumulate: bool = False) -> bool:
+    """Every (tile, k-block) is computed exactly once, no unit gets two pieces of the tail, and no slice is empty."""
+    units, work = gemm_schedule(tiles, max_units, kblocks, accumulate)
+    seen = {}
+    tail_units = set()
+    for unit, tile, kb0, kb1, sl, n in work:
+        if kb1 <= kb0 or unit >= units:
+            return False
+        if n > 1:
+            if unit in tail_units:
+                return False
+            tail_units.add(unit)
+        for kb in range(kb0, kb1):
+            if (tile, kb) in seen:
+                return False
+            seen[(tile, kb)] = unit
+    return len(seen) == tiles * kblocks
+
+
 def tile_schedule_is_permutation(tiles_m: int, tiles_n: int, nranks: int, ctas: int) -> bool:
+    """The rotated m-tile order of the fused collectives (local shard first for the all-gather, next rank's rows
+    first for the reduce-scatter) still visits every tile exactly once for every rank."""
     per = tiles_m // nranks
     for me in range(nranks):
-        seen = set()
-        for cta in range(ctas):
-            for tile in range(cta, tiles_m * tiles_n, ctas):
-                seen.add((rotate_m(tile % tiles_m, tiles_m, per, me), tile // tiles_m))
-        if len(seen) != tiles_m * tiles_n:
-            return False
+        for first in (me * per, ((me + 1) % nranks) * per):
+            seen = set()
+            for cta in range(ctas):
+                for tile in range(cta, tiles_m * tiles_n, ctas):
+                    seen.add((rotate_m(tile % tiles_m, tiles_m, first), tile // tiles_m))
+            if len(seen) != tiles_m * tiles_n:
+                return False
     return True

@@ -89,6 +89,25 @@ def test_debug_helpers():
     assert debug.tile_schedule_is_permutation(16, 10, 8, 132) and debug.tile_schedule_is_permutation(16, 16, 2, 148)
 
 
+def test_gemm_schedule_covers_every_k_block_once():
+    """Property test of the GEMM work distribution (full waves + K-split tail), the host model of the index
+    arithmetic in ops/csrc/gemm.cu: the shapes of the training step and a random sweep."""
+    from hypothesis import given, settings, strategies as st
+    from state_space_models_neuron_b200.utils import debug
+    for tiles, units, kb in [(160, 148, 64), (80, 74, 64), (208, 148, 64), (20, 148, 80), (1, 148, 3), (148, 148, 16),
+                             (149, 148, 16), (295, 148, 1), (6, 74, 5), (73, 74, 4), (75, 74, 8)]:
+        assert debug.gemm_schedule_covers_once(tiles, units, kb), (tiles, units, kb)
+        assert debug.gemm_schedule_covers_once(tiles, units, kb, accumulate=True), (tiles, units, kb)
+    units, work = debug.gemm_schedule(80, 74, 64)
+    assert units == 74 and sum(1 for w in work if w[5] > 1) == 24 and max(w[5] for w in work) == 4
+
+    @settings(max_examples=300, deadline=None)
+    @given(st.integers(1, 2000), st.sampled_from([1, 2, 37, 74, 132, 148, 160]), st.integers(1, 300), st.booleans())
+    def prop(tiles, units, kb, acc):
+        assert debug.gemm_schedule_covers_once(tiles, units, kb, acc)
+    prop()
+
+
 def test_ncu_command_always_leaves_clocks_alone():
     from state_space_models_neuron_b200.utils.profiling import ncu_command
     cmd = ncu_command(["python", "bench.py", "--small"], "gemm_bf16", launches=2, skip=1, out="x/prof")
@@ -100,19 +119,79 @@ def test_ncu_command_always_leaves_clocks_alone():
 
 def test_fused_sequence_numbers_advance_on_their_own(monkeypatch):
     """Gradient accumulation makes far more than 65536 fused collective calls between optimizer steps: the
-    workspace starts a new block of sequence numbers by itself instead of failing, at the same call on every rank."""
+    workspace starts a new block of sequence numbers by itself instead of failing, at the same call on every rank.
+    Buffer parity alternates per kind and is not reset when a new block starts."""
     from state_space_models_neuron_b200.ops import cuda_ops
     from state_space_models_neuron_b200.parallel import symm
     launched = []
     monkeypatch.setattr(cuda_ops, "_run", lambda name, *a: launched.append((name, a[1])))
     monkeypatch.setattr(cuda_ops, "_st", lambda: None)
     ws = symm.SymmWorkspace.__new__(symm.SymmWorkspace)
-    ws.seq, ws.seq_base = 0, torch.zeros(1, dtype=torch.int32)
-    positions = [ws.next_seq() for _ in range(150000)]
+    symm.SeqCounter.__init__(ws)
+    ws.seq_base, ws.base_ptrs, ws.me = torch.zeros(1, dtype=torch.int32), [0], 0
+    got = [ws.next_seq(symm.KIND_AG if i % 3 else symm.KIND_RS) for i in range(150000)]
+    positions = [s for s, _ in got]
     assert min(positions) == 1 and max(positions) < symm.SymmWorkspace.STEP_STRIDE
     assert [n for n, _ in launched] == ["ssm_advance_counter"] * 2 and all(s == symm.SymmWorkspace.STEP_STRIDE for _, s in launched)
+    for kind in (symm.KIND_AG, symm.KIND_RS):
+        pars = [p for i, (_, p) in enumerate(got) if (symm.KIND_AG if i % 3 else symm.KIND_RS) == kind]
+        assert pars[:4] == [0, 1, 0, 1] and all(a != b for a, b in zip(pars, pars[1:]))
+    last_par = ws.kind_calls[symm.KIND_AG] & 1
     ws.advance_step()
-    assert ws.seq == 0 and ws.next_seq() == 1
+    assert ws.seq == 0 and ws.next_seq(symm.KIND_AG) == (1, last_par)
+    ws.next_seq(symm.KIND_AG)
+    ws.next_seq(symm.KIND_AG)
+    ws.advance_step(compact=True)
+    assert launched[-1] == ("ssm_advance_counter", 4)          # 3 calls -> next even number above them
+
+
+def test_sequence_compare_is_wrap_safe():
+    """The kernels decide "flag has reached seq" by the signed 32-bit distance.  Model of that arithmetic: it holds
+    across the wrap from 2^31 - 1 to -2^31 and for every gap below 2^31; a flag that lags more than 2^29 behind is
+    pulled up to the base when the base crosses a multiple of 2^29, and a base value never satisfies a wait of its
+    own block."""
+    def i32(x):
+        return (x + 2 ** 31) % 2 ** 32 - 2 ** 31
+
+    def reached(flag, seq):
+        return i32(flag - seq) >= 0
+
+    for base in (0, 2 ** 31 - 70000, 2 ** 31 - 3, -2 ** 31 + 5, -70000, 2 ** 32 - 10):
+        for pos in (1, 2, 65533):
+            seq = i32(base + pos)
+            assert reached(seq, seq) and reached(i32(seq + 1), seq) and reached(i32(seq + 65536 * 3), seq)
+            assert not reached(i32(seq - 1), seq) and not reached(i32(base), seq)
+            assert not reached(i32(seq - 65536 * 1000), seq)
+
+    def advance(base, stride, flags):             # advance_counter_kernel
+        old, new = base % 2 ** 32, (base + stride) % 2 ** 32
+        if (old >> 29) != (new >> 29):
+            flags = [i32(new) if i32(new - f) > 2 ** 29 else f for f in flags]
+        return i32(new), flags
+
+    base, flags = 0, [0, 0]                      # flag 0 is in use every step, flag 1 never
+    for step in range(70000):                    # more than one full trip around the 32-bit range
+        seq = i32(base + 7)
+        assert not reached(flags[1], seq), step   # an idle flag must never look "arrived"
+        flags[0] = seq
+        base, flags = advance(base, 65536, flags)
+
+
+def test_replay_safety_check():
+    from state_space_models_neuron_b200.parallel import symm
+    AG, RS, AR = symm.KIND_AG, symm.KIND_RS, symm.KIND_AR
+    c = symm.SeqCounter()
+    c.recording = []
+    for k in (AG, RS, RS, AG, RS, AG, AR):               # odd counts per kind, other collectives in between
+        c.take(k)
+    rec = c.recording
+    assert rec[0] == (AG, 0) and rec[3] == (AG, 1) and rec[5] == (AG, 0)
+    symm.check_replay_safe(rec + rec)
+    symm.check_replay_safe([(AG, 0), (AG, 1)] * 2)         # alternating buffers back to back are fine
+    with pytest.raises(RuntimeError):
+        symm.check_replay_safe([(AG, 0)] * 2)              # the same buffer back to back across replays
+    with pytest.raises(RuntimeError):
+        symm.check_replay_safe([(RS, 1), (AG, 0), (AG, 1), (AG, 1)])
 
 
 def test_symmetric_workspace_regions_do_not_overlap():
@@ -123,9 +202,9 @@ def test_symmetric_workspace_regions_do_not_overlap():
         ws = symm.SymmWorkspace.__new__(symm.SymmWorkspace)
         ws.nranks, ws.rows_total, ws.cols = nranks, rows, cols
         elems = rows * cols
-        ws.gather_bytes, ws.flags_bytes = elems * 2, 4096
+        ws.gather_bytes, ws.flags_bytes = (elems * 2 + 1023) // 1024 * 1024, 4096
         ws.slots_bytes = 2 * symm.MAX_RANKS * symm.SMALL_N_MAX * 4
-        ws.embed_bytes = (-(-elems // nranks) * 2 + 255) // 256 * 256
+        ws.embed_bytes = (-(-elems // nranks) * 2 + 1023) // 1024 * 1024
         total = ws.flags_bytes + 4 * ws.gather_bytes + ws.slots_bytes + 2 * ws.embed_bytes
         regions = [(0, ws.flags_bytes)]
         regions += [(ws.gather_offset(p), ws.gather_bytes) for p in (0, 1)]
@@ -137,5 +216,5 @@ def test_symmetric_workspace_regions_do_not_overlap():
             assert off >= end and off % 16 == 0, (nranks, off, end)
             end = off + size
         assert end <= total
-        # flag words of the four kinds x two parities x eight sources fit in the flag page
-        assert (symm.KIND_EMB * 2 + 1) * symm.MAX_RANKS + symm.MAX_RANKS <= ws.flags_bytes // 4
+        # flag words of the four kinds x two parities x (eight sources x four row groups) fit in the flag page
+        assert ws.flag_base(symm.KIND_EMB, 1) + symm.FLAG_SLOTS == symm.N_FLAGS <= ws.flags_bytes // 4

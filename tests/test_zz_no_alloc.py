@@ -70,3 +70,29 @@ def test_no_alloc_entry_point_rejects_oversize():
     w = torch.ones(D, device="cuda", dtype=torch.bfloat16)
     code, _, _ = _noalloc(res, w, res, res, 1e-5)
     assert code == -4
+
+
+def test_no_alloc_entry_point_rejects_misaligned_pointers():
+    """A row pointer that is not 16-byte aligned must come back as a bad-argument code; nothing is launched."""
+    from state_space_models_neuron_b200.ops import native
+    torch.cuda.set_device(0)
+    lib = native.lib()
+    fn = lib.ssm_add_rmsnorm_bwd_noalloc
+    fn.restype = ctypes.c_int
+    rows, D = 4, 256
+    buf = torch.zeros(rows * D + 8, device="cuda", dtype=torch.bfloat16)
+    ok = buf[:rows * D]
+    odd = buf[1:rows * D + 1]                      # starts 2 bytes past a 16-byte boundary
+    w = torch.ones(D, device="cuda", dtype=torch.bfloat16)
+    dw = torch.zeros(D, device="cuda", dtype=torch.float32)
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def call(res, dout, dsum):
+        return fn(ctypes.c_void_p(res.data_ptr()), ctypes.c_void_p(w.data_ptr()), ctypes.c_void_p(dout.data_ptr()),
+                  ctypes.c_void_p(0), ctypes.c_void_p(dsum.data_ptr()), ctypes.c_void_p(dw.data_ptr()),
+                  ctypes.c_longlong(rows), D, ctypes.c_float(1e-5), 0, st)
+
+    out = torch.zeros(rows * D, device="cuda", dtype=torch.bfloat16)
+    assert call(odd, ok, out) == -3
+    assert call(ok, odd, out) == -3
+    assert call(ok, ok, odd) == -3

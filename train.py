@@ -8,7 +8,10 @@ warm-up, `LOG` lines from rank 0, periodic sharded checkpoints.  Launch one proc
         --sequence_parallel_enabled --dtype bfloat16 --data_dir DATA ...
 
 Additions: --synthetic_data, --n_groups, --head_dim, --fused_comm, --resume (optimizer + scheduler +
-step, where the reference restores the model only), --profile.
+step, where the reference restores the model only), --profile, --cuda_graph, --heartbeat_timeout.
+Between steps the loop reads the kernels' status word (a bounded wait that ran out raises here and no checkpoint
+is written from such a state), polls a heartbeat of the other ranks, and reports optimizer steps that were skipped
+on the device because the gradient norm was not finite.
 """
 from __future__ import annotations
 
@@ -117,91 +120,113 @@ def run(args):
         from state_space_models_neuron_b200.utils.profiling import StepProfiler
         prof = StepProfiler(args.output_dir)
 
+    # ---- failure detection: host-side, between steps (no kernel or collective of this rank is in flight then)
+    from state_space_models_neuron_b200.utils.failure import Heartbeat, RankFailure
+    heartbeat = None
+    if dist.is_initialized() and ps.get_world_size() > 1 and args.heartbeat_timeout > 0:
+        store = getattr(dist.distributed_c10d, "_get_default_store", lambda: None)()
+        if store is not None:
+            heartbeat = Heartbeat(store, ps.get_rank(), ps.get_world_size(), period_s=min(1.0, args.heartbeat_timeout / 4),
+                                  timeout_s=args.heartbeat_timeout).start()
+
+    def health_check():
+        """Raise if a bounded device-side wait ran out (a fused collective never completed) or a peer stopped
+        answering; called at every logging interval and before every checkpoint, never with work in flight that
+        this call would not wait for."""
+        if use_cuda:
+            from state_space_models_neuron_b200.ops import cuda_ops
+            torch.cuda.synchronize()
+            cuda_ops.check_status()
+        if heartbeat is not None:
+            heartbeat.check()
+
+    if args.cuda_graph and not use_cuda:
+        raise SystemExit("--cuda_graph needs a CUDA device")
+    # With --cuda_graph the first optimizer steps run eagerly on their own batches (they are ordinary training
+    # steps: allocator, workspaces and kernel attributes settle, data order and step count stay those of an eager
+    # run), then the step is captured once and replayed.
+    graph_after = global_step + 2 if args.cuda_graph else None
     graphed = None
-    if args.cuda_graph:
-        if not use_cuda:
-            raise SystemExit("--cuda_graph needs a CUDA device")
+    skipped_reported = 0
+
+    def finish_optimizer_step(reduced, dev_timer=True):
+        """Bookkeeping after an optimizer step: schedule, logging, health check, checkpoint."""
+        nonlocal global_step, skipped_reported
+        scheduler.step()
+        global_step += 1
+        if prof is not None:
+            prof.step()
+        logging_now = global_step % args.logging_interval == 0
+        saving_now = args.checkpoint_freq > 0 and global_step % args.checkpoint_freq == 0
+        if logging_now or saving_now:
+            health_check()
+        if is_root and logging_now:
+            dev_time = None
+            if use_cuda:
+                ev_end.record()
+                ev_end.synchronize()
+                dev_time = ev_start.elapsed_time(ev_end) / 1e3 / args.logging_interval
+                ev_start.record()
+            step_time, tput, mfu = throughput.get_throughput()
+            gn = optimizer.last_grad_norm
+            logger.log(global_step, reduced.item(), optimizer.param_groups[0]["lr"], step_time, tput, mfu,
+                       tokens_per_s=tput * args.seq_len, device_step_time=dev_time,
+                       grad_norm=None if gn is None else float(gn))
+            skipped = optimizer.skipped_steps() if hasattr(optimizer, "skipped_steps") else 0
+            if skipped > skipped_reported:
+                print(f"LOG WARNING {skipped - skipped_reported} optimizer step(s) skipped: non-finite gradient norm "
+                      f"(total {skipped})", flush=True)
+                skipped_reported = skipped
+        if saving_now:
+            save(global_step)
+
     done = global_step >= args.max_steps
     # a resumed run continues with the batch that the interrupted run would have seen next
     skip_batches = global_step * args.grad_accum_usteps if args.resume else 0
-    while not done:
-        for data in device_loader:
-            if skip_batches > 0:
-                skip_batches -= 1
-                continue
-            training_step += 1
-            if args.cuda_graph:
-                if graphed is None:
-                    from state_space_models_neuron_b200.parallel.graph import GraphedAccumulationStep, GraphedTrainStep
+    try:
+        while not done:
+            for data in device_loader:
+                if skip_batches > 0:
+                    skip_batches -= 1
+                    continue
+                training_step += 1
+                boundary = training_step % args.grad_accum_usteps == 0
+                if graph_after is not None and global_step >= graph_after:
+                    if graphed is None:
+                        from state_space_models_neuron_b200.parallel.graph import GraphedAccumulationStep, GraphedTrainStep
+                        if args.grad_accum_usteps == 1:
+                            graphed = GraphedTrainStep(model, optimizer, data, warmup=0)
+                        else:       # one graph per kind of micro-step plus one for the update
+                            graphed = GraphedAccumulationStep(model, optimizer, data, args.grad_accum_usteps, warmup=0)
                     if args.grad_accum_usteps == 1:
-                        graphed = GraphedTrainStep(model, optimizer, data, warmup=2)
-                    else:       # one graph per kind of micro-step plus one for the update
-                        graphed = GraphedAccumulationStep(model, optimizer, data, args.grad_accum_usteps, warmup=1)
-                    global_step += graphed.eager_steps
-                    for _ in range(graphed.eager_steps):
-                        scheduler.step()
-                if args.grad_accum_usteps == 1:
-                    running_loss += graphed(data)
+                        running_loss += graphed(data)
+                    else:
+                        running_loss += graphed.micro_step(data)
                 else:
-                    running_loss += graphed.micro_step(data)
-                    if not graphed.at_step_boundary:
-                        continue
-                reduced = running_loss / dp_size
-                if dp_size > 1:
-                    dist.all_reduce(reduced, group=ps.get_data_parallel_group())
-                reduced = reduced.clone()
-                running_loss.zero_()
-                scheduler.step()
-                global_step += 1
-                if is_root and global_step % args.logging_interval == 0:
-                    ev_end.record()
-                    ev_end.synchronize()
-                    dev_time = ev_start.elapsed_time(ev_end) / 1e3 / args.logging_interval
-                    ev_start.record()
-                    step_time, tput, mfu = throughput.get_throughput()
-                    logger.log(global_step, reduced.item(), optimizer.param_groups[0]["lr"], step_time, tput, mfu,
-                               tokens_per_s=tput * args.seq_len, device_step_time=dev_time)
-                if args.checkpoint_freq > 0 and global_step % args.checkpoint_freq == 0:
-                    save(global_step)
+                    out = model(input_ids=data["input_ids"], labels=data["labels"], return_logits=False)
+                    loss = out.loss / args.grad_accum_usteps
+                    loss.backward()
+                    running_loss += loss.detach()
+                    if boundary:
+                        optimizer.step()
+                        optimizer.zero_grad()
+                if boundary:
+                    reduced = running_loss / dp_size
+                    if dp_size > 1:
+                        dist.all_reduce(reduced, group=ps.get_data_parallel_group())
+                    reduced = reduced.clone()
+                    running_loss.zero_()
+                    finish_optimizer_step(reduced)
                 if global_step >= args.max_steps:
                     done = True
                     break
-                continue
-            out = model(input_ids=data["input_ids"], labels=data["labels"], return_logits=False)
-            loss = out.loss / args.grad_accum_usteps
-            loss.backward()
-            running_loss += loss.detach()
-            if training_step % args.grad_accum_usteps == 0:
-                reduced = running_loss / dp_size
-                if dp_size > 1:
-                    dist.all_reduce(reduced, group=ps.get_data_parallel_group())
-                reduced = reduced.clone()
-                running_loss.zero_()
-                optimizer.step()
-                optimizer.zero_grad()
-                scheduler.step()
-                global_step += 1
-                if prof is not None:
-                    prof.step()
-                if is_root and global_step % args.logging_interval == 0:
-                    dev_time = None
-                    if use_cuda:
-                        ev_end.record()
-                        ev_end.synchronize()
-                        dev_time = ev_start.elapsed_time(ev_end) / 1e3 / args.logging_interval
-                        ev_start.record()
-                    step_time, tput, mfu = throughput.get_throughput()
-                    gn = optimizer.last_grad_norm
-                    logger.log(global_step, reduced.item(), optimizer.param_groups[0]["lr"], step_time, tput, mfu,
-                               tokens_per_s=tput * args.seq_len, device_step_time=dev_time,
-                               grad_norm=None if gn is None else float(gn))
-                if args.checkpoint_freq > 0 and global_step % args.checkpoint_freq == 0:
-                    save(global_step)
-            if global_step >= args.max_steps:
-                done = True
-                break
-    if args.save_last_step and (args.checkpoint_freq <= 0 or global_step % args.checkpoint_freq):
-        save(global_step)
+        if args.save_last_step and (args.checkpoint_freq <= 0 or global_step % args.checkpoint_freq):
+            health_check()
+            save(global_step)
+        health_check()
+    finally:
+        if heartbeat is not None:
+            heartbeat.stop()
     if is_root:
         logger.close()
     ps.barrier()
@@ -253,9 +278,12 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--profile", action="store_true")
     p.add_argument("--cuda_graph", action="store_true",
                    help="capture the whole optimizer step (fwd+bwd+collectives+AdamW) in one CUDA graph and replay it; "
-                        "with --grad_accum_usteps > 1: one graph per kind of micro-step plus one for the update "
-                        "(that variant has not been run on a GPU yet)")
+                        "with --grad_accum_usteps > 1: one graph per kind of micro-step plus one for the update; the "
+                        "first two optimizer steps run eagerly")
     p.add_argument("--device", default=None)
+    p.add_argument("--heartbeat_timeout", type=float, default=60.0,
+                   help="seconds without a heartbeat after which a peer rank counts as dead (checked between steps at "
+                        "every logging interval and before checkpoints); 0 turns the heartbeat off")
     return p
 
 
