@@ -62,7 +62,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t) :: "memory");      // not to be moved across barriers
   return t;
 }
 // Bounded wait: gives up after SSM_WAIT_NS nanoseconds (or when another thread already recorded an

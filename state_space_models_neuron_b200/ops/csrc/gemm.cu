@@ -5,7 +5,7 @@
 //     warps 2..5  epilogue: tcgen05.ld -> bf16 (plain, or +bias / GELU) -> swizzled smem -> TMA store,
 //                 or fp32 TMA store / TMA reduce-add for gradient outputs (optionally adding sum(C^2) to a scalar),
 //                 or TMA stores into the peers' landing zones (reduce-scatter);
-//                 in the all-gather variant the same warps first push this rank's shard to the peers
+//                 in the all-gather variant their first thread first pushes this rank's shard to the peers
 //     warp 6      second TMA producer: the B loads of every stage
 // Two accumulator stages in TMEM let the epilogue of tile i overlap the main loop of tile i+1.
 //
@@ -61,6 +61,7 @@ struct GemmParams {
   // are cut into `split` K slices each, one slice per unit
   int units, full_tiles, rem, split;
   float* ws;             // scratch for partial sums of split tiles: [rem][split][CTAs per unit][128 x BN] fp32
+                         // (rem * split <= units, so it never exceeds one 128 x 256 block per CTA of the grid)
   int* ws_counters;      // [rem][CTAs per unit] arrival counters (zero between launches)
   // cross-entropy statistics of the rows of C (mode 0, LM head): per n-tile (max, sum exp(x - max)) of the bf16-rounded
   // logits and the logit at the row's label
@@ -76,16 +77,19 @@ struct PeerPtrs { void* p[MAX_RANKS]; };
 
 // Fusion of the GEMM with the tensor-parallel collectives over peer memory.
 //  * all-gather side (ag): the A operand is a gather buffer [nranks * rows_per_shard, K] in local memory that
-//    every rank fills by pushing its shard into all ranks' buffers.  The epilogue warps of every CTA push a slice
-//    of each row group of the local shard (P2P stores) before they turn to their tiles; the CTA that completes a
-//    group publishes flag[me][group] = seq on every rank.  Meanwhile the producer and MMA warps already work: tiles
-//    of the local shard read the shard itself (second tensor map), tiles of a remote shard wait (bounded) for the
-//    flag of exactly the row group they read, so a remote group is consumed as soon as its bytes have landed.
+//    every rank fills by pushing its shard into all ranks' buffers.  One thread per CTA moves boxes of the local
+//    shard through shared memory (TMA load, then one TMA store per destination rank over NVLink) before the
+//    epilogue warps turn to their tiles; the CTA that completes a row group publishes flag[me][group] = seq on
+//    every rank.  Meanwhile the producer and MMA warps already work: tiles of the local shard read the shard
+//    itself (second tensor map), tiles of a remote shard wait (bounded) for the flag of exactly the row group they
+//    read, so a remote group is consumed as soon as its bytes have landed.  (No TMA load touches peer memory.)
 //  * reduce-scatter side (rs, epilogue mode 3): output rows belong to owner = row / rows_per_owner; each tile is
 //    TMA-stored into the owner's landing slot for this rank (one tensor map per owner, peer memory), remote
 //    owners first; when all of this rank's tiles for an owner have landed, flag[me] = seq is published there.
-//    With rs_out set the kernel also finishes the collective: after its tiles every CTA waits (bounded) for the
-//    flags of all sources and sums a slice of the landing slots into rs_out (fp32 accumulate, bf16 result).
+//    Tiles are visited owner by owner, this rank's own rows last.  With rs_out set the kernel also finishes the
+//    collective: the epilogue of a tile of this rank's own rows waits (bounded, once) for the flags of the other
+//    sources, adds their partial blocks from the landing zone to its fp32 accumulators and stores the reduced
+//    rows into rs_out; nothing of this rank's own partial ever takes the detour through the landing zone.
 struct GemmComm {
   int nranks, me, seq;          // sequence number of this call = *seq_base + seq (seq_base may be null)
   const int* seq_base;          // device counter advanced once per training step (keeps CUDA-graph replays unique)
@@ -103,6 +107,7 @@ struct GemmComm {
   const __nv_bfloat16* rs_land_local; long long rs_slot_stride;   // this rank's landing zone [nranks][rows][ld]
   __nv_bfloat16* rs_out; long long rs_out_ld;                     // reduced block [rows_per_owner, N] or null
 };
+// one tensor map per rank: the owners' landing slots (reduce-scatter) or the ranks' gather buffers (all-gather push)
 struct RsMaps { CUtensorMap m[MAX_RANKS]; };
 
 __device__ __forceinline__ void st_release_sys_s32(int* p, int v) {
@@ -131,12 +136,6 @@ __device__ __forceinline__ bool wait_flag(const int* flag, int seq, int* status)
   if (status != nullptr) atomicCAS(status, 0, SSM_ERR_TIMEOUT_FLAG);
   return false;
 }
-// m-tile visiting order: rotate so that tile `first` comes first
-__device__ __forceinline__ int rotate_m(int tm, int tiles_m, int first) {
-  int v = tm + first;
-  return v >= tiles_m ? v - tiles_m : v;
-}
-
 __device__ __forceinline__ void trace_mark(const GemmParams& p, int slot) {
   if (p.trace != nullptr) p.trace[(size_t)blockIdx.x * 16 + slot] = global_timer_ns();
 }
@@ -174,15 +173,30 @@ __device__ __forceinline__ bool get_work(const GemmParams& p, int unit, int it, 
   return true;
 }
 
-// (first row of this CTA's 128 accumulator rows, first column of the tile)
+// (first row of this CTA's 128 accumulator rows, first column of the tile).  Plain GEMMs walk the tiles column by
+// column.  The collective variants walk them block by block, a block being the rows of one source shard (all-gather)
+// or of one owner (reduce-scatter): the all-gather starts with the local shard, whose rows need no transfer, and
+// takes the remote shards in ring order behind it; the reduce-scatter starts with the next rank's rows, so that
+// every partial block is on its way as early as possible, and ends with this rank's own rows.  With whole tiles
+// dealt round-robin every unit therefore begins with work that does not wait for a peer, as far as there is any.
 template <int BN, bool PAIR>
 __device__ __forceinline__ void tile_origin(const GemmParams& p, const GemmComm& cm, int tile, int cta_rank, int& m0, int& n0) {
   constexpr int TILE_M = PAIR ? 256 : 128;
-  int tm = tile % p.tiles_m;
-  if (cm.ag) tm = rotate_m(tm, p.tiles_m, (cm.me * cm.rows_per_shard) / TILE_M);
-  if (cm.rs) tm = rotate_m(tm, p.tiles_m, ((cm.me + 1) % cm.nranks) * cm.rows_per_owner / TILE_M);
+  int tm, tn;
+  if (cm.ag || cm.rs) {
+    const int tpb = (cm.ag ? cm.rows_per_shard : cm.rows_per_owner) / TILE_M;    // m-tiles per block (host: divisible)
+    const int per_block = tpb * p.tiles_n;
+    const int bi = tile / per_block, within = tile - bi * per_block;
+    int block = (cm.ag ? cm.me : (cm.me + 1 == cm.nranks ? 0 : cm.me + 1)) + bi;
+    if (block >= cm.nranks) block -= cm.nranks;
+    tn = within / tpb;
+    tm = block * tpb + (within - tn * tpb);
+  } else {
+    tm = tile % p.tiles_m;
+    tn = tile / p.tiles_m;
+  }
   m0 = tm * TILE_M + cta_rank * GEMM_BM;
-  n0 = (tile / p.tiles_m) * BN;
+  n0 = tn * BN;
 }
 
 template <int BN, int STAGES, bool PAIR>
@@ -198,9 +212,9 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* tfull_bar = empty_bar + STAGES;
   uint64_t* tempty_bar = tfull_bar + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  uint64_t* push_bar = tempty_bar + 2;                         // all-gather push: shard tile landed in shared memory
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(push_bar + 1);
   int* epi_flag = reinterpret_cast<int*>(tmem_slot + 1);      // epilogue warps: "this slice arrived last"
-  int* tail_ok = epi_flag + 1;                                 // reduce-scatter tail: all flags arrived
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int cta_rank = PAIR ? (int)cluster_ctarank() : 0;
@@ -212,13 +226,13 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], p.dual ? 2 : 1); mbar_init(&empty_bar[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], 4 * CTAS_PER_UNIT); }
+    mbar_init(push_bar, 1);
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
-    if (p.mode != 3) tma_prefetch_desc(&tmap_c);
-    if (p.mode == 3) for (int t = 0; t < cm.nranks; ++t) tma_prefetch_desc(&rsm.m[t]);
+    if (p.mode != 3 || cm.rs_out != nullptr) tma_prefetch_desc(&tmap_c);
+    if (p.mode == 3 || cm.ag) for (int t = 0; t < cm.nranks; ++t) tma_prefetch_desc(&rsm.m[t]);
     if (cm.ag) tma_prefetch_desc(&tmap_a_local);
-    *tail_ok = 1;
   }
   constexpr int TMEM_COLS = 2 * BN <= 256 ? 256 : 512;      // allocation sizes are powers of two
   if (warp == 1) {
@@ -263,6 +277,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             if (!(group_seen & bit)) {
               if (!wait_flag(cm.ag_flags + cm.ag_flag_base + shard * AG_MAX_GROUPS + grp, seqv, p.status)) { ok = false; break; }
               fence_proxy_async_all();      // rows were written by generic-proxy stores of peer SMs
+              if (group_seen == 0) trace_mark(p, 12);
               group_seen |= bit;
             }
           }
@@ -377,58 +392,99 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     uint8_t* epi_buf = smem + L::EPI_OFF;
 
     if (cm.ag) {
-      // -------- all-gather push: this CTA's slice of every row group of the local shard, to all ranks
-      const int vec_per_row = cm.ag_cols / 8;
-      const int ngroups = cm.rows_per_shard / cm.ag_group_rows;
-      const long long vec_per_group = (long long)cm.ag_group_rows * vec_per_row;
-      const long long row_off = (long long)cm.me * cm.rows_per_shard;
-      const long long lo = vec_per_group * blockIdx.x / gridDim.x, hi = vec_per_group * (blockIdx.x + 1) / gridDim.x;
-      for (int g = 0; g < ngroups; ++g) {
-        for (long long i0 = lo + epi_tid; i0 < hi; i0 += 128 * 4) {
-          uint4 v[4];
-          long long off[4];
-          #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const long long i = i0 + u * 128;
-            if (i < hi) {
-              const long long r = (long long)g * cm.ag_group_rows + i / vec_per_row;
-              const int c = (int)(i % vec_per_row) * 8;
-              v[u] = *reinterpret_cast<const uint4*>(cm.ag_src + r * cm.ag_src_ld + c);
-              off[u] = (row_off + r) * cm.ag_dst_ld + c;
+      // -------- all-gather push: the local shard goes to every rank's gather buffer in boxes of 128 rows x 64
+      // columns (16 KB): TMA load into the (still idle) epilogue staging buffers, one TMA store per destination.
+      // One thread per CTA drives it; the boxes of a row group are dealt round-robin over the CTAs of the grid, and
+      // the CTA that completes a group publishes its flag on every rank.  The bulk copies leave the load/store
+      // units and their path to L2 alone, which the main loop running next to them needs.
+      if (epi_tid == 0) {
+        const int boxes_per_row = (cm.ag_cols + 63) / 64;
+        const int boxes_per_group = (cm.ag_group_rows / GEMM_BM) * boxes_per_row;
+        const int ngroups = cm.rows_per_shard / cm.ag_group_rows;
+        const int grid = (int)gridDim.x;
+        uint32_t phase = 0;
+        int committed = 0;                          // boxes (bulk groups) committed so far
+        int group_last[AG_MAX_GROUPS];              // value of `committed` after the last box of each row group
+        bool pok = true;
+        // issue everything first: load a box, store it to every rank; the only waits are for a staging buffer to
+        // be readable again
+        for (int g = 0; g < ngroups && pok; ++g) {
+          const int start = ((int)blockIdx.x - (int)(((long long)g * boxes_per_group) % grid) + grid) % grid;
+          for (int b = start; b < boxes_per_group; b += grid) {
+            const int row = g * cm.ag_group_rows + (b / boxes_per_row) * GEMM_BM;
+            const int col = (b % boxes_per_row) * 64;
+            uint8_t* buf = epi_buf + (committed & 1) * EPI_BUF_BYTES;
+            asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");     // the stores that last read this buffer
+            mbar_expect_tx(push_bar, EPI_BUF_BYTES);
+            tma_load_2d(buf, &tmap_a_local, col, row, push_bar);
+            if (!mbar_wait(push_bar, phase, p.status)) { pok = false; break; }
+            phase ^= 1;
+            #pragma unroll 1
+            for (int k = 1; k <= cm.nranks; ++k) {
+              // peers first, the local copy last; rank me - 1 consumes this shard earliest (right after its own)
+              int t = cm.me - k;
+              if (t < 0) t += cm.nranks;
+              tma_store_2d(&rsm.m[t], buf, col, cm.me * cm.rows_per_shard + row);
             }
+            tma_store_commit();
+            ++committed;
           }
-          #pragma unroll
-          for (int k = 1; k <= MAX_RANKS; ++k) {           // peers first (ring order), the local copy last
-            const int t = (cm.me + k) % MAX_RANKS;
-            if (t < cm.nranks) {
-              #pragma unroll
-              for (int u = 0; u < 4; ++u)
-                if (i0 + u * 128 < hi)
-                  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(cm.ag_dst.p[t]) + off[u]) = v[u];
-            }
-          }
+          group_last[g] = committed;
         }
-        __threadfence_system();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (epi_tid == 0) {
+        // then, group by group: once this CTA's boxes of the group have landed, report; the CTA that completes the
+        // count publishes the group's flag on every rank
+        for (int g = 0; g < ngroups && pok; ++g) {
+          const int after = committed - group_last[g];      // boxes committed after the group's last one may pend
+          switch (after) {
+            case 0: asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); break;
+            case 1: asm volatile("cp.async.bulk.wait_group 1;" ::: "memory"); break;
+            case 2: asm volatile("cp.async.bulk.wait_group 2;" ::: "memory"); break;
+            case 3: asm volatile("cp.async.bulk.wait_group 3;" ::: "memory"); break;
+            default: asm volatile("cp.async.bulk.wait_group 4;" ::: "memory"); break;
+          }
+          fence_proxy_async_all();
+          __threadfence_system();
           const int done = atomicAdd(cm.ag_counter + g, 1) + 1;
-          if (done == (int)gridDim.x) {
+          if (done == grid) {
             cm.ag_counter[g] = 0;
             __threadfence_system();
             for (int t = 0; t < cm.nranks; ++t)
               st_release_sys_s32(reinterpret_cast<int*>(cm.flag_ptrs.p[t]) + cm.ag_flag_base + cm.me * AG_MAX_GROUPS + g, seqv);
           }
         }
+        tma_store_wait_all();
+        trace_mark(p, 11);
       }
+      asm volatile("bar.sync 1, 128;" ::: "memory");       // the staging buffers are free for the epilogue again
     }
 
     int acc = 0; uint32_t acc_phase = 0;
     bool ok = true;
     int stores_issued = 0;
     float ssq = 0.f;                               // this thread's share of sum(C^2) (mode 1 with p.sumsq)
-    int rs_count[MAX_RANKS];
-    #pragma unroll
-    for (int t = 0; t < MAX_RANKS; ++t) rs_count[t] = 0;
+    // reduce-scatter: tiles are visited owner by owner; when this CTA has stored its last tile for an owner it
+    // reports them, and the CTA that completes an owner's count publishes the flag there: a partial block is
+    // announced as soon as it has landed, not when the whole GEMM is over
+    int rs_owner = -1, rs_pending = 0;
+    bool rs_seen = false;
+    auto rs_report = [&](int owner_, int count_) {
+      if (p.direct) {                                // rows were written with ordinary stores by all epilogue threads
+        __threadfence_system();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+      if (epi_tid == 0) {
+        tma_store_wait_all();
+        fence_proxy_async_all();
+        __threadfence_system();
+        const int per_owner = (cm.rows_per_owner / GEMM_BM) * p.tiles_n;
+        const int done = atomicAdd(cm.rs_counters + owner_, count_) + count_;
+        if (done == per_owner) {
+          cm.rs_counters[owner_] = 0;
+          __threadfence_system();
+          st_release_sys_s32(reinterpret_cast<int*>(cm.flag_ptrs.p[owner_]) + cm.rs_flag_base + cm.me, seqv);
+        }
+      }
+    };
     Work w;
     for (int it = 0; ok && get_work(p, unit, it, kblocks, w); ++it) {
       int m0, n0;
@@ -450,21 +506,45 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       }
       tc_fence_after_sync();
       if (epi_tid == 0) trace_mark(p, it == 0 ? 4 : 6);
+      // ---- reduce-scatter, tiles of this rank's own rows: the other ranks' partial blocks are added right here in
+      // the epilogue (they computed this rank's rows before their own, so their data is normally waiting); the first
+      // such tile makes sure of it (bounded wait for the flags of all other sources)
+      const bool own = cm.rs && cm.rs_out != nullptr && owner == cm.me;
+      if (own && !rs_seen && ok) {
+        uint32_t mine = 1u, all;
+        if (epi_tid < cm.nranks && epi_tid != cm.me) {
+          const int* flags = reinterpret_cast<const int*>(cm.flag_ptrs.p[cm.me]);
+          mine = wait_flag(flags + cm.rs_flag_base + epi_tid, seqv, p.status) ? 1u : 0u;
+        }
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p, q;\n\t"
+            "setp.ne.u32 p, %1, 0;\n\t"
+            "bar.red.and.pred q, 1, 128, p;\n\t"
+            "selp.u32 %0, 1, 0, q;\n\t"
+            "}\n"
+            : "=r"(all) : "r"(mine) : "memory");
+        ok = all != 0;
+        rs_seen = true;
+        if (epi_tid == 0) trace_mark(p, 13);
+      }
       // ---- tail tiles cut along K: exchange partial sums, the slice that arrives last runs the epilogue
       bool run_epilogue = ok && m0 < p.M;
       const float* others = nullptr;       // partial sums of the other slices (this CTA's rows), null: none
       if (ok && w.nslices > 1 && p.mode != 2) {
-        float* mine = p.ws + ((size_t)(w.tail * MAX_SPLIT + w.slice) * CTAS_PER_UNIT + cta_rank) * (GEMM_BM * BN);
+        float* mine = p.ws + ((size_t)(w.tail * p.split + w.slice) * CTAS_PER_UNIT + cta_rank) * (GEMM_BM * BN);
         #pragma unroll 1
         for (int j = 0; j < BN / 32; ++j) {
           if (n0 + j * 32 >= p.N) break;
           uint32_t v[32];
           tmem_ld32(tmem_addr(tmem_base, q * 32, acc * BN + j * 32), v);
           tmem_ld_wait();
-          #pragma unroll
-          for (int c = 0; c < 8; ++c)           // layout [BN / 4][128 rows][4]: a warp writes 512 contiguous bytes
-            *reinterpret_cast<uint4*>(mine + ((size_t)(j * 8 + c) * GEMM_BM + row) * 4) =
-                make_uint4(v[c * 4], v[c * 4 + 1], v[c * 4 + 2], v[c * 4 + 3]);
+          if (m0 + row < p.M) {
+            #pragma unroll
+            for (int c = 0; c < 8; ++c)         // layout [BN / 4][128 rows][4]: a warp writes 512 contiguous bytes
+              *reinterpret_cast<uint4*>(mine + ((size_t)(j * 8 + c) * GEMM_BM + row) * 4) =
+                  make_uint4(v[c * 4], v[c * 4 + 1], v[c * 4 + 2], v[c * 4 + 3]);
+          }
         }
         __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -477,11 +557,15 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         run_epilogue = run_epilogue && (*epi_flag != 0);
-        others = p.ws + ((size_t)(w.tail * MAX_SPLIT) * CTAS_PER_UNIT + cta_rank) * (GEMM_BM * BN);
+        others = p.ws + ((size_t)(w.tail * p.split) * CTAS_PER_UNIT + cta_rank) * (GEMM_BM * BN);
       }
-      if (run_epilogue && cm.rs) {
-        #pragma unroll
-        for (int t = 0; t < MAX_RANKS; ++t) if (t == owner) rs_count[t] += 1;
+      if (run_epilogue && cm.rs && !own) {
+        if (owner != rs_owner) {
+          if (rs_pending > 0) rs_report(rs_owner, rs_pending);
+          rs_owner = owner;
+          rs_pending = 0;
+        }
+        rs_pending += 1;
       }
       float ce_m = -INFINITY, ce_s = 0.f;
       long long ce_lbl = -1;
@@ -507,41 +591,36 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
               #pragma unroll
               for (int e = 0; e < 32; ++e) v[h][e] = 0u;
             }
-            for (int s = 0; s < w.nslices; ++s) {
-              const float* src = others + (size_t)s * CTAS_PER_UNIT * (GEMM_BM * BN);
+            if (m0 + row < p.M) {                  // rows beyond M hold nothing anyone reads
               #pragma unroll
               for (int h = 0; h < 2; ++h) {
                 if (nb + h * 32 >= p.N) break;
-                #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                  const float4 o = __ldcg(reinterpret_cast<const float4*>(src + ((size_t)(j * 16 + h * 8 + c) * GEMM_BM + row) * 4));
-                  v[h][c * 4 + 0] = __float_as_uint(__uint_as_float(v[h][c * 4 + 0]) + o.x);
-                  v[h][c * 4 + 1] = __float_as_uint(__uint_as_float(v[h][c * 4 + 1]) + o.y);
-                  v[h][c * 4 + 2] = __float_as_uint(__uint_as_float(v[h][c * 4 + 2]) + o.z);
-                  v[h][c * 4 + 3] = __float_as_uint(__uint_as_float(v[h][c * 4 + 3]) + o.w);
+                for (int s0 = 0; s0 < w.nslices; s0 += 2) {      // two slices (16 vector loads) in flight per thread
+                  float4 o[2][8];
+                  #pragma unroll
+                  for (int t = 0; t < 2; ++t) {
+                    const float* src = others + (size_t)(s0 + t) * CTAS_PER_UNIT * (GEMM_BM * BN);
+                    #pragma unroll
+                    for (int c = 0; c < 8; ++c)
+                      o[t][c] = (s0 + t < w.nslices)
+                                    ? __ldcg(reinterpret_cast<const float4*>(src + ((size_t)(j * 16 + h * 8 + c) * GEMM_BM + row) * 4))
+                                    : make_float4(0.f, 0.f, 0.f, 0.f);
+                  }
+                  #pragma unroll
+                  for (int t = 0; t < 2; ++t) {
+                    #pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                      v[h][c * 4 + 0] = __float_as_uint(__uint_as_float(v[h][c * 4 + 0]) + o[t][c].x);
+                      v[h][c * 4 + 1] = __float_as_uint(__uint_as_float(v[h][c * 4 + 1]) + o[t][c].y);
+                      v[h][c * 4 + 2] = __float_as_uint(__uint_as_float(v[h][c * 4 + 2]) + o[t][c].z);
+                      v[h][c * 4 + 3] = __float_as_uint(__uint_as_float(v[h][c * 4 + 3]) + o[t][c].w);
+                    }
+                  }
                 }
               }
             }
           }
-          if (p.direct && p.mode == 3) {
-            // reduce-scatter: the row goes straight into the owner's landing slot (peer memory, P2P stores)
-            __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(cm.rs_land.p[owner]) +
-                                  (long long)(m0 - owner * cm.rows_per_owner + row) * cm.rs_land_ld;
-            #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              #pragma unroll
-              for (int c = 0; c < 4; ++c) {
-                const int col = nb + h * 32 + c * 8;
-                if (col >= p.N) break;
-                uint4 o;
-                o.x = pack_bf16(__uint_as_float(v[h][c * 8 + 0]), __uint_as_float(v[h][c * 8 + 1]));
-                o.y = pack_bf16(__uint_as_float(v[h][c * 8 + 2]), __uint_as_float(v[h][c * 8 + 3]));
-                o.z = pack_bf16(__uint_as_float(v[h][c * 8 + 4]), __uint_as_float(v[h][c * 8 + 5]));
-                o.w = pack_bf16(__uint_as_float(v[h][c * 8 + 6]), __uint_as_float(v[h][c * 8 + 7]));
-                *reinterpret_cast<uint4*>(base + col) = o;        // N % 8 == 0 on this path
-              }
-            }
-          } else if (p.direct) {
+          if (p.direct) {
             // every thread owns one output row: 64 consecutive columns = 128 B (bf16) or 2 x 128 B (fp32)
             const int r = m0 + row;
             if (r < p.M) {
@@ -597,6 +676,28 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             uint8_t* buf = epi_buf + (stores_issued & 1) * EPI_BUF_BYTES;
             if (epi_tid == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
             asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (own) {
+              const long long r_in = (long long)(m0 - owner * cm.rows_per_owner + row);
+              for (int src_rank = 0; src_rank < cm.nranks; ++src_rank) {      // fixed order: reproducible sums
+                if (src_rank == cm.me) continue;
+                const __nv_bfloat16* src = cm.rs_land_local + src_rank * cm.rs_slot_stride + r_in * cm.rs_land_ld + nb;
+                uint4 u[8];
+                #pragma unroll
+                for (int c = 0; c < 8; ++c)
+                  u[c] = (nb + c * 8 < p.N) ? __ldcg(reinterpret_cast<const uint4*>(src + c * 8)) : make_uint4(0u, 0u, 0u, 0u);
+                #pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                  const uint32_t pk[4] = {u[c].x, u[c].y, u[c].z, u[c].w};
+                  #pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    uint32_t& lo = v[c >> 2][(c & 3) * 8 + 2 * e];
+                    uint32_t& hi = v[c >> 2][(c & 3) * 8 + 2 * e + 1];
+                    lo = __float_as_uint(__uint_as_float(lo) + bf16_lo(pk[e]));
+                    hi = __float_as_uint(__uint_as_float(hi) + bf16_hi(pk[e]));
+                  }
+                }
+              }
+            }
             if (p.bias == nullptr && p.act == 0) {
               // plain output (every GEMM of the training step except the MLP up-projection): convert and stage only;
               // keeping the bias / GELU arithmetic out of this loop matters, the compiler otherwise evaluates it
@@ -659,6 +760,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (epi_tid == 0) {
               if (p.mode == 0) tma_store_2d(&tmap_c, buf, nb, m0);
+              else if (own) tma_store_2d(&tmap_c, buf, nb, m0 - owner * cm.rows_per_owner);     // reduced block
               else tma_store_2d(&rsm.m[owner], buf, nb, m0 - owner * cm.rows_per_owner);
               tma_store_commit();
             }
@@ -709,70 +811,31 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         else mbar_arrive(&tempty_bar[acc]);
       }
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      if (cm.rs && ok && rs_pending > 0) {
+        // last tile of this CTA for the current owner?  then report it now, while the next tile's main loop runs
+        Work nw;
+        int next_owner = -1;
+        if (get_work(p, unit, it + 1, kblocks, nw)) {
+          int nm0, nn0;
+          tile_origin<BN, PAIR>(p, cm, nw.tile, cta_rank, nm0, nn0);
+          next_owner = nm0 / cm.rows_per_owner;
+        }
+        if (next_owner != rs_owner) { rs_report(rs_owner, rs_pending); rs_pending = 0; }
+      }
     }
     if (p.sumsq != nullptr && p.mode == 1) {
       #pragma unroll
       for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
       if (lane == 0) atomicAdd(p.sumsq, ssq);
     }
-    if (cm.rs && p.direct) {
-      // the rows were written with ordinary stores by all epilogue threads: make them visible system-wide before
-      // thread 0 reports this CTA's tiles
-      __threadfence_system();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-    }
+    if (cm.rs && ok && rs_pending > 0) rs_report(rs_owner, rs_pending);
     if (epi_tid == 0) {
       tma_store_wait_all();
-      if (cm.rs && ok) {
-        // all tiles of this CTA have landed: publish per owner once every CTA has reported its share
-        fence_proxy_async_all();
-        __threadfence_system();
-        const int per_owner = (cm.rows_per_owner / GEMM_BM) * p.tiles_n;
-        #pragma unroll
-        for (int t = 0; t < MAX_RANKS; ++t) {
-          if (t < cm.nranks && rs_count[t] > 0) {
-            const int done = atomicAdd(cm.rs_counters + t, rs_count[t]) + rs_count[t];
-            if (done == per_owner) {
-              cm.rs_counters[t] = 0;
-              __threadfence_system();
-              st_release_sys_s32(reinterpret_cast<int*>(cm.flag_ptrs.p[t]) + cm.rs_flag_base + cm.me, seqv);
-            }
-          }
-        }
-      }
+      trace_mark(p, 14);
     }
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (cm.rs && cm.rs_out != nullptr) {
-    // ------------------------------------------------------------------ reduce-scatter tail
-    // every CTA sums a slice of the T partial blocks that the sources stored into this rank's landing zone; the
-    // wait is for the peers' flags only (they do not depend on this kernel), never for another CTA of this grid
-    if ((int)threadIdx.x < cm.nranks) {
-      const int* flags = reinterpret_cast<const int*>(cm.flag_ptrs.p[cm.me]);
-      if (!wait_flag(flags + cm.rs_flag_base + threadIdx.x, seqv, p.status)) *tail_ok = 0;
-    }
-    __syncthreads();
-    if (*tail_ok) {
-      const int vec_per_row = p.N / 8;
-      const long long total = (long long)cm.rows_per_owner * vec_per_row;
-      for (long long i = (long long)blockIdx.x * GEMM_THREADS + threadIdx.x; i < total; i += (long long)gridDim.x * GEMM_THREADS) {
-        const long long r = i / vec_per_row;
-        const int c = (int)(i % vec_per_row) * 8;
-        float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        #pragma unroll 4
-        for (int s = 0; s < cm.nranks; ++s) {
-          const uint4 u = *reinterpret_cast<const uint4*>(cm.rs_land_local + s * cm.rs_slot_stride + r * cm.rs_land_ld + c);
-          a[0] += bf16_lo(u.x); a[1] += bf16_hi(u.x); a[2] += bf16_lo(u.y); a[3] += bf16_hi(u.y);
-          a[4] += bf16_lo(u.z); a[5] += bf16_hi(u.z); a[6] += bf16_lo(u.w); a[7] += bf16_hi(u.w);
-        }
-        uint4 o;
-        o.x = pack_bf16(a[0], a[1]); o.y = pack_bf16(a[2], a[3]);
-        o.z = pack_bf16(a[4], a[5]); o.w = pack_bf16(a[6], a[7]);
-        *reinterpret_cast<uint4*>(cm.rs_out + r * cm.rs_out_ld + c) = o;
-      }
-    }
-  }
   if (threadIdx.x == 0) trace_mark(p, 10);
   if (PAIR) {
     // neither CTA may leave (or free TMEM) while its partner can still signal its barriers or read its shared memory
@@ -808,16 +871,22 @@ static int epilogue_direct() {
   }
   return v;
 }
-// SSM_GEMM_PAIR=0 never uses CTA pairs; SSM_GEMM_SPLIT=0 never cuts tail tiles along K.
-static int gemm_pairs_enabled() {
-  static int v = -1;
-  if (v < 0) v = env_int("SSM_GEMM_PAIR", 1) ? 1 : 0;
-  return v;
+// Scheduling options: environment defaults (SSM_GEMM_PAIR=0|1|2: never / by cost / whenever possible use CTA pairs;
+// SSM_GEMM_SPLIT=0: never cut tail tiles along K; SSM_GEMM_FORCE_BN=128|192|256: tile width), overridden at run time
+// by ssm_gemm_set_options (tests and benchmarks).
+static int g_opt_pair = -1, g_opt_split = -1, g_opt_bn = -1;
+static int gemm_pair_mode() {
+  if (g_opt_pair < 0) g_opt_pair = env_int("SSM_GEMM_PAIR", 1);
+  return g_opt_pair;
 }
+static int gemm_pairs_enabled() { return gemm_pair_mode() != 0; }
 static int gemm_split_enabled() {
-  static int v = -1;
-  if (v < 0) v = env_int("SSM_GEMM_SPLIT", 1) ? 1 : 0;
-  return v;
+  if (g_opt_split < 0) g_opt_split = env_int("SSM_GEMM_SPLIT", 1) ? 1 : 0;
+  return g_opt_split;
+}
+static int gemm_forced_bn() {
+  if (g_opt_bn < 0) g_opt_bn = env_int("SSM_GEMM_FORCE_BN", 0);
+  return g_opt_bn;
 }
 
 // Scratch for the split tail (allocated once per device, on first use): partial sums and arrival counters.
@@ -846,8 +915,7 @@ struct TileChoice { int bn; int pair; };
 // k-block: 48 KB for 128x256, 32 KB for a 128x128 tile or for its half of a 256x256 pair tile, 24 KB for its half
 // of a 256x128 pair tile).  SSM_GEMM_FORCE_BN=128|192|256 and SSM_GEMM_PAIR=0|1|2 (2 = always) override.
 static TileChoice pick_tile(int M, int N, int K, int b_mn, int allow_pair) {
-  static int forced_bn = -1, forced_pair = -1;
-  if (forced_bn < 0) { forced_bn = env_int("SSM_GEMM_FORCE_BN", 0); forced_pair = env_int("SSM_GEMM_PAIR", 1); }
+  const int forced_bn = gemm_forced_bn(), forced_pair = gemm_pair_mode();
   const int sms = g_num_sms > 0 ? g_num_sms : 148;
   const int kblocks = (K + GEMM_BK - 1) / GEMM_BK;
   struct Cand { int bn, pair; double cost; };
@@ -992,15 +1060,15 @@ extern "C" int ssm_gemm_bf16_ex(const void* A, const void* B, void* C, int M, in
 
 // Number of column tiles the kernel will use for an [M, N] x K product with K-major operands: the leading extent of
 // the per-tile cross-entropy statistics that ssm_gemm_bf16_ce / the fused variant write.
-extern "C" int ssm_gemm_ce_tiles(int M, int N, int K, int fused) {
+// (rows_per_shard: shard rows of the all-gather variant, 0 for the plain GEMM).
+extern "C" int ssm_gemm_ce_tiles(int M, int N, int K, int rows_per_shard) {
   using namespace ssm;
   if (g_num_sms == 0) {
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
   }
-  (void)fused;
-  const TileChoice c = pick_tile(M, N, K, 0, gemm_pairs_enabled());
+  const TileChoice c = pick_tile(M, N, K, 0, gemm_pairs_enabled() && rows_per_shard % 256 == 0);
   return (N + c.bn - 1) / c.bn;
 }
 
@@ -1029,7 +1097,11 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
   }
-  const TileChoice tcw = pick_tile(M, N, K, b_mn, gemm_pairs_enabled());
+  // the collective variants walk the tiles block by block (rows of one shard / owner): pair tiles need whole blocks
+  int allow_pair = gemm_pairs_enabled();
+  if (comm != nullptr && comm->ag && comm->rows_per_shard % 256) allow_pair = 0;
+  if (comm != nullptr && comm->rs && comm->rows_per_owner % 256) allow_pair = 0;
+  const TileChoice tcw = pick_tile(M, N, K, b_mn, allow_pair);
   const int BN = tcw.bn;
   const bool pair = tcw.pair != 0;
   if (tiles_n_out) *tiles_n_out = (N + BN - 1) / BN;
@@ -1049,6 +1121,9 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
     if ((ldc % 4) || (reinterpret_cast<uintptr_t>(C) & 15)) return -SSM_ERR_BAD_ARG;
     r = make_tmap_2d(&tc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc * 4, 32, 128);
     if (r) return -300 - r;
+  } else if (comm != nullptr && comm->rs && comm->rs_out != nullptr) {
+    r = make_tmap_2d_bf16(&tc, comm->rs_out, (uint64_t)N, (uint64_t)comm->rows_per_owner, (uint64_t)comm->rs_out_ld * 2, 64, 128);
+    if (r) return -300 - r;
   } else {
     tc = ta;
   }
@@ -1059,6 +1134,10 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
     r = make_tmap_2d_bf16(&ta_local, comm->ag_src, (uint64_t)K, (uint64_t)comm->rows_per_shard,
                           (uint64_t)comm->ag_src_ld * 2, 64, 128);
     if (r) return -500 - r;
+    for (int t = 0; t < comm->nranks; ++t) {      // every rank's gather buffer: destinations of the shard push
+      r = make_tmap_2d_bf16(&maps.m[t], comm->ag_dst.p[t], (uint64_t)K, (uint64_t)M, (uint64_t)comm->ag_dst_ld * 2, 64, 128);
+      if (r) return -600 - r;
+    }
   }
   if (comm != nullptr && comm->rs) {
     for (int t = 0; t < comm->nranks; ++t) {
@@ -1075,7 +1154,7 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
   p.c16 = mode == 0 ? reinterpret_cast<__nv_bfloat16*>(C) : nullptr;
   p.ldc16 = ldc; p.direct = epilogue_direct(); p.trace = g_trace; p.sumsq = sumsq;
   p.dual = gemm_dual_producers();
-  if (sumsq != nullptr) p.direct = 0;      // the sum of squares is formed in the staged (TMA-store) epilogue
+  if (sumsq != nullptr || mode == 3) p.direct = 0;   // sum of squares / peer stores go through the staged epilogue
   if (extra != nullptr && extra->ce_labels != nullptr) {
     if (mode != 0 || bias != nullptr || act != 0) return -SSM_ERR_BAD_ARG;
     p.direct = 0;
@@ -1085,7 +1164,7 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
     p.ce_sum = reinterpret_cast<float*>(extra->ce_sum);
     p.ce_tgt = reinterpret_cast<float*>(extra->ce_tgt);
   }
-  const RsMaps* mp = (comm != nullptr && comm->rs) ? &maps : nullptr;
+  const RsMaps* mp = (comm != nullptr && (comm->rs || comm->ag)) ? &maps : nullptr;
   if (pair) {
     if (BN == 256) return launch_gemm<256, 6, true>(ta, tb, tc, p, stream, comm, mp, &ta_local);
     return launch_gemm<128, 8, true>(ta, tb, tc, p, stream, comm, mp, &ta_local);
@@ -1101,9 +1180,10 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
 //           ready flags of this call are flag_ptrs[t][ag_flag_base + source * 4 + row group]; ag_counter points at
 //           4 local ints that are zero between launches.
 //   rs = 1: mode is forced to 3; land_ptrs[o] is the base of the [rows_per_owner, N] slot this rank owns inside
-//           rank o's landing zone (row stride land_ld); C is ignored.  With rs_out the kernel also reduces this
-//           rank's landing zone (rs_land_local: [nranks] slots, rs_slot_stride elements apart) into
-//           rs_out [rows_per_owner, N] (row stride rs_out_ld) once all sources have published; N % 8 == 0 then.
+//           rank o's landing zone (row stride land_ld); C is ignored.  With rs_out the kernel also reduces: the
+//           partial blocks of the other sources are read from this rank's landing zone (rs_land_local: [nranks]
+//           slots, rs_slot_stride elements apart) and the sum goes to rs_out [rows_per_owner, N] (row stride
+//           rs_out_ld); N % 8 == 0 then.
 //   ce_labels: as in ssm_gemm_bf16_ce (all-gather + LM head).
 // rows_per_shard / rows_per_owner must be multiples of 128 and M = nranks * rows.
 extern "C" int ssm_gemm_bf16_fused(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
@@ -1152,10 +1232,21 @@ extern "C" int ssm_gemm_bf16_fused(const void* A, const void* B, void* C, int M,
                         ce_labels != nullptr ? &ex : nullptr, &cm, land_ptrs, land_ld, nullptr);
 }
 
+// pair: 0 never / 1 by cost / 2 whenever possible use CTA-pair tiles; split: 0/1 K-split of tail tiles; bn: 0 (by cost)
+// or 128 / 192 / 256.  A negative value leaves that option as it is.
+extern "C" int ssm_gemm_set_options(int pair, int split, int bn) {
+  if (pair >= 0) ssm::g_opt_pair = pair;
+  if (split >= 0) ssm::g_opt_split = split ? 1 : 0;
+  if (bn >= 0) ssm::g_opt_bn = bn;
+  return 0;
+}
+
 // Pipeline analysis: buf = device array of gridDim * 16 uint64 (or null to switch tracing off).  Slots (ns, global
 // timer): 0 CTA set-up done, 8 first TMA load issued, 1 first stage landed, 2/3 MMAs of the first / a later tile
 // issued, 4/6 first / later accumulator complete (seen by the epilogue), 5/7 epilogue of that tile done, 9 producer
-// finished, 10 CTA done.
+// finished, 10 CTA done (after the reduce-scatter tail); collective variants: 11 all-gather push finished, 12 first
+// wait for a remote row group over, 13 reduce-scatter tail: flags of all sources seen, 14 epilogue warps done with
+// their tiles (stores complete, flags published).
 extern "C" int ssm_gemm_set_trace(void* buf) {
   ssm::g_trace = reinterpret_cast<unsigned long long*>(buf);
   return 0;

@@ -145,12 +145,13 @@ def gemm(a: torch.Tensor, b: torch.Tensor, a_mn: bool = False, b_mn: bool = Fals
     return out
 
 
-def ce_epilogue_buffers(M: int, N: int, K: int, labels: torch.Tensor, vocab_start: int):
+def ce_epilogue_buffers(M: int, N: int, K: int, labels: torch.Tensor, vocab_start: int, rows_per_shard: int = 0):
     """Buffers for a GEMM whose epilogue emits cross-entropy statistics of its [M, N] output (the LM head):
-    (arguments for the kernel, number of column tiles).  `labels` [M] int64 global ids, negative = ignored."""
+    (arguments for the kernel, number of column tiles).  `labels` [M] int64 global ids, negative = ignored;
+    `rows_per_shard`: shard rows when the GEMM is the all-gather variant (it decides the tile shape), else 0."""
     fn = _lib().ssm_gemm_ce_tiles
     fn.restype = _c.c_int
-    tiles = int(fn(int(M), int(N), int(K), 0))
+    tiles = int(fn(int(M), int(N), int(K), int(rows_per_shard)))
     dev = labels.device
     lab = labels.reshape(-1).contiguous()
     if lab.numel() != M or lab.dtype != torch.int64:

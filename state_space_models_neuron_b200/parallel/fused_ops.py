@@ -75,7 +75,7 @@ def _ag_gemm(x_shard2, w, b_mn, bias, ws, act=0, ce=None):
     ced, stats = None, None
     if ce is not None:
         labels, vocab_start = ce
-        ced, stats = cuda_ops.ce_epilogue_buffers(M, N, K, labels, vocab_start)
+        ced, stats = cuda_ops.ce_epilogue_buffers(M, N, K, labels, vocab_start, rows_per_shard=Ls)
     _fused_gemm(gathered, w, y, M, N, K, K, w.stride(0), y.stride(0), False, b_mn, 0, bias, act, ws, seq,
                 ag=dict(on=1, rows=Ls, base=ws.flag_base(symm.KIND_AG, par), src=x_shard2, src_ld=x_shard2.stride(0),
                         dst=ws.peer_ptrs(off), dst_ld=K, counter=ws.counter_ptr(0)), ce=ced)

@@ -18,9 +18,22 @@ import torch
 from .cross_entropy import parallel_argmax
 
 
+def _require_side_stream_without_warmup(warmup: int) -> None:
+    """Capture needs every stream that autograd associates with the parameters to be able to join the capture; the
+    legacy default stream cannot.  The warm-up steps of the graph classes run on a side stream for that reason; a
+    caller that passes warmup=0 because it has already run real steps must have run them on a side stream too."""
+    if warmup == 0 and torch.cuda.current_stream() == torch.cuda.default_stream():
+        raise RuntimeError("warmup=0 needs the preceding eager steps (and this call) to run under "
+                           "torch.cuda.stream(side_stream), not on the default stream")
+
+
 class GraphedTrainStep:
+    """`warmup` eager optimizer steps on the example batch (on a side stream), then capture.  With warmup=0 the caller
+    has already taken real steps itself, on a non-default stream (see train.py)."""
+
     def __init__(self, model, optimizer, example_batch: Dict[str, torch.Tensor], loss_fn: Optional[Callable] = None,
                  warmup: int = 2, grad_accum_usteps: int = 1):
+        _require_side_stream_without_warmup(warmup)
         self.model, self.optimizer = model, optimizer
         self.accum = grad_accum_usteps
         self.static = {k: v.clone() for k, v in example_batch.items()}
@@ -41,7 +54,11 @@ class GraphedTrainStep:
         from . import symm
         symm.start_recording()
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
+        # after a caller's own eager steps (warmup=0) the capture runs on the stream those steps ran on: autograd ties
+        # every parameter's gradient accumulation to that stream, and a capture on another stream would have to wait
+        # on work that is not part of the capture
+        cap = dict(stream=torch.cuda.current_stream()) if warmup == 0 else {}
+        with torch.cuda.graph(self.graph, **cap):
             self.static_loss = self._eager_step()
         rec = symm.stop_recording()
         symm.check_replay_safe(rec + rec)          # double-buffer parities must survive back-to-back replays
@@ -84,6 +101,7 @@ class GraphedAccumulationStep:
                  loss_fn: Optional[Callable] = None, warmup: int = 1):
         if grad_accum_usteps < 2:
             raise ValueError("use GraphedTrainStep for grad_accum_usteps == 1")
+        _require_side_stream_without_warmup(warmup)
         self.model, self.optimizer, self.accum = model, optimizer, grad_accum_usteps
         self.static = {k: v.clone() for k, v in example_batch.items()}
         self.loss_fn = loss_fn or (lambda m, b: m(input_ids=b["input_ids"], labels=b["labels"], return_logits=False).loss)
@@ -105,10 +123,11 @@ class GraphedAccumulationStep:
         # the ones it will meet at replay: first (gradients stale) -> next (accumulating) -> update
         from . import symm
         kinds = []
+        cap = dict(stream=torch.cuda.current_stream()) if warmup == 0 else {}      # see GraphedTrainStep
         for graph, body, name in ((self.g_first, self._micro, "loss_first"), (self.g_next, self._micro, "loss_next"),
                                   (self.g_update, self._update, None)):
             symm.start_recording()
-            with torch.cuda.graph(graph, pool=pool):
+            with torch.cuda.graph(graph, pool=pool, **cap):
                 out = body()
             kinds.append(symm.stop_recording())
             if name:

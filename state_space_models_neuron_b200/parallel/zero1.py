@@ -52,6 +52,10 @@ class Zero1Optimizer(torch.optim.Optimizer):
         self.grad_dtype = grad_dtype
         self.step_count = 0
         self.last_grad_norm: Optional[torch.Tensor] = None
+        # called in step() once the local gradients are final (lazy zeroing finished, sequence-parallel-tagged
+        # gradients summed over the TP group), before the data-parallel reduction: per-parameter `main_grad` can be
+        # inspected there (gradient statistics, tests); not called while a CUDA graph is being captured
+        self.post_reduce_hook = None
         self._build_flat_buffers()
 
     # ------------------------------------------------------------------------------------
@@ -318,6 +322,8 @@ class Zero1Optimizer(torch.optim.Optimizer):
             self.upload_learning_rates()
         self._finish_lazy_zero()
         self._allreduce_sequence_parallel_grads()
+        if self.post_reduce_hook is not None and not capturing:
+            self.post_reduce_hook(self)
         self.step_count += 1
         if self._fused_dp:
             return self._fused_step()

@@ -52,10 +52,15 @@ def check_finite(t: torch.Tensor, name: str = "tensor") -> None:
         raise FloatingPointError(f"{name} has {bad} non-finite values")
 
 
-def rotate_m(tm: int, tiles_m: int, first: int) -> int:
-    """Host copy of the device tile rotation (ops/csrc/gemm.cu `rotate_m`): m-tile `first` is visited first."""
-    v = tm + first
-    return v - tiles_m if v >= tiles_m else v
+def collective_tile_origin(tile: int, tiles_n: int, tiles_per_block: int, nranks: int, first_block: int):
+    """Host copy of the tile order of the GEMMs fused with a collective (ops/csrc/gemm.cu `tile_origin`): tiles are
+    visited block by block (a block = the rows of one shard / owner, `tiles_per_block` m-tiles), starting with
+    `first_block` and going round the ranks; returns (m-tile, n-tile)."""
+    per_block = tiles_per_block * tiles_n
+    bi, within = divmod(tile, per_block)
+    block = (first_block + bi) % nranks
+    tn, tm_in = divmod(within, tiles_per_block)
+    return block * tiles_per_block + tm_in, tn
 
 
 def gemm_schedule(tiles: int, max_units: int, kblocks: int, accumulate: bool = False, split_enabled: bool = True):
@@ -111,15 +116,18 @@ def gemm_schedule_covers_once(tiles: int, max_units: int, kblocks: int, accumula
 
 
 def tile_schedule_is_permutation(tiles_m: int, tiles_n: int, nranks: int, ctas: int) -> bool:
-    """The rotated m-tile order of the fused collectives (local shard first for the all-gather, next rank's rows
-    first for the reduce-scatter) still visits every tile exactly once for every rank."""
+    """The block-major tile order of the fused collectives (local shard first for the all-gather, next rank's rows
+    first for the reduce-scatter) visits every tile exactly once for every rank, and a rank's first
+    `tiles_per_block * tiles_n` tiles are exactly the rows of its first block."""
     per = tiles_m // nranks
     for me in range(nranks):
-        for first in (me * per, ((me + 1) % nranks) * per):
-            seen = set()
+        for first in (me, (me + 1) % nranks):
+            seen = []
             for cta in range(ctas):
                 for tile in range(cta, tiles_m * tiles_n, ctas):
-                    seen.add((rotate_m(tile % tiles_m, tiles_m, first), tile // tiles_m))
-            if len(seen) != tiles_m * tiles_n:
+                    seen.append((tile, collective_tile_origin(tile, tiles_n, per, nranks, first)))
+            if len({o for _, o in seen}) != tiles_m * tiles_n or len(seen) != tiles_m * tiles_n:
+                return False
+            if any(tm // per != first for tile, (tm, tn) in seen if tile < per * tiles_n):
                 return False
     return True

@@ -92,7 +92,8 @@ def trace_gemm(a):
     t0 = t[:, 0][t[:, 0] > 0].min()
     names = [(0, "CTA set-up done"), (8, "first TMA load issued"), (1, "first stage landed"),
              (2, "first tile: MMAs issued"), (4, "first tile: accumulator complete"), (5, "first tile: epilogue done"),
-             (3, "last tile: MMAs issued"), (6, "last tile: accumulator complete"), (7, "last tile: epilogue done")]
+             (3, "last tile: MMAs issued"), (6, "last tile: accumulator complete"), (7, "last tile: epilogue done"),
+             (9, "producer finished"), (10, "CTA done")]
     out = {"kernel": "gemm-trace", "m": a.m, "n": a.n, "k": a.k, "out": str(odt), "events_us": {}}
     for slot, name in names:
         col = t[:, slot]
@@ -263,6 +264,39 @@ def bench_fused(a):
             symm.advance_step()
             fn()
         return run
+    if a.trace:
+        # in-kernel timeline of one fused call (timestamps from the global timer, one record per CTA)
+        import ctypes
+        from ..ops import native
+        lib = native.lib()
+        for _ in range(3):
+            stepped(fused_fn)()
+        torch.cuda.synchronize()
+        dist.barrier()
+        tr = torch.zeros(148 * 16, dtype=torch.int64, device="cuda")
+        lib.ssm_gemm_set_trace(ctypes.c_void_p(tr.data_ptr()))
+        stepped(fused_fn)()
+        torch.cuda.synchronize()
+        lib.ssm_gemm_set_trace(ctypes.c_void_p(0))
+        t = tr.view(148, 16).cpu().double()
+        t0 = t[:, 0][t[:, 0] > 0].min()
+        names = [(0, "set-up done"), (11, "push finished"), (12, "first remote group arrived"), (1, "first stage landed"),
+                 (4, "first accumulator complete"), (5, "first epilogue done"), (6, "last accumulator complete"),
+                 (7, "last epilogue done"), (9, "producer finished"), (14, "tiles stored, flags published"),
+                 (13, "tail: all sources seen"), (10, "CTA done")]
+        out = {"kernel": a.kernel + "-trace", "rank": dist.get_rank(), "ranks": T, "events_us": {}}
+        for slot, name in names:
+            col = t[:, slot]
+            col = col[col > 0]
+            if len(col):
+                out["events_us"][name] = [round(float((col.min() - t0) / 1e3), 1), round(float((col.median() - t0) / 1e3), 1),
+                                          round(float((col.max() - t0) / 1e3), 1)]
+        for r in range(T):
+            if r == dist.get_rank():
+                print(json.dumps(out), flush=True)
+            dist.barrier()
+        torch.cuda.synchronize()
+        os._exit(0)
     ms = _time_collective(stepped(fused_fn), a.iters)
     ms_lib = _time_collective(lib_fn, a.iters)
     ms_plain = _time_collective(plain_fn, a.iters)

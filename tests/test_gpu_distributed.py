@@ -26,6 +26,31 @@ def test_tp_matches_single_gpu(extra):
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
 
 
+def test_fused_collectives_against_torch_distributed():
+    """Every fused compute+collective kernel against fp32 matmul + torch.distributed on the same ranks."""
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    world = n if n in (2, 4, 8) else 2
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", "29641", os.path.join(ROOT, "tests", "gpu_collectives_check.py")]
+    r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-4000:] + r.stderr[-3000:]
+
+
+def test_graphed_accumulation_matches_eager():
+    """train.py with --cuda_graph and gradient accumulation (three graphs) reproduces the eager run's losses."""
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29651", os.path.join(ROOT, "tests", "gpu_graph_accum_check.py")]
+    r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-4000:] + r.stderr[-3000:]
+
+
 def test_tp_decode_matches_forward():
     """Token-by-token decode under TP=2 (one-kernel all-reduce after out_proj, graph-free) reproduces the logits of
     the full forward pass on every rank's vocabulary shard."""

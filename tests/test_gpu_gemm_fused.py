@@ -69,6 +69,26 @@ def test_gemm_schedules(M, N, K, layout):
     assert abs(ss.item() - want) <= 2e-3 * want
 
 
+@pytest.mark.parametrize("pair,split,bn", [(0, 1, 0), (0, 1, 128), (0, 1, 192), (0, 0, 256), (2, 1, 256), (2, 1, 128), (2, 0, 0)])
+def test_gemm_forced_tilings(pair, split, bn):
+    """Every tile family with and without the K-split tail, on shapes whose last wave is partial."""
+    from state_space_models_neuron_b200.ops import cuda_ops, native
+    lib = native.lib()
+    lib.ssm_gemm_set_options(pair, split, bn)
+    try:
+        for M, N, K in [(2048, 2320, 4096), (2176, 4096, 1024), (64, 2560, 5120), (1152, 1000, 520)]:
+            a, b = _rand((M, K), M, 0.5), _rand((N, K), N, 0.5)
+            ref = a.float() @ b.float().t()
+            _close(cuda_ops.gemm(a, b), ref, atol=0.02 * K ** 0.5 * 0.25 + 0.02)
+            bt = b.t().contiguous()
+            if bt.shape[1] % 8:
+                bt = torch.nn.functional.pad(bt, (0, (-bt.shape[1]) % 8))[:, :N]
+            f32 = cuda_ops.gemm(a, bt, b_mn=True, out_dtype=torch.float32)
+            _close(f32, ref, atol=1e-2 + 1e-4 * K ** 0.5, rtol=1e-3)
+    finally:
+        lib.ssm_gemm_set_options(1, 1, 0)
+
+
 def test_gemm_repeated_launches_reuse_split_scratch():
     """Tail tiles exchange partial sums through a scratch buffer and arrival counters that must be clean again after
     every launch: run a tail-heavy shape many times back to back."""
@@ -214,8 +234,10 @@ def test_gemm_reduce_scatter_one_rank_of_T(T, me, Ls, K, N, b_mn):
         torch.cuda.synchronize()
         tol = 0.02 * K ** 0.5 * 0.25 + 0.02
         for o in range(T):
+            if o == me:          # this rank's own rows never take the detour through the landing zone
+                continue
             _close(lands[o][me], full[o * Ls:(o + 1) * Ls], atol=tol)
             assert int(flags[o][base + me]) == want_seq
-        ref = lands[me][me].float() + sum(others[s].float() for s in range(T) if s != me)
-        _close(out, ref, atol=2e-2, rtol=1e-2)
+        ref = full[me * Ls:(me + 1) * Ls] + sum(others[s].float() for s in range(T) if s != me)
+        _close(out, ref, atol=2e-2 + 0.004 * K ** 0.5, rtol=1e-2)
         assert int(counters.abs().sum()) == 0

@@ -183,7 +183,8 @@ def run(args):
     done = global_step >= args.max_steps
     # a resumed run continues with the batch that the interrupted run would have seen next
     skip_batches = global_step * args.grad_accum_usteps if args.resume else 0
-    try:
+    def training_loop():
+        nonlocal done, skip_batches, training_step, graphed
         while not done:
             for data in device_loader:
                 if skip_batches > 0:
@@ -199,14 +200,14 @@ def run(args):
                         else:       # one graph per kind of micro-step plus one for the update
                             graphed = GraphedAccumulationStep(model, optimizer, data, args.grad_accum_usteps, warmup=0)
                     if args.grad_accum_usteps == 1:
-                        running_loss += graphed(data)
+                        running_loss.add_(graphed(data))
                     else:
-                        running_loss += graphed.micro_step(data)
+                        running_loss.add_(graphed.micro_step(data))
                 else:
                     out = model(input_ids=data["input_ids"], labels=data["labels"], return_logits=False)
                     loss = out.loss / args.grad_accum_usteps
                     loss.backward()
-                    running_loss += loss.detach()
+                    running_loss.add_(loss.detach())
                     if boundary:
                         optimizer.step()
                         optimizer.zero_grad()
@@ -224,6 +225,18 @@ def run(args):
             health_check()
             save(global_step)
         health_check()
+
+    try:
+        if args.cuda_graph:
+            # graph capture cannot involve the legacy default stream, and autograd remembers the stream on which a
+            # parameter's gradient was first accumulated: with --cuda_graph the whole loop runs on a side stream
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                training_loop()
+            torch.cuda.current_stream().wait_stream(side)
+        else:
+            training_loop()
     finally:
         if heartbeat is not None:
             heartbeat.stop()
