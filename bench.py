@@ -146,7 +146,9 @@ def main():
     fused = args.fused_comm == "on" and args.impl == "ours"
     if args.impl == "baseline":
         from baseline import nccl_cublas
-        nccl_cublas.enable()
+        # one GPU holds all 126 GB of weights, gradients and optimizer state of the 7B model: the saved scan
+        # intermediates of 64 layers do not fit next to them, so only that case recomputes the mixer in backward
+        nccl_cublas.enable(checkpoint_mixer=(args.gpus == 1 and not args.small))
     cfg = nxd.parallel_config(
         tensor_parallel_size=tp, optimizer_config={"zero_one_enabled": True, "grad_clipping": True, "max_grad_norm": 1.0},
         sequence_parallel=tp > 1, fused_comm=fused, init_seed=0)

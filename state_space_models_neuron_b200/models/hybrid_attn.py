@@ -4,8 +4,9 @@ Parameters `q_proj/k_proj/v_proj` (column parallel) and `o_proj` (row parallel),
 dropout, per-rank heads = attn_num_heads/TP and kv heads = attn_key_value_heads/TP
 (mamba2hybrid/mamba2hybrid_attn.py:305-362,491-514).  The three projections share one sequence
 all-gather, K/V heads are never replicated in memory (the kernel indexes kv head = q head // ratio,
-where the reference materialises `repeat_kv`, mamba2hybrid_attn.py:440-447), and rotary embedding is an
-option that is off by default as in the reference hybrid (mamba2hybrid_attn.py:500-503).
+where the reference materialises `repeat_kv`, mamba2hybrid_attn.py:440-447), and rotary embedding (its own
+kernel, forward and backward, with cached tables) is an option that is off by default as in the reference
+hybrid (mamba2hybrid_attn.py:500-503).
 """
 from __future__ import annotations
 
@@ -74,8 +75,8 @@ class Mamba2HybridAttention(nn.Module):
         k = qkv[1].view(B, L, self.num_kv_heads, self.head_dim)
         v = qkv[2].view(B, L, self.num_kv_heads, self.head_dim)
         if self.rotary_emb_dim is not None:
-            cos, sin = ops.oracle.rotary_tables(L, self.rotary_emb_dim, self.rope_theta, device=q.device)
-            q = ops.oracle.apply_rotary(q, cos, sin)
-            k = ops.oracle.apply_rotary(k, cos, sin)
+            cos, sin = ops.rotary_tables(L, self.rotary_emb_dim, self.rope_theta, device=q.device)
+            q = ops.apply_rotary(q, cos, sin)
+            k = ops.apply_rotary(k, cos, sin)
         o = ops.attention(q, k, v, causal=True)
         return self.o_proj(o.reshape(B, L, self.num_heads * self.head_dim))

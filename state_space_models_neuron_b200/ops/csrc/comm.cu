@@ -162,6 +162,7 @@ static PeerPtrs to_peers(const void* const* ptrs, int n) {
 }
 
 extern "C" int ssm_comm_max_ranks() { return MAX_RANKS; }
+SSM_DEBUG_BOUNDS_GETTER(ssm_debug_bounds_comm)
 
 extern "C" int ssm_push_shard(const void* src, long long src_ld, const void* const* dst_ptrs, long long dst_ld,
                               long long row_off, int rows, int cols, int nranks, int me, const void* const* flag_ptrs,
@@ -432,7 +433,7 @@ vocab_embed_push_kernel(const long long* __restrict__ ids, const __nv_bfloat16* 
     if (id < 0 || id >= vloc) continue;
     const int b = (int)(t / L), l = (int)(t % L);
     const int owner = l / Ls;
-    if (owner >= nranks) continue;
+    if (!SSM_INDEX_OK(owner, nranks)) continue;
     __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(dst.p[owner]) + ((long long)b * Ls + (l % Ls)) * D;
     for (int c = threadIdx.x; c < vec; c += blockDim.x)
       *reinterpret_cast<uint4*>(o + c * 8) = *reinterpret_cast<const uint4*>(weight + id * D + c * 8);
@@ -488,6 +489,7 @@ embed_bwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restr
     const int b = (int)(t / L), l = (int)(t % L);
     // row of token (b, l) in g: [B, L] order on one rank, [owner][b][l % Ls] in the gather buffer
     const long long r = nranks > 1 ? ((long long)(l / Ls) * B + b) * Ls + (l % Ls) : t;
+    if (!SSM_INDEX_OK(r, ntok) || !SSM_INDEX_OK(D - 1, g_ld)) continue;
     const __nv_bfloat16* src = g + r * g_ld;
     float* dstp = grad32 + id * D;
     for (int c = threadIdx.x; c < vec; c += blockDim.x) {

@@ -15,6 +15,7 @@
 #define SSM_ERR_TIMEOUT_MBAR 1      // an mbarrier phase never completed
 #define SSM_ERR_TIMEOUT_FLAG 2      // a global-memory flag (peer or local) never arrived
 #define SSM_ERR_BAD_ARG 3
+#define SSM_ERR_BOUNDS 4            // debug build only: an index check failed (the access was skipped)
 
 
 namespace ssm {
@@ -281,6 +282,45 @@ __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + __ex
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : log1pf(__expf(x)); }
 
 }  // namespace ssm
+
+// ---------------------------------------------------------------- debug build: index checks
+// Compiled with -DSSM_DEBUG_BOUNDS (a second library next to the regular one, ops/native.py build(debug=True)),
+// SSM_INDEX_OK(index, limit) checks 0 <= index < limit on the device.  A failed check records
+// {SSM_ERR_BOUNDS, source line, index, limit} once in a per-file device array and evaluates to false, and the
+// kernel skips that access: no trap, no fault, the context stays usable and the host reads the record through the
+// file's ssm_debug_bounds_* function.  In the regular build the macro is the constant `true` and costs nothing.
+#ifdef SSM_DEBUG_BOUNDS
+namespace ssm {
+static __device__ int g_debug_bounds[4];
+__device__ __forceinline__ bool debug_index_ok(long long idx, long long limit, int line) {
+  if (idx >= 0 && idx < limit) return true;
+  if (atomicCAS(&g_debug_bounds[0], 0, SSM_ERR_BOUNDS) == 0) {
+    g_debug_bounds[1] = line;
+    g_debug_bounds[2] = (int)idx;
+    g_debug_bounds[3] = (int)limit;
+  }
+  return false;
+}
+}  // namespace ssm
+#define SSM_INDEX_OK(idx, limit) ssm::debug_index_ok((long long)(idx), (long long)(limit), __LINE__)
+#define SSM_DEBUG_BOUNDS_GETTER(name)                                                          \
+  extern "C" int name(int* out4, int reset) {                                                  \
+    cudaError_t e = cudaMemcpyFromSymbol(out4, ssm::g_debug_bounds, 4 * sizeof(int));          \
+    if (e == cudaSuccess && reset) {                                                           \
+      const int z[4] = {0, 0, 0, 0};                                                           \
+      e = cudaMemcpyToSymbol(ssm::g_debug_bounds, z, sizeof(z));                               \
+    }                                                                                          \
+    return (int)e;                                                                             \
+  }
+#else
+#define SSM_INDEX_OK(idx, limit) true
+#define SSM_DEBUG_BOUNDS_GETTER(name)                                                          \
+  extern "C" int name(int* out4, int reset) {                                                  \
+    out4[0] = out4[1] = out4[2] = out4[3] = 0;                                                 \
+    (void)reset;                                                                               \
+    return 0;                                                                                  \
+  }
+#endif
 
 // ---------------------------------------------------------------- host side
 #include <cudaTypedefs.h>

@@ -15,6 +15,7 @@ decode_conv_step_kernel(const __nv_bfloat16* __restrict__ xnew, long long xs, __
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   const int b = blockIdx.y;
   if (c >= C) return;
+  if (!SSM_INDEX_OK(c, xs)) return;               // the new token's row must hold all C channels
   uint2* sp = reinterpret_cast<uint2*>(state + ((long long)b * C + c) * 4);
   const uint2 s = *sp;
   const float x1 = bf16_hi(s.x), x2 = bf16_lo(s.y), x3 = bf16_hi(s.y);
@@ -30,7 +31,7 @@ decode_conv_step_kernel(const __nv_bfloat16* __restrict__ xnew, long long xs, __
   act[(long long)b * C + c] = silu_f(pre);
 }
 
-// grid (H, B), 128 threads: warp w owns rows p = w, w+4, ...; lanes own n = 4*lane + 128*r.
+// grid (H, B), 128 threads: warp w owns rows p = 4w .. 4w+3, 4w+16 .., ...; lanes own n = 4*lane + 128*r.
 __global__ void __launch_bounds__(128)
 decode_ssm_step_kernel(const float* __restrict__ act, const __nv_bfloat16* __restrict__ dt_raw, long long dts,
                        const float* __restrict__ dt_bias, const float* __restrict__ A, const float* __restrict__ D,
@@ -45,29 +46,54 @@ decode_ssm_step_kernel(const float* __restrict__ act, const __nv_bfloat16* __res
   const float* ab = act + (long long)b * C;
   const float* Bv = ab + d_in + g * N;
   const float* Cv = ab + d_in + G * N + g * N;
+  // the activation row [x | B | C] must hold d_in + 2 G N values and the head's x slice must lie inside d_in
+  if (!SSM_INDEX_OK(d_in + 2 * G * N - 1, C) || !SSM_INDEX_OK(h * P + P - 1, d_in)) return;
   float* S = state + (((long long)b * H + h) * P) * N;
-  for (int pp = warp; pp < P; pp += 4) {
-    const float x = ab[h * P + pp];
-    const float dx = dt * x;
-    float acc = 0.f;
+  // four rows per warp iteration: four independent 16-byte loads per lane are in flight before any arithmetic,
+  // and the four row sums are reduced together (the state makes one round trip; this loop is latency-bound otherwise)
+  for (int p0 = warp * 4; p0 < P; p0 += 16) {
+    float4 s[4];
+    float xs[4], acc[4];
+    #pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int pp = p0 + r;
+      xs[r] = pp < P ? ab[h * P + pp] : 0.f;
+      acc[r] = 0.f;
+    }
     for (int n = lane * 4; n < N; n += 128) {
-      float4 s = *reinterpret_cast<float4*>(S + (long long)pp * N + n);
+      #pragma unroll
+      for (int r = 0; r < 4; ++r)
+        if (p0 + r < P) s[r] = *reinterpret_cast<const float4*>(S + (long long)(p0 + r) * N + n);
       const float4 bv = *reinterpret_cast<const float4*>(Bv + n);
       const float4 cv = *reinterpret_cast<const float4*>(Cv + n);
-      s.x = s.x * decay + dx * bv.x; s.y = s.y * decay + dx * bv.y;
-      s.z = s.z * decay + dx * bv.z; s.w = s.w * decay + dx * bv.w;
-      *reinterpret_cast<float4*>(S + (long long)pp * N + n) = s;
-      acc += s.x * cv.x + s.y * cv.y + s.z * cv.z + s.w * cv.w;
+      #pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        if (p0 + r < P) {
+          const float dx = dt * xs[r];
+          s[r].x = s[r].x * decay + dx * bv.x; s[r].y = s[r].y * decay + dx * bv.y;
+          s[r].z = s[r].z * decay + dx * bv.z; s[r].w = s[r].w * decay + dx * bv.w;
+          *reinterpret_cast<float4*>(S + (long long)(p0 + r) * N + n) = s[r];
+          acc[r] += s[r].x * cv.x + s[r].y * cv.y + s[r].z * cv.z + s[r].w * cv.w;
+        }
+      }
     }
     #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (lane == 0) y[(long long)b * d_in + h * P + pp] = __float2bfloat16(acc + Dh * x);
+    for (int o = 16; o > 0; o >>= 1) {
+      #pragma unroll
+      for (int r = 0; r < 4; ++r) acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], o);
+    }
+    if (lane < 4 && p0 + lane < P) {
+      const float a = lane == 0 ? acc[0] : lane == 1 ? acc[1] : lane == 2 ? acc[2] : acc[3];
+      const float x = lane == 0 ? xs[0] : lane == 1 ? xs[1] : lane == 2 ? xs[2] : xs[3];
+      y[(long long)b * d_in + h * P + p0 + lane] = __float2bfloat16(a + Dh * x);
+    }
   }
 }
 
 }  // namespace ssm
 
 using namespace ssm;
+SSM_DEBUG_BOUNDS_GETTER(ssm_debug_bounds_decode)
 
 extern "C" int ssm_decode_conv_step(const void* xnew, long long xs, void* state, const void* w, const void* bias,
                                     void* act, int B, int C, cudaStream_t st) {

@@ -74,6 +74,7 @@ conv1d_silu_fwd_kernel(const __nv_bfloat16* __restrict__ x, long long xs, const 
                        __nv_bfloat16* __restrict__ out, long long os, int L, int C) {
   const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (c0 >= C) return;
+  if (!SSM_INDEX_OK(c0 + 7, C) || !SSM_INDEX_OK(C - 1, xs) || !SSM_INDEX_OK(C - 1, os)) return;   // whole 8-channel vectors inside a row
   const int t0 = blockIdx.y * TOK;
   const int b = blockIdx.z;
   float wt[CONV_K][8], bs[8];
@@ -538,6 +539,59 @@ ce_backward_kernel(const T* __restrict__ logits, long long ld, const long long* 
   }
 }
 
+// =====================================================================================
+// Rotary position embedding (rotate-half convention) on the first `rd` channels of every head:
+//   out[:, :rd/2] = x1 * cos - sign * x2 * sin,   out[:, rd/2:rd] = x2 * cos + sign * x1 * sin
+// x, out: [tokens, H, Dh] bf16 with a token stride; cos / sin: fp32 tables [L, rd/2], position = token % L + offset
+// already folded into the table.  sign = +1 applies the rotation (forward), -1 its inverse (the backward pass:
+// the Jacobian of a rotation is the rotation by the opposite angle).  Channels >= rd are copied.
+// The reference's rotary helpers are mamba2hybrid/mamba2hybrid_attn.py:101-226 (applied at :428-430).
+// =====================================================================================
+__global__ void __launch_bounds__(256)
+rope_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, __nv_bfloat16* __restrict__ out, long long out_ld,
+            const float* __restrict__ cs, const float* __restrict__ sn, long long tokens, int L, int H, int Dh, int rd,
+            float sign) {
+  const int half = rd / 2;
+  const int vec_rot = half / 8;                 // 8-channel vectors in each rotated half
+  const int vec_rest = (Dh - rd) / 8;
+  const int per_head = vec_rot + vec_rest;
+  const long long total = tokens * H * per_head;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int v = (int)(i % per_head);
+    const long long th = i / per_head;
+    const int h = (int)(th % H);
+    const long long t = th / H;
+    const __nv_bfloat16* xr = x + t * x_ld + (long long)h * Dh;
+    __nv_bfloat16* orow = out + t * out_ld + (long long)h * Dh;
+    if (v >= vec_rot) {                          // pass-through channels
+      const int c = rd + (v - vec_rot) * 8;
+      *reinterpret_cast<uint4*>(orow + c) = *reinterpret_cast<const uint4*>(xr + c);
+      continue;
+    }
+    const int c = v * 8;
+    const uint4 a = *reinterpret_cast<const uint4*>(xr + c);
+    const uint4 b = *reinterpret_cast<const uint4*>(xr + half + c);
+    if (!SSM_INDEX_OK((long long)h * Dh + half + c + 7, x_ld) || !SSM_INDEX_OK((long long)h * Dh + half + c + 7, out_ld)) continue;
+    const float* cp = cs + (t % L) * half + c;
+    const float* sp = sn + (t % L) * half + c;
+    const float4 c0 = *reinterpret_cast<const float4*>(cp), c1 = *reinterpret_cast<const float4*>(cp + 4);
+    const float4 s0 = *reinterpret_cast<const float4*>(sp), s1 = *reinterpret_cast<const float4*>(sp + 4);
+    const float cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float ss[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    const uint32_t ap[4] = {a.x, a.y, a.z, a.w}, bp[4] = {b.x, b.y, b.z, b.w};
+    uint32_t o1[4], o2[4];
+    #pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float x1l = bf16_lo(ap[e]), x1h = bf16_hi(ap[e]), x2l = bf16_lo(bp[e]), x2h = bf16_hi(bp[e]);
+      const float sl = sign * ss[2 * e], sh = sign * ss[2 * e + 1];
+      o1[e] = pack_bf16(x1l * cc[2 * e] - x2l * sl, x1h * cc[2 * e + 1] - x2h * sh);
+      o2[e] = pack_bf16(x2l * cc[2 * e] + x1l * sl, x2h * cc[2 * e + 1] + x1h * sh);
+    }
+    *reinterpret_cast<uint4*>(orow + c) = make_uint4(o1[0], o1[1], o1[2], o1[3]);
+    *reinterpret_cast<uint4*>(orow + half + c) = make_uint4(o2[0], o2[1], o2[2], o2[3]);
+  }
+}
+
 // Row statistics that a GEMM epilogue produced per column tile -> one (max, sum exp(x - max)) per row.
 // tmax / tsum: [tiles][rows].
 __global__ void __launch_bounds__(256)
@@ -876,6 +930,21 @@ extern "C" int ssm_ce_partials(const void* logits, long long ld, int is_fp32, co
   else ce_partials_kernel<__nv_bfloat16><<<(unsigned)rows, 256, 0, st>>>(BF(logits), ld, lb, V, vocab_start, a, b, c);
   return (int)cudaGetLastError();
 }
+SSM_DEBUG_BOUNDS_GETTER(ssm_debug_bounds_elementwise)
+
+extern "C" int ssm_rope(const void* x, long long x_ld, void* out, long long out_ld, const void* cos_tab, const void* sin_tab,
+                        long long tokens, int L, int H, int Dh, int rd, int inverse, cudaStream_t st) {
+  if (tokens < 1 || L < 1 || H < 1 || rd < 16 || rd > Dh || rd % 16 || Dh % 8 || x_ld % 8 || out_ld % 8 ||
+      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(cos_tab) |
+        reinterpret_cast<uintptr_t>(sin_tab)) & 15))
+    return -SSM_ERR_BAD_ARG;
+  const long long total = tokens * H * (rd / 16 + (Dh - rd) / 8);
+  const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+  rope_kernel<<<blocks, 256, 0, st>>>(BF(x), x_ld, BFM(out), out_ld, reinterpret_cast<const float*>(cos_tab),
+                                      reinterpret_cast<const float*>(sin_tab), tokens, L, H, Dh, rd, inverse ? -1.f : 1.f);
+  return (int)cudaGetLastError();
+}
+
 extern "C" int ssm_ce_merge_tiles(const void* tmax, const void* tsum, int tiles, long long rows, void* omax, void* osum,
                                   cudaStream_t st) {
   if (tiles < 1 || rows < 1) return -SSM_ERR_BAD_ARG;

@@ -39,7 +39,7 @@ constexpr int EPI_BLOCK_COLS = 64;                       // bf16 columns per TMA
 constexpr int EPI_BUF_BYTES = GEMM_BM * EPI_BLOCK_COLS * 2;  // 16 KiB
 constexpr int MAX_SPLIT = 8;                             // K slices of a tail tile (upper bound of GemmParams::split)
 constexpr int MAX_UNITS = 160;                           // scheduling units (CTAs or pairs) the scratch is sized for
-constexpr int AG_MAX_GROUPS = 4;                         // row groups of a shard with a ready flag of their own
+constexpr int AG_MAX_GROUPS = 4;                         // column (K) groups of a shard with a ready flag of their own
 
 struct GemmParams {
   int M, N, K;
@@ -79,22 +79,29 @@ struct PeerPtrs { void* p[MAX_RANKS]; };
 //  * all-gather side (ag): the A operand is a gather buffer [nranks * rows_per_shard, K] in local memory that
 //    every rank fills by pushing its shard into all ranks' buffers.  One thread per CTA moves boxes of the local
 //    shard through shared memory (TMA load, then one TMA store per destination rank over NVLink) before the
-//    epilogue warps turn to their tiles; the CTA that completes a row group publishes flag[me][group] = seq on
-//    every rank.  Meanwhile the producer and MMA warps already work: tiles of the local shard read the shard
-//    itself (second tensor map), tiles of a remote shard wait (bounded) for the flag of exactly the row group they
-//    read, so a remote group is consumed as soon as its bytes have landed.  (No TMA load touches peer memory.)
+//    epilogue warps turn to their tiles.  The shard travels in up to four groups of columns (ranges of K), first
+//    columns first; the CTA that completes a group publishes flag[me][group] = seq on every rank.  Meanwhile the
+//    producer and MMA warps already work: tiles of the local shard read the shard itself (second tensor map);
+//    the main loop of a tile of a remote shard waits (bounded) for a column group only when it reaches that
+//    group's first k-block, so it starts when a quarter of the shard has landed and computes on it while the rest
+//    is still crossing NVLink.  (No TMA load touches peer memory.)
 //  * reduce-scatter side (rs, epilogue mode 3): output rows belong to owner = row / rows_per_owner; each tile is
 //    TMA-stored into the owner's landing slot for this rank (one tensor map per owner, peer memory), remote
 //    owners first; when all of this rank's tiles for an owner have landed, flag[me] = seq is published there.
 //    Tiles are visited owner by owner, this rank's own rows last.  With rs_out set the kernel also finishes the
-//    collective: the epilogue of a tile of this rank's own rows waits (bounded, once) for the flags of the other
-//    sources, adds their partial blocks from the landing zone to its fp32 accumulators and stores the reduced
-//    rows into rs_out; nothing of this rank's own partial ever takes the detour through the landing zone.
+//    collective, in one of two ways.  Two ranks (rs_tail = 0): the epilogue of a tile of this rank's own rows
+//    waits (bounded, once) for the flag of the other source, adds its partial block from the landing zone to the
+//    fp32 accumulators and stores the reduced rows into rs_out.  More ranks (rs_tail = 1): summing T - 1 blocks in
+//    the epilogues of the few CTAs that hold own tiles would be a long chain of dependent loads, so the own tiles
+//    store their partial into rs_out, and after its tiles every CTA of the grid waits (bounded) for the flags of
+//    all sources (this rank's included) and sums a slice: rs_out += the T - 1 landed blocks, fp32 accumulate.
+//    The waits are for flags that peers (or this grid's epilogues, which never wait for the tail) publish.
 struct GemmComm {
   int nranks, me, seq;          // sequence number of this call = *seq_base + seq (seq_base may be null)
   const int* seq_base;          // device counter advanced once per training step (keeps CUDA-graph replays unique)
   // all-gather side
-  int ag, rows_per_shard, ag_group_rows, ag_flag_base, ag_cols;
+  int ag, rows_per_shard, ag_group_kb, ag_flag_base, ag_cols;   // ag_group_kb: 64-column blocks per flag group
+  int ag_push_rows;                    // rows of a push box (128, 64 or 32)
   const int* ag_flags;                 // local flag array
   const __nv_bfloat16* ag_src; long long ag_src_ld;
   PeerPtrs ag_dst; long long ag_dst_ld;
@@ -106,6 +113,8 @@ struct GemmComm {
   PeerPtrs rs_land; long long rs_land_ld;   // landing slots as plain pointers (direct-store epilogue)
   const __nv_bfloat16* rs_land_local; long long rs_slot_stride;   // this rank's landing zone [nranks][rows][ld]
   __nv_bfloat16* rs_out; long long rs_out_ld;                     // reduced block [rows_per_owner, N] or null
+  int rs_tail;                         // how the partial blocks are summed into rs_out: 0 in the epilogues of this
+                                       // rank's own tiles, 1 by all CTAs after their tiles (see below)
 };
 // one tensor map per rank: the owners' landing slots (reduce-scatter) or the ranks' gather buffers (all-gather push)
 struct RsMaps { CUtensorMap m[MAX_RANKS]; };
@@ -203,7 +212,8 @@ template <int BN, int STAGES, bool PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                   const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_a_local,
-                  const GemmParams p, const GemmComm cm, const __grid_constant__ RsMaps rsm) {
+                  const __grid_constant__ CUtensorMap tmap_push, const GemmParams p, const GemmComm cm,
+                  const __grid_constant__ RsMaps rsm) {
   using L = GemmSmem<BN, STAGES, PAIR>;
   constexpr int CTAS_PER_UNIT = PAIR ? 2 : 1;
   extern __shared__ uint8_t smem_raw[];
@@ -232,7 +242,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     tma_prefetch_desc(&tmap_b);
     if (p.mode != 3 || cm.rs_out != nullptr) tma_prefetch_desc(&tmap_c);
     if (p.mode == 3 || cm.ag) for (int t = 0; t < cm.nranks; ++t) tma_prefetch_desc(&rsm.m[t]);
-    if (cm.ag) tma_prefetch_desc(&tmap_a_local);
+    if (cm.ag) { tma_prefetch_desc(&tmap_a_local); tma_prefetch_desc(&tmap_push); }
   }
   constexpr int TMEM_COLS = 2 * BN <= 256 ? 256 : 512;      // allocation sizes are powers of two
   if (warp == 1) {
@@ -266,23 +276,27 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         const int nb0 = n0 + cta_rank * L::B_ROWS;         // first B row (= output column) this CTA loads
         const CUtensorMap* ta = &tmap_a;
         int am0 = m0;
+        int remote_shard = -1;                             // >= 0: the rows come from that rank's push
         if (cm.ag) {
           const int shard = m0 / cm.rows_per_shard;
           if (shard == cm.me) {
             ta = &tmap_a_local;                            // the local shard is read in place
             am0 = m0 - shard * cm.rows_per_shard;
-          } else if (m0 < p.M) {
-            const int grp = (m0 - shard * cm.rows_per_shard) / cm.ag_group_rows;
-            const uint32_t bit = 1u << (shard * AG_MAX_GROUPS + grp);
+          } else if (m0 < p.M && do_a) {
+            remote_shard = shard;
+          }
+        }
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
+          if (remote_shard >= 0) {
+            const int grp = kb / cm.ag_group_kb;
+            const uint32_t bit = 1u << (remote_shard * AG_MAX_GROUPS + grp);
             if (!(group_seen & bit)) {
-              if (!wait_flag(cm.ag_flags + cm.ag_flag_base + shard * AG_MAX_GROUPS + grp, seqv, p.status)) { ok = false; break; }
-              fence_proxy_async_all();      // rows were written by generic-proxy stores of peer SMs
+              if (!wait_flag(cm.ag_flags + cm.ag_flag_base + remote_shard * AG_MAX_GROUPS + grp, seqv, p.status)) { ok = false; break; }
+              fence_proxy_async_all();      // the columns were written by the peer's bulk stores; TMA reads them
               if (group_seen == 0) trace_mark(p, 12);
               group_seen |= bit;
             }
           }
-        }
-        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status)) { ok = false; break; }
           uint8_t* sa = smem + stage * L::STAGE_BYTES;
           uint8_t* sb = sa + L::A_BYTES;
@@ -392,15 +406,18 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     uint8_t* epi_buf = smem + L::EPI_OFF;
 
     if (cm.ag) {
-      // -------- all-gather push: the local shard goes to every rank's gather buffer in boxes of 128 rows x 64
-      // columns (16 KB): TMA load into the (still idle) epilogue staging buffers, one TMA store per destination.
-      // One thread per CTA drives it; the boxes of a row group are dealt round-robin over the CTAs of the grid, and
-      // the CTA that completes a group publishes its flag on every rank.  The bulk copies leave the load/store
-      // units and their path to L2 alone, which the main loop running next to them needs.
+      // -------- all-gather push: the local shard goes to every rank's gather buffer in boxes of 128 / 64 / 32 rows x
+      // 64 columns: TMA load into the (still idle) epilogue staging buffers, one TMA store per destination.  One
+      // thread per CTA drives it.  The boxes are dealt round-robin over the CTAs of the grid, column group by column
+      // group, and the host picks the box height so that every CTA gets about one box per group: all SMs push the
+      // first columns first, which is what lets remote tiles start early.  The CTA that completes a group publishes
+      // its flag on every rank.  The bulk copies leave the load/store units and their path to L2 alone, which the
+      // main loop running next to them needs.
       if (epi_tid == 0) {
-        const int boxes_per_row = (cm.ag_cols + 63) / 64;
-        const int boxes_per_group = (cm.ag_group_rows / GEMM_BM) * boxes_per_row;
-        const int ngroups = cm.rows_per_shard / cm.ag_group_rows;
+        const int col_blocks = (cm.ag_cols + 63) / 64;                 // 64-column blocks of the shard
+        const int row_blocks = cm.rows_per_shard / cm.ag_push_rows;
+        const uint32_t box_bytes = (uint32_t)cm.ag_push_rows * 128u;
+        const int ngroups = (col_blocks + cm.ag_group_kb - 1) / cm.ag_group_kb;
         const int grid = (int)gridDim.x;
         uint32_t phase = 0;
         int committed = 0;                          // boxes (bulk groups) committed so far
@@ -408,15 +425,19 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         bool pok = true;
         // issue everything first: load a box, store it to every rank; the only waits are for a staging buffer to
         // be readable again
+        int dealt = 0;                              // boxes dealt so far over all CTAs (round-robin start of a group)
         for (int g = 0; g < ngroups && pok; ++g) {
-          const int start = ((int)blockIdx.x - (int)(((long long)g * boxes_per_group) % grid) + grid) % grid;
-          for (int b = start; b < boxes_per_group; b += grid) {
-            const int row = g * cm.ag_group_rows + (b / boxes_per_row) * GEMM_BM;
-            const int col = (b % boxes_per_row) * 64;
+          const int cols_g = min(cm.ag_group_kb, col_blocks - g * cm.ag_group_kb);
+          const int boxes_g = cols_g * row_blocks;
+          const int start = ((int)blockIdx.x - dealt % grid + grid) % grid;
+          dealt += boxes_g;
+          for (int b = start; b < boxes_g; b += grid) {
+            const int row = (b / cols_g) * cm.ag_push_rows;
+            const int col = (g * cm.ag_group_kb + b % cols_g) * 64;
             uint8_t* buf = epi_buf + (committed & 1) * EPI_BUF_BYTES;
             asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");     // the stores that last read this buffer
-            mbar_expect_tx(push_bar, EPI_BUF_BYTES);
-            tma_load_2d(buf, &tmap_a_local, col, row, push_bar);
+            mbar_expect_tx(push_bar, box_bytes);
+            tma_load_2d(buf, &tmap_push, col, row, push_bar);
             if (!mbar_wait(push_bar, phase, p.status)) { pok = false; break; }
             phase ^= 1;
             #pragma unroll 1
@@ -510,7 +531,8 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       // the epilogue (they computed this rank's rows before their own, so their data is normally waiting); the first
       // such tile makes sure of it (bounded wait for the flags of all other sources)
       const bool own = cm.rs && cm.rs_out != nullptr && owner == cm.me;
-      if (own && !rs_seen && ok) {
+      const bool own_sum = own && !cm.rs_tail;        // this epilogue adds the other sources' blocks itself
+      if (own_sum && !rs_seen && ok) {
         uint32_t mine = 1u, all;
         if (epi_tid < cm.nranks && epi_tid != cm.me) {
           const int* flags = reinterpret_cast<const int*>(cm.flag_ptrs.p[cm.me]);
@@ -559,7 +581,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         run_epilogue = run_epilogue && (*epi_flag != 0);
         others = p.ws + ((size_t)(w.tail * p.split) * CTAS_PER_UNIT + cta_rank) * (GEMM_BM * BN);
       }
-      if (run_epilogue && cm.rs && !own) {
+      if (run_epilogue && cm.rs && !own_sum) {
         if (owner != rs_owner) {
           if (rs_pending > 0) rs_report(rs_owner, rs_pending);
           rs_owner = owner;
@@ -676,7 +698,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             uint8_t* buf = epi_buf + (stores_issued & 1) * EPI_BUF_BYTES;
             if (epi_tid == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
             asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (own) {
+            if (own_sum) {
               const long long r_in = (long long)(m0 - owner * cm.rows_per_owner + row);
               for (int src_rank = 0; src_rank < cm.nranks; ++src_rank) {      // fixed order: reproducible sums
                 if (src_rank == cm.me) continue;
@@ -836,6 +858,65 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (cm.rs && cm.rs_out != nullptr && cm.rs_tail) {
+    // ------------------------------------------------------------------ reduce-scatter tail (more than two ranks)
+    // rs_out holds this rank's own partial block; every CTA adds a slice of the T - 1 blocks that the other sources
+    // stored into this rank's landing zone.  The wait is for flags only.
+    if ((int)threadIdx.x < cm.nranks) {
+      const int* flags = reinterpret_cast<const int*>(cm.flag_ptrs.p[cm.me]);
+      if (!wait_flag(flags + cm.rs_flag_base + threadIdx.x, seqv, p.status)) *epi_flag = -1;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) trace_mark(p, 13);
+    if (*epi_flag != -1) {
+      const int vec_per_row = p.N / 8;
+      const long long total = (long long)cm.rows_per_owner * vec_per_row;
+      const long long stride = (long long)gridDim.x * GEMM_THREADS;
+      constexpr int U = 4;                       // vectors in flight per thread and source
+      for (long long i0 = (long long)blockIdx.x * GEMM_THREADS + threadIdx.x; i0 < total; i0 += stride * U) {
+        float a[U][8];
+        long long off_in[U], off_out[U];
+        #pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i = i0 + u * stride;
+          const long long r = i / vec_per_row;
+          const int c = (int)(i - r * vec_per_row) * 8;
+          off_in[u] = r * cm.rs_land_ld + c;
+          off_out[u] = r * cm.rs_out_ld + c;
+        }
+        for (int s = -1; s < cm.nranks; ++s) {     // own partial first, then the sources in rank order: reproducible
+          if (s == cm.me) continue;
+          uint4 v[U];
+          #pragma unroll
+          for (int u = 0; u < U; ++u)
+            if (i0 + u * stride < total)
+              v[u] = __ldcg(reinterpret_cast<const uint4*>(s < 0 ? cm.rs_out + off_out[u]
+                                                                   : cm.rs_land_local + s * cm.rs_slot_stride + off_in[u]));
+          #pragma unroll
+          for (int u = 0; u < U; ++u) {
+            if (i0 + u * stride < total) {
+              if (s < 0) {
+                a[u][0] = bf16_lo(v[u].x); a[u][1] = bf16_hi(v[u].x); a[u][2] = bf16_lo(v[u].y); a[u][3] = bf16_hi(v[u].y);
+                a[u][4] = bf16_lo(v[u].z); a[u][5] = bf16_hi(v[u].z); a[u][6] = bf16_lo(v[u].w); a[u][7] = bf16_hi(v[u].w);
+              } else {
+                a[u][0] += bf16_lo(v[u].x); a[u][1] += bf16_hi(v[u].x); a[u][2] += bf16_lo(v[u].y); a[u][3] += bf16_hi(v[u].y);
+                a[u][4] += bf16_lo(v[u].z); a[u][5] += bf16_hi(v[u].z); a[u][6] += bf16_lo(v[u].w); a[u][7] += bf16_hi(v[u].w);
+              }
+            }
+          }
+        }
+        #pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (i0 + u * stride < total) {
+            uint4 o;
+            o.x = pack_bf16(a[u][0], a[u][1]); o.y = pack_bf16(a[u][2], a[u][3]);
+            o.z = pack_bf16(a[u][4], a[u][5]); o.w = pack_bf16(a[u][6], a[u][7]);
+            *reinterpret_cast<uint4*>(cm.rs_out + off_out[u]) = o;
+          }
+        }
+      }
+    }
+  }
   if (threadIdx.x == 0) trace_mark(p, 10);
   if (PAIR) {
     // neither CTA may leave (or free TMEM) while its partner can still signal its barriers or read its shared memory
@@ -950,7 +1031,7 @@ static TileChoice pick_tile(int M, int N, int K, int b_mn, int allow_pair) {
 template <int BN, int STAGES, bool PAIR>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, GemmParams p,
                        cudaStream_t stream, const GemmComm* comm = nullptr, const RsMaps* maps = nullptr,
-                       const CUtensorMap* ta_local = nullptr) {
+                       const CUtensorMap* ta_local = nullptr, const CUtensorMap* ta_push = nullptr) {
   using L = GemmSmem<BN, STAGES, PAIR>;
   static bool configured = false;
   auto kern = gemm_bf16_tcgen05<BN, STAGES, PAIR>;
@@ -1021,7 +1102,8 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, ta_local ? *ta_local : ta, p, cm, maps ? *maps : no_maps);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, ta_local ? *ta_local : ta, ta_push ? *ta_push : ta, p, cm,
+                                     maps ? *maps : no_maps);
   if (e != cudaSuccess) return (int)e;
   return (int)cudaGetLastError();
 }
@@ -1130,14 +1212,27 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
   ta_local = ta;
   RsMaps maps;
   memset(&maps, 0, sizeof(maps));
+  CUtensorMap ta_push = ta;
+  GemmComm cm_local;
+  if (comm != nullptr) cm_local = *comm;
   if (comm != nullptr && comm->ag) {
     r = make_tmap_2d_bf16(&ta_local, comm->ag_src, (uint64_t)K, (uint64_t)comm->rows_per_shard,
                           (uint64_t)comm->ag_src_ld * 2, 64, 128);
     if (r) return -500 - r;
+    // push boxes: as tall as possible while every CTA still gets about one box per column group
+    const int col_blocks = (K + GEMM_BK - 1) / GEMM_BK;
+    int push_rows = 128;
+    while (push_rows > 32 && (long long)(comm->rows_per_shard / push_rows) * col_blocks < 3LL * g_num_sms) push_rows /= 2;
+    cm_local.ag_push_rows = push_rows;
+    r = make_tmap_2d_bf16(&ta_push, comm->ag_src, (uint64_t)K, (uint64_t)comm->rows_per_shard,
+                          (uint64_t)comm->ag_src_ld * 2, 64, (uint32_t)push_rows);
+    if (r) return -500 - r;
     for (int t = 0; t < comm->nranks; ++t) {      // every rank's gather buffer: destinations of the shard push
-      r = make_tmap_2d_bf16(&maps.m[t], comm->ag_dst.p[t], (uint64_t)K, (uint64_t)M, (uint64_t)comm->ag_dst_ld * 2, 64, 128);
+      r = make_tmap_2d_bf16(&maps.m[t], comm->ag_dst.p[t], (uint64_t)K, (uint64_t)M, (uint64_t)comm->ag_dst_ld * 2, 64,
+                            (uint32_t)push_rows);
       if (r) return -600 - r;
     }
+    comm = &cm_local;
   }
   if (comm != nullptr && comm->rs) {
     for (int t = 0; t < comm->nranks; ++t) {
@@ -1166,18 +1261,18 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
   }
   const RsMaps* mp = (comm != nullptr && (comm->rs || comm->ag)) ? &maps : nullptr;
   if (pair) {
-    if (BN == 256) return launch_gemm<256, 6, true>(ta, tb, tc, p, stream, comm, mp, &ta_local);
-    return launch_gemm<128, 8, true>(ta, tb, tc, p, stream, comm, mp, &ta_local);
+    if (BN == 256) return launch_gemm<256, 6, true>(ta, tb, tc, p, stream, comm, mp, &ta_local, &ta_push);
+    return launch_gemm<128, 8, true>(ta, tb, tc, p, stream, comm, mp, &ta_local, &ta_push);
   }
-  if (BN == 256) return launch_gemm<256, 4, false>(ta, tb, tc, p, stream, comm, mp, &ta_local);
-  if (BN == 192) return launch_gemm<192, 4, false>(ta, tb, tc, p, stream, comm, mp, &ta_local);
-  return launch_gemm<128, 6, false>(ta, tb, tc, p, stream, comm, mp, &ta_local);
+  if (BN == 256) return launch_gemm<256, 4, false>(ta, tb, tc, p, stream, comm, mp, &ta_local, &ta_push);
+  if (BN == 192) return launch_gemm<192, 4, false>(ta, tb, tc, p, stream, comm, mp, &ta_local, &ta_push);
+  return launch_gemm<128, 6, false>(ta, tb, tc, p, stream, comm, mp, &ta_local, &ta_push);
 }
 
 // GEMM fused with a tensor-parallel collective over peer memory (see GemmComm).
 //   ag = 1: A must be this rank's gather buffer [nranks * rows_per_shard, K] (= ag_dst_ptrs[me], row stride
 //           ag_dst_ld); ag_src is the local shard [rows_per_shard, K]; flag_ptrs[t] is rank t's flag array; the
-//           ready flags of this call are flag_ptrs[t][ag_flag_base + source * 4 + row group]; ag_counter points at
+//           ready flags of this call are flag_ptrs[t][ag_flag_base + source * 4 + column group]; ag_counter points at
 //           4 local ints that are zero between launches.
 //   rs = 1: mode is forced to 3; land_ptrs[o] is the base of the [rows_per_owner, N] slot this rank owns inside
 //           rank o's landing zone (row stride land_ld); C is ignored.  With rs_out the kernel also reduces: the
@@ -1210,10 +1305,9 @@ extern "C" int ssm_gemm_bf16_fused(const void* A, const void* B, void* C, int M,
   for (int t = 0; t < MAX_RANKS; ++t) cm.flag_ptrs.p[t] = t < nranks ? const_cast<void*>(flag_ptrs[t]) : nullptr;
   if (ag) {
     cm.ag = 1; cm.rows_per_shard = rows_per_shard; cm.ag_flag_base = ag_flag_base;
-    // at most AG_MAX_GROUPS row groups per shard, each a multiple of 128 rows
-    int group = GEMM_BM;
-    while (rows_per_shard / group > AG_MAX_GROUPS || rows_per_shard % group) group += GEMM_BM;
-    cm.ag_group_rows = group;
+    // at most AG_MAX_GROUPS column groups per shard, each a whole number of 64-column blocks
+    const int col_blocks = (K + GEMM_BK - 1) / GEMM_BK;
+    cm.ag_group_kb = (col_blocks + AG_MAX_GROUPS - 1) / AG_MAX_GROUPS;
     cm.ag_cols = K; cm.ag_flags = reinterpret_cast<const int*>(flag_ptrs[me]);
     cm.ag_src = reinterpret_cast<const __nv_bfloat16*>(ag_src); cm.ag_src_ld = ag_src_ld;
     for (int t = 0; t < MAX_RANKS; ++t) cm.ag_dst.p[t] = t < nranks ? const_cast<void*>(ag_dst_ptrs[t]) : nullptr;
@@ -1226,6 +1320,7 @@ extern "C" int ssm_gemm_bf16_fused(const void* A, const void* B, void* C, int M,
     cm.rs_land_local = reinterpret_cast<const __nv_bfloat16*>(rs_land_local);
     cm.rs_slot_stride = rs_slot_stride;
     cm.rs_out = reinterpret_cast<__nv_bfloat16*>(rs_out); cm.rs_out_ld = rs_out_ld;
+    cm.rs_tail = env_int("SSM_RS_TAIL", nranks > 2 ? 1 : 0) ? 1 : 0;
   }
   GemmExtra ex = {ce_labels, ce_vocab_start, ce_max, ce_sum, ce_tgt};
   return gemm_bf16_impl(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, mode, bias, act, status, stream, nullptr,

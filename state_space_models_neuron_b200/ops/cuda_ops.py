@@ -810,6 +810,21 @@ def ssd_chunk_scan(x, dt_raw, A, Bm, Cm, D, dt_bias, chunk_size, initial_state, 
 # ======================================================================================
 # decode
 # ======================================================================================
+_DECODE_PARAMS = {}
+
+
+def _decode_params_fp32(A_log, D, dt_bias):
+    """(-exp(A_log), D, dt_bias) in fp32 for the decode kernel, prepared once per parameter version instead of three
+    casts per layer and token (inference leaves the parameters untouched, so this is once per model)."""
+    key = (A_log.data_ptr(), D.data_ptr(), dt_bias.data_ptr())
+    ver = (A_log._version, D._version, dt_bias._version)
+    hit = _DECODE_PARAMS.get(key)
+    if hit is None or hit[0] != ver:
+        hit = (ver, _mixer_params_fp32(A_log.detach(), D.detach(), dt_bias.detach()))
+        _DECODE_PARAMS[key] = hit
+    return hit[1]
+
+
 @torch.no_grad()
 def ssm_decode_step(zxBCdt, conv_state, ssm_state, conv_w, conv_b, dt_bias, A_log, D, norm_w, d_inner, n_groups,
                     d_state, head_dim, eps, norm_group_size):
@@ -829,11 +844,59 @@ def ssm_decode_step(zxBCdt, conv_state, ssm_state, conv_w, conv_b, dt_bias, A_lo
     _run("ssm_decode_conv_step", _p(xBC), _ll(zxBCdt.stride(0)), _p(conv_state), _p(conv_w.reshape(C, 4).contiguous()),
          _p(conv_b), _p(act), B, C, _st())
     y = torch.empty(B, d_inner, dtype=torch.bfloat16, device=dev)
-    A = -torch.exp(A_log.float())
-    _run("ssm_decode_ssm_step", _p(act), _p(zxBCdt[:, d_inner + C:]), _ll(zxBCdt.stride(0)), _p(dt_bias.float()),
-         _p(A), _p(D.float()), _p(ssm_state), _p(y), B, C, H, head_dim, d_state, n_groups, d_inner, _st())
+    A, Df, bf = _decode_params_fp32(A_log, D, dt_bias)
+    _run("ssm_decode_ssm_step", _p(act), _p(zxBCdt[:, d_inner + C:]), _ll(zxBCdt.stride(0)), _p(bf),
+         _p(A), _p(Df), _p(ssm_state), _p(y), B, C, H, head_dim, d_state, n_groups, d_inner, _st())
     gs = d_inner if norm_group_size is None else norm_group_size
     return _gated_fwd(y, zxBCdt[:, :d_inner], norm_w, eps, gs)
+
+
+# ======================================================================================
+# rotary position embedding
+# ======================================================================================
+_ROPE_TABLES = {}
+
+
+def rotary_tables(seq_len: int, dim: int, theta: float, device, offset: int = 0):
+    """fp32 cos / sin tables [seq_len, dim / 2], built once per (length, dim, theta, offset, device) and kept."""
+    key = (int(seq_len), int(dim), float(theta), int(offset), str(device))
+    if key not in _ROPE_TABLES:
+        from . import oracle
+        cos, sin = oracle.rotary_tables(seq_len, dim, theta, device=device, offset=offset)
+        _ROPE_TABLES[key] = (cos.contiguous(), sin.contiguous())
+    return _ROPE_TABLES[key]
+
+
+def _rope_launch(x, cos, sin, inverse: bool):
+    B, L, H, Dh = x.shape
+    rd = cos.shape[-1] * 2
+    x3 = x if (x.stride(3) == 1 and x.stride(2) == Dh and x.stride(0) == L * x.stride(1)) else x.contiguous()
+    out = torch.empty(B, L, H, Dh, dtype=x.dtype, device=x.device)
+    _run("ssm_rope", _p(x3), _ll(x3.stride(1)), _p(out), _ll(H * Dh), _p(cos), _p(sin), _ll(B * L), L, H, Dh, rd,
+         int(inverse), _st())
+    return out
+
+
+class _Rope(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cos, sin):
+        ctx.save_for_backward(cos, sin)
+        return _rope_launch(x, cos, sin, False)
+
+    @staticmethod
+    def backward(ctx, dy):
+        cos, sin = ctx.saved_tensors
+        return _rope_launch(dy, cos, sin, True), None, None
+
+
+def apply_rotary(x, cos, sin):
+    """Rotate-half rotary embedding on the first 2 * cos.shape[-1] channels of x [B, L, H, Dh] (bf16); cos / sin fp32
+    [L, rd / 2].  The backward pass is the same kernel with the angle negated."""
+    _require_bf16(x)
+    rd = cos.shape[-1] * 2
+    if x.shape[-1] % 8 or rd % 16 or cos.dtype != torch.float32 or cos.shape[0] != x.shape[1]:
+        raise ValueError("rotary kernel needs head_dim % 8 == 0, rotary dim % 16 == 0 and fp32 tables of the sequence length")
+    return _Rope.apply(x, cos, sin)
 
 
 # ======================================================================================

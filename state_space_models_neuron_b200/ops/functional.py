@@ -45,6 +45,20 @@ def linear_ce(x: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor, vocab
     return F.linear(x, weight), None
 
 
+def rotary_tables(seq_len: int, dim: int, theta: float, device=None, offset: int = 0):
+    """cos / sin tables [seq_len, dim / 2] in fp32 (cached on the GPU path)."""
+    if device is not None and torch.device(device).type == "cuda" and not _BASELINE[0]:
+        return _cuda().rotary_tables(seq_len, dim, theta, device, offset)
+    return oracle.rotary_tables(seq_len, dim, theta, device=device, offset=offset)
+
+
+def apply_rotary(x, cos, sin):
+    """Rotary position embedding (rotate-half) on the leading channels of every head of x [B, L, H, Dh]."""
+    if _native(x) and x.dtype == torch.bfloat16:
+        return _cuda().apply_rotary(x, cos, sin)
+    return oracle.apply_rotary(x, cos, sin)
+
+
 # ---- conv ---------------------------------------------------------------------------------
 def causal_conv1d_silu(x, weight, bias, initial_state=None):
     """Depthwise causal conv (taps = weight.shape[-1]) + SiLU on channels-last x [B,L,C]."""

@@ -20,6 +20,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_HERE, "csrc")
 OUT_DIR = os.path.join(_HERE, "_native")
 LIB_PATH = os.path.join(OUT_DIR, "libssm_b200.so")
+DEBUG_LIB_PATH = os.path.join(OUT_DIR, "libssm_b200_debug.so")       # same sources with -DSSM_DEBUG_BOUNDS
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--use_fast_math", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]
 _lock = threading.Lock()
@@ -48,29 +49,34 @@ def _source_hash() -> str:
     return h.hexdigest()
 
 
-def is_current() -> bool:
-    stamp = os.path.join(OUT_DIR, "build.hash")
-    if not (os.path.exists(LIB_PATH) and os.path.exists(stamp)):
+def is_current(debug: bool = False) -> bool:
+    stamp = os.path.join(OUT_DIR, "build_debug.hash" if debug else "build.hash")
+    if not (os.path.exists(DEBUG_LIB_PATH if debug else LIB_PATH) and os.path.exists(stamp)):
         return False
     with open(stamp) as f:
         return f.read().strip() == _source_hash()
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile all kernels (parallel over files) and link the shared library.  Returns its path."""
+def build(force: bool = False, verbose: bool = False, debug: bool = False) -> str:
+    """Compile all kernels (parallel over files) and link the shared library.  Returns its path.
+    `debug=True` builds a second library, `libssm_b200_debug.so`, from the same sources with -DSSM_DEBUG_BOUNDS:
+    device-side index checks that record the first violation in a status array and skip the access (no trap);
+    `debug_bounds(lib)` reads the record."""
     import fcntl
     os.makedirs(OUT_DIR, exist_ok=True)
+    lib_path = DEBUG_LIB_PATH if debug else LIB_PATH
     # one builder at a time, across threads and across processes (several ranks may find a stale library at once)
     with _lock, open(os.path.join(OUT_DIR, "build.lock"), "w") as lockf:
         fcntl.flock(lockf, fcntl.LOCK_EX)
-        if not force and is_current():
-            return LIB_PATH
+        if not force and is_current(debug):
+            return lib_path
         nvcc = _nvcc()
-        tag = f".{os.getpid()}"
+        tag = f".{os.getpid()}" + (".dbg" if debug else "")
+        extra = ["-DSSM_DEBUG_BOUNDS"] if debug else []
 
         def compile_one(src):
             obj = os.path.join(OUT_DIR, src[:-3] + tag + ".o")
-            cmd = [nvcc, *NVCC_FLAGS, "-I", CSRC, "-c", os.path.join(CSRC, src), "-o", obj]
+            cmd = [nvcc, *NVCC_FLAGS, *extra, "-I", CSRC, "-c", os.path.join(CSRC, src), "-o", obj]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             r = subprocess.run(cmd, capture_output=True, text=True)
@@ -82,17 +88,17 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
         with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as ex:
             objs = list(ex.map(compile_one, _sources()))
-        tmp = LIB_PATH + tag + ".tmp"
+        tmp = lib_path + tag + ".tmp"
         r = subprocess.run([nvcc, "-shared", "-o", tmp, *objs, "-gencode", "arch=compute_100a,code=sm_100a"],
                            capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-        os.replace(tmp, LIB_PATH)
+        os.replace(tmp, lib_path)
         for o in objs:
             os.remove(o)
-        with open(os.path.join(OUT_DIR, "build.hash"), "w") as f:
+        with open(os.path.join(OUT_DIR, "build_debug.hash" if debug else "build.hash"), "w") as f:
             f.write(_source_hash())
-        return LIB_PATH
+        return lib_path
 
 
 def lib() -> ctypes.CDLL:
@@ -102,6 +108,35 @@ def lib() -> ctypes.CDLL:
             build()
         _lib = ctypes.CDLL(LIB_PATH)
     return _lib
+
+
+_debug_lib = None
+
+
+def debug_lib() -> ctypes.CDLL:
+    """The -DSSM_DEBUG_BOUNDS build (built on first use), for tests and for chasing a suspected bad index."""
+    global _debug_lib
+    if _debug_lib is None:
+        if not is_current(debug=True):
+            build(debug=True)
+        _debug_lib = ctypes.CDLL(DEBUG_LIB_PATH)
+    return _debug_lib
+
+
+def debug_bounds(library: ctypes.CDLL, reset: bool = True):
+    """First failed index check of each source file since the last reset: {file: (code, line, index, limit)} for the
+    files that recorded one (empty dict: all checks passed; always empty for the regular build)."""
+    out = {}
+    for name in ("elementwise", "comm", "decode"):
+        rec = (ctypes.c_int * 4)()
+        fn = getattr(library, f"ssm_debug_bounds_{name}")
+        fn.restype = ctypes.c_int
+        code = fn(rec, int(reset))
+        if code != 0:
+            raise RuntimeError(f"reading the debug record of {name} failed with cudaError {code}")
+        if rec[0] != 0:
+            out[name] = tuple(rec)
+    return out
 
 
 def check(code: int, what: str) -> None:

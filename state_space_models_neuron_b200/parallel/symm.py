@@ -5,8 +5,8 @@ addresses of all peers' copies; the fused kernels take those addresses and move 
 NVLink.  Layout (per rank):
 
     flags    int32 [4 kinds][2 parities][32 slots]     published sequence numbers.  The all-gather kind uses slot
-                                                       source * 4 + row group (a shard becomes consumable group by
-                                                       group), the other kinds (reduce-scatter, small all-reduce,
+                                                       source * 4 + column group (a shard becomes consumable group
+                                                       by group), the other kinds (reduce-scatter, small all-reduce,
                                                        embedding) use slot = source
     gather   2 x [rows_total, cols] bf16              all-gather destinations, alternating by call parity
     land     2 x [nranks][rows_per_owner, cols] bf16  reduce-scatter landing zones, alternating by call parity
@@ -35,7 +35,7 @@ import torch.distributed as dist
 KIND_AG, KIND_RS, KIND_AR, KIND_EMB = 0, 1, 2, 3
 N_KINDS = 4
 MAX_RANKS = 8
-AG_GROUPS = 4                      # row groups per shard with a ready flag of their own (all-gather)
+AG_GROUPS = 4                      # column groups per shard with a ready flag of their own (all-gather)
 FLAG_SLOTS = MAX_RANKS * AG_GROUPS
 N_FLAGS = N_KINDS * 2 * FLAG_SLOTS
 SMALL_N_MAX = 16384

@@ -196,7 +196,9 @@ def test_all_gather_gemm_one_rank_of_T(T, me, Ls, K, N, b_mn):
         full = torch.cat(shards).float()
         ref = full @ (w.float() if b_mn else w.float().t())
         _close(y, ref, atol=0.02 * K ** 0.5 * 0.25 + 0.02)
-        groups = min(AG_GROUPS, Ls // 128)
+        kb = (K + 63) // 64
+        per = (kb + AG_GROUPS - 1) // AG_GROUPS
+        groups = (kb + per - 1) // per                     # column groups of the shard, each with its own flag
         for t in range(T):
             assert torch.equal(gathers[t][me * Ls:(me + 1) * Ls], shards[me]), f"push to rank {t} incomplete"
             got = flags[t][base + me * AG_GROUPS: base + me * AG_GROUPS + groups]

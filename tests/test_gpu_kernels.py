@@ -407,3 +407,68 @@ def test_gradient_norm_from_wgrad_epilogues():
         opt.step()
         got = float(opt.last_grad_norm)
         assert abs(got - want) <= 2e-4 * want, (micro_steps, got, want)
+
+
+@pytest.mark.parametrize("rd", [128, 64])
+def test_rotary_embedding_fwd_bwd(rd):
+    """Rotary kernel (forward and its inverse rotation as backward) against the fp32 oracle, full and partial
+    rotary dimension, on a strided view like the one the attention block passes."""
+    from state_space_models_neuron_b200 import ops
+    from state_space_models_neuron_b200.ops import oracle
+    g = torch.Generator(device="cuda").manual_seed(21)
+    B, L, H, Dh = 2, 256, 4, 128
+    x = torch.randn(B, L, H * Dh, device="cuda", generator=g).bfloat16().requires_grad_(True)
+    cos, sin = ops.rotary_tables(L, rd, 10000.0, device=x.device)
+    assert ops.rotary_tables(L, rd, 10000.0, device=x.device)[0] is cos          # cached, not rebuilt
+    y = ops.apply_rotary(x.view(B, L, H, Dh), cos, sin)
+    gy = torch.randn(y.shape, device="cuda", generator=g).bfloat16()
+    y.backward(gy)
+    xr = x.detach().float().requires_grad_(True)
+    yr = oracle.apply_rotary(xr.view(B, L, H, Dh), cos, sin)
+    yr.backward(gy.float())
+    _close(y, yr, atol=2e-2, rtol=1e-2, frac=1.0)
+    _close(x.grad, xr.grad, atol=2e-2, rtol=1e-2, frac=1.0)
+
+
+def test_debug_bounds_build_reports_bad_index_without_faulting():
+    """The -DSSM_DEBUG_BOUNDS library runs the same kernels with device-side index checks.  A consistent call leaves
+    no record and gives the regular library's result; a call whose declared row width is too small for the layout it
+    describes (the buffers themselves are large enough, so nothing can fault) is caught: the record names the check,
+    the kernel skips the access and the context stays usable."""
+    import ctypes
+    from state_space_models_neuron_b200.ops import native
+    dbg, reg = native.debug_lib(), native.lib()
+    assert native.debug_bounds(dbg) == {}
+    B, H, P, N, G = 2, 4, 64, 128, 2
+    d_in, C = H * P, H * P + 2 * G * N
+    g = torch.Generator(device="cuda").manual_seed(4)
+    act = torch.randn(B, C, device="cuda", generator=g)
+    dt_raw = torch.randn(B, 8, device="cuda", generator=g).bfloat16()
+    dt_bias, A, D = torch.zeros(H, device="cuda"), -torch.ones(H, device="cuda"), torch.ones(H, device="cuda")
+    state0 = torch.randn(B, H, P, N, device="cuda", generator=g)
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def step(lib, c_arg):
+        state = state0.clone()
+        y = torch.full((B, d_in), float("nan"), device="cuda", dtype=torch.bfloat16)
+        fn = lib.ssm_decode_ssm_step
+        fn.restype = ctypes.c_int
+        code = fn(ctypes.c_void_p(act.data_ptr()), ctypes.c_void_p(dt_raw.data_ptr()), ctypes.c_longlong(8),
+                  ctypes.c_void_p(dt_bias.data_ptr()), ctypes.c_void_p(A.data_ptr()), ctypes.c_void_p(D.data_ptr()),
+                  ctypes.c_void_p(state.data_ptr()), ctypes.c_void_p(y.data_ptr()), B, c_arg, H, P, N, G, d_in, st)
+        torch.cuda.synchronize()
+        assert code == 0
+        return y, state
+
+    y_ref, s_ref = step(reg, C)
+    y_dbg, s_dbg = step(dbg, C)
+    assert torch.equal(y_ref, y_dbg) and torch.equal(s_ref, s_dbg) and not torch.isnan(y_dbg.float()).any()
+    assert native.debug_bounds(dbg) == {}
+    # declared width 8 short of x | B | C: the check fires, nothing is read or written
+    y_bad, s_bad = step(dbg, C - 8)
+    rec = native.debug_bounds(dbg)
+    assert set(rec) == {"decode"} and rec["decode"][0] == 4 and rec["decode"][2] == C - 1 and rec["decode"][3] == C - 8
+    assert torch.isnan(y_bad.float()).all() and torch.equal(s_bad, state0)
+    assert native.debug_bounds(dbg) == {}                          # reading resets the record
+    y_again, _ = step(dbg, C)                                      # the context is still usable
+    assert torch.equal(y_again, y_ref)

@@ -35,7 +35,11 @@ fi
 WORLD=$((GPUS_PER_NODE * NODES))
 DP=$((WORLD / TP_DEGREE))
 ACC_STEPS=$((GBS / MBS / DP))
-echo "world=$WORLD tp=$TP_DEGREE dp=$DP acc_steps=$ACC_STEPS"
+# CUDA graphs: every micro-step (forward + backward + fused collectives) and the optimizer update replay as captured
+# graphs, which takes the host out of the loop (thousands of launches per micro-step); CUDA_GRAPH=0 runs eagerly.
+GRAPH_FLAG=""
+if [ "${CUDA_GRAPH:-1}" != "0" ]; then GRAPH_FLAG="--cuda_graph"; fi
+echo "world=$WORLD tp=$TP_DEGREE dp=$DP acc_steps=$ACC_STEPS cuda_graph=${CUDA_GRAPH:-1}"
 
 torchrun $DIST_ARGS train.py \
   --model $MODEL --tp $TP_DEGREE --use_zero_1 --sequence_parallel_enabled --rmsnorm_across_groups \
@@ -43,4 +47,5 @@ torchrun $DIST_ARGS train.py \
   --grad_accum_usteps $ACC_STEPS --lr $LR --weight_decay 0.1 --beta1 0.9 --beta2 0.95 \
   --warmup_steps $WARMUP_STEPS --max_steps $TOTAL_STEPS --logging_interval 1 \
   --checkpoint_freq $CKPT_FREQ --checkpoint_dir "$CKPT_DIR" --num_kept_checkpoint 3 --save_last_step \
+  $GRAPH_FLAG \
   --tag mamba2hybrid_8b "${@:3}"
