@@ -48,8 +48,11 @@ class Mamba2HybridMLP(nn.Module):
     def forward(self, hidden_states: torch.Tensor, cache_params=None) -> torch.Tensor:
         h = self.gate_up_proj(hidden_states)
         if self.gated:
-            gate, up = h.split(self.split_size, dim=-1)
-            h = self._act(gate) * up
+            if self.act_name in ("gelu", "silu", "swish", "relu"):
+                h = ops.glu(h, self.act_name)           # act(gate) * up in one kernel on the GPU path
+            else:
+                gate, up = h.split(self.split_size, dim=-1)
+                h = self._act(gate) * up
         else:
             h = self._act(h)
         return self.down_proj(h)

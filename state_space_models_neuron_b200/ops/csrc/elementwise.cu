@@ -907,6 +907,73 @@ extern "C" int ssm_add_rmsnorm_bwd(const void* res, const void* w, const void* d
   return (int)cudaGetLastError();
 }
 
+// -------------------------------------------------------------------------------------
+// gated linear unit of the MLP: h = [gate | up] (row stride ld, halves of S columns), out = act(gate) * up.
+// act: 0 GELU (erf), 1 SiLU.  Backward writes d(gate) | d(up) into dh with the same layout.
+// (the reference's gated variant is mamba2hybrid/mamba2hybrid_mlp.py:118-134 in ATen ops)
+// -------------------------------------------------------------------------------------
+namespace ssm {
+__device__ __forceinline__ float glu_act(float x, int act) {
+  return act == 0 ? 0.5f * x * (1.f + erff(x * 0.70710678118654752f)) : x / (1.f + __expf(-x));
+}
+__device__ __forceinline__ float glu_act_grad(float x, int act) {
+  if (act == 0) return 0.5f * (1.f + erff(x * 0.70710678118654752f)) + x * 0.3989422804014327f * __expf(-0.5f * x * x);
+  const float sg = 1.f / (1.f + __expf(-x));
+  return sg * (1.f + x * (1.f - sg));
+}
+__global__ void __launch_bounds__(256)
+glu_fwd_kernel(const __nv_bfloat16* __restrict__ h, long long ld, __nv_bfloat16* __restrict__ out, long long rows, int S, int act) {
+  const int vec = S / 8;
+  const long long total = rows * vec;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / vec;
+    const int c = (int)(i - r * vec) * 8;
+    float g[8], u[8];
+    load8(h + r * ld + c, g);
+    load8(h + r * ld + S + c, u);
+    #pragma unroll
+    for (int e = 0; e < 8; ++e) g[e] = glu_act(g[e], act) * u[e];
+    store8(out + r * S + c, g);
+  }
+}
+__global__ void __launch_bounds__(256)
+glu_bwd_kernel(const __nv_bfloat16* __restrict__ h, long long ld, const __nv_bfloat16* __restrict__ dout,
+               __nv_bfloat16* __restrict__ dh, long long rows, int S, int act) {
+  const int vec = S / 8;
+  const long long total = rows * vec;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / vec;
+    const int c = (int)(i - r * vec) * 8;
+    float g[8], u[8], d[8], dg[8], du[8];
+    load8(h + r * ld + c, g);
+    load8(h + r * ld + S + c, u);
+    load8(dout + r * S + c, d);
+    #pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      dg[e] = d[e] * u[e] * glu_act_grad(g[e], act);
+      du[e] = d[e] * glu_act(g[e], act);
+    }
+    store8(dh + r * 2 * S + c, dg);
+    store8(dh + r * 2 * S + S + c, du);
+  }
+}
+}  // namespace ssm
+extern "C" int ssm_glu_fwd(const void* h, long long ld, void* out, long long rows, int S, int act, cudaStream_t st) {
+  if (S % 8 || ld % 8 || rows < 1 || act < 0 || act > 1) return -SSM_ERR_BAD_ARG;
+  const long long total = rows * (S / 8);
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  glu_fwd_kernel<<<blocks, 256, 0, st>>>(BF(h), ld, BFM(out), rows, S, act);
+  return (int)cudaGetLastError();
+}
+extern "C" int ssm_glu_bwd(const void* h, long long ld, const void* dout, void* dh, long long rows, int S, int act,
+                           cudaStream_t st) {
+  if (S % 8 || ld % 8 || rows < 1 || act < 0 || act > 1) return -SSM_ERR_BAD_ARG;
+  const long long total = rows * (S / 8);
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  glu_bwd_kernel<<<blocks, 256, 0, st>>>(BF(h), ld, BF(dout), BFM(dh), rows, S, act);
+  return (int)cudaGetLastError();
+}
+
 extern "C" int ssm_gelu_fwd(const void* x, void* y, long long n, cudaStream_t st) {
   if (n % 8) return -SSM_ERR_BAD_ARG;
   const long long n8 = n / 8;

@@ -453,6 +453,37 @@ def gelu(x):
     return _Gelu.apply(x)
 
 
+class _Glu(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, h, act):
+        S = h.shape[-1] // 2
+        h2 = h.reshape(-1, 2 * S)
+        if h2.stride(1) != 1 or h2.stride(0) % 8 or h2.data_ptr() % 16:
+            h2 = h2.contiguous()
+        out = torch.empty(h2.shape[0], S, dtype=h.dtype, device=h.device)
+        _run("ssm_glu_fwd", _p(h2), _ll(h2.stride(0)), _p(out), _ll(h2.shape[0]), S, act, _st())
+        ctx.save_for_backward(h2)
+        ctx.act, ctx.shape = act, h.shape
+        return out.reshape(*h.shape[:-1], S)
+
+    @staticmethod
+    def backward(ctx, dout):
+        (h2,) = ctx.saved_tensors
+        S = h2.shape[1] // 2
+        d2 = dout.reshape(-1, S).contiguous()
+        dh = torch.empty(h2.shape[0], 2 * S, dtype=h2.dtype, device=h2.device)
+        _run("ssm_glu_bwd", _p(h2), _ll(h2.stride(0)), _p(d2), _p(dh), _ll(h2.shape[0]), S, ctx.act, _st())
+        return dh.reshape(ctx.shape), None
+
+
+def glu(h, act: str = "silu"):
+    """act(h[..., :S]) * h[..., S:] for h = [gate | up] in one kernel (forward and backward); act gelu or silu."""
+    _require_bf16(h)
+    if h.shape[-1] % 16 or act not in ("gelu", "silu", "swish"):
+        raise ValueError("glu kernel needs an even split into multiples of 8 columns and act in {gelu, silu}")
+    return _Glu.apply(h, 0 if act == "gelu" else 1)
+
+
 # ======================================================================================
 # embedding
 # ======================================================================================

@@ -184,6 +184,16 @@ def gelu(x):
     return F.gelu(x)
 
 
+def glu(h, act: str = "silu"):
+    """Gated linear unit on h = [gate | up]: act(gate) * up (act gelu or silu)."""
+    S = h.shape[-1] // 2
+    if _native(h) and h.dtype == torch.bfloat16 and h.shape[-1] % 16 == 0 and act in ("gelu", "silu", "swish"):
+        return _cuda().glu(h, act)
+    gate, up = h[..., :S], h[..., S:]
+    a = F.gelu(gate) if act == "gelu" else F.relu(gate) if act == "relu" else F.silu(gate)
+    return a * up
+
+
 # ---- embedding ----------------------------------------------------------------------------
 def embedding(ids, weight, vocab_start: int = 0):
     """Vocabulary-shard lookup: rows `weight[ids - vocab_start]`, zeros for ids outside the shard."""

@@ -472,3 +472,19 @@ def test_debug_bounds_build_reports_bad_index_without_faulting():
     assert native.debug_bounds(dbg) == {}                          # reading resets the record
     y_again, _ = step(dbg, C)                                      # the context is still usable
     assert torch.equal(y_again, y_ref)
+
+
+@pytest.mark.parametrize("act", ["silu", "gelu"])
+def test_glu_fwd_bwd(act):
+    from state_space_models_neuron_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(8)
+    h = torch.randn(3, 100, 2 * 264, device="cuda", generator=g).bfloat16().requires_grad_(True)
+    y = ops.glu(h, act)
+    gy = torch.randn(y.shape, device="cuda", generator=g).bfloat16()
+    y.backward(gy)
+    hr = h.detach().float().requires_grad_(True)
+    gate, up = hr[..., :264], hr[..., 264:]
+    yr = (torch.nn.functional.gelu(gate) if act == "gelu" else torch.nn.functional.silu(gate)) * up
+    yr.backward(gy.float())
+    _close(y, yr, atol=2e-2, rtol=2e-2, frac=1.0)
+    _close(h.grad, hr.grad, atol=3e-2, rtol=2e-2, frac=1.0)
