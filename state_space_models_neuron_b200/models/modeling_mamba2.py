@@ -174,7 +174,7 @@ class Mamba2Model(Mamba2PreTrainedModel):
         """One decode token through all blocks (mamba2/modeling_mamba2.py:337-350)."""
         if ps.get_tensor_model_parallel_size() > 1 and input_ids.is_cuda:
             from ..parallel import symm
-            symm.advance_step()      # fresh sequence numbers for this token's fused collectives
+            symm.advance_step(compact=True)      # fresh sequence numbers for this token's fused collectives
         hidden = self.embeddings(input_ids)
         residual = None
         for block in self.layers:

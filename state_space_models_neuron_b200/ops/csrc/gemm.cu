@@ -183,7 +183,7 @@ __device__ __forceinline__ bool get_work(const GemmParams& p, int unit, int it, 
 }
 
 // (first row of this CTA's 128 accumulator rows, first column of the tile).  Plain GEMMs walk the tiles column by
-// column.  The collective variants walk them block by block, a block being the rows of one source shard (all-gather)
+// column inside bands of 8 m-tiles.  The collective variants walk them block by block, a block being the rows of one source shard (all-gather)
 // or of one owner (reduce-scatter): the all-gather starts with the local shard, whose rows need no transfer, and
 // takes the remote shards in ring order behind it; the reduce-scatter starts with the next rank's rows, so that
 // every partial block is on its way as early as possible, and ends with this rank's own rows.  With whole tiles
@@ -201,8 +201,16 @@ __device__ __forceinline__ void tile_origin(const GemmParams& p, const GemmComm&
     tn = within / tpb;
     tm = block * tpb + (within - tn * tpb);
   } else {
-    tm = tile % p.tiles_m;
-    tn = tile / p.tiles_m;
+    // bands of RASTER_M m-tiles, column by column inside a band: the tiles of one wave then share a few A row blocks
+    // and a few B column blocks instead of all of A (tall outputs like the wgrad of in_proj re-read A from DRAM once
+    // per wave otherwise: ncu showed 7.6x the operand bytes)
+    constexpr int RASTER_M = 8;
+    const int band = tile / (RASTER_M * p.tiles_n);
+    const int within = tile - band * (RASTER_M * p.tiles_n);
+    const int first_m = band * RASTER_M;
+    const int rows_in_band = p.tiles_m - first_m < RASTER_M ? p.tiles_m - first_m : RASTER_M;
+    tn = within / rows_in_band;
+    tm = first_m + (within - tn * rows_in_band);
   }
   m0 = tm * TILE_M + cta_rank * GEMM_BM;
   n0 = tn * BN;
