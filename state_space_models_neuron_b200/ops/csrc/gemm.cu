@@ -429,11 +429,30 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         const int grid = (int)gridDim.x;
         uint32_t phase = 0;
         int committed = 0;                          // boxes (bulk groups) committed so far
-        int group_last[AG_MAX_GROUPS];              // value of `committed` after the last box of each row group
         bool pok = true;
-        // issue everything first: load a box, store it to every rank; the only waits are for a staging buffer to
-        // be readable again
+        // Column group g + 1 is issued before this CTA waits for its boxes of group g: the link always has work, but
+        // a group's stores get a head start of one group over the next one's, so the first columns of a shard land
+        // (and their flag goes out) after about 1 / ngroups of the transfer.  Issuing every group at once made all
+        // groups complete together, at the end.
+        auto report_group = [&](int g, int pending_after) {
+          // boxes committed after the group's last one may still be in flight
+          if (pending_after <= 0)      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+          else if (pending_after == 1) asm volatile("cp.async.bulk.wait_group 1;" ::: "memory");
+          else if (pending_after == 2) asm volatile("cp.async.bulk.wait_group 2;" ::: "memory");
+          else if (pending_after == 3) asm volatile("cp.async.bulk.wait_group 3;" ::: "memory");
+          else                         asm volatile("cp.async.bulk.wait_group 4;" ::: "memory");
+          fence_proxy_async_all();
+          __threadfence_system();
+          const int done = atomicAdd(cm.ag_counter + g, 1) + 1;
+          if (done == grid) {                       // this CTA completed the group: publish its flag on every rank
+            cm.ag_counter[g] = 0;
+            __threadfence_system();
+            for (int t = 0; t < cm.nranks; ++t)
+              st_release_sys_s32(reinterpret_cast<int*>(cm.flag_ptrs.p[t]) + cm.ag_flag_base + cm.me * AG_MAX_GROUPS + g, seqv);
+          }
+        };
         int dealt = 0;                              // boxes dealt so far over all CTAs (round-robin start of a group)
+        int prev_committed = 0;                     // value of `committed` after the previous group's last box
         for (int g = 0; g < ngroups && pok; ++g) {
           const int cols_g = min(cm.ag_group_kb, col_blocks - g * cm.ag_group_kb);
           const int boxes_g = cols_g * row_blocks;
@@ -458,29 +477,10 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             tma_store_commit();
             ++committed;
           }
-          group_last[g] = committed;
+          if (pok && g > 0) report_group(g - 1, committed - prev_committed);
+          prev_committed = committed;
         }
-        // then, group by group: once this CTA's boxes of the group have landed, report; the CTA that completes the
-        // count publishes the group's flag on every rank
-        for (int g = 0; g < ngroups && pok; ++g) {
-          const int after = committed - group_last[g];      // boxes committed after the group's last one may pend
-          switch (after) {
-            case 0: asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); break;
-            case 1: asm volatile("cp.async.bulk.wait_group 1;" ::: "memory"); break;
-            case 2: asm volatile("cp.async.bulk.wait_group 2;" ::: "memory"); break;
-            case 3: asm volatile("cp.async.bulk.wait_group 3;" ::: "memory"); break;
-            default: asm volatile("cp.async.bulk.wait_group 4;" ::: "memory"); break;
-          }
-          fence_proxy_async_all();
-          __threadfence_system();
-          const int done = atomicAdd(cm.ag_counter + g, 1) + 1;
-          if (done == grid) {
-            cm.ag_counter[g] = 0;
-            __threadfence_system();
-            for (int t = 0; t < cm.nranks; ++t)
-              st_release_sys_s32(reinterpret_cast<int*>(cm.flag_ptrs.p[t]) + cm.ag_flag_base + cm.me * AG_MAX_GROUPS + g, seqv);
-          }
-        }
+        if (pok && ngroups > 0) report_group(ngroups - 1, 0);
         tma_store_wait_all();
         trace_mark(p, 11);
       }
@@ -961,7 +961,7 @@ static int epilogue_direct() {
   return v;
 }
 // Scheduling options: environment defaults (SSM_GEMM_PAIR=0|1|2: never / by cost / whenever possible use CTA pairs;
-// SSM_GEMM_SPLIT=0: never cut tail tiles along K; SSM_GEMM_FORCE_BN=128|192|256: tile width), overridden at run time
+// SSM_GEMM_SPLIT=0|1|2: never / where it pays / wherever possible cut tail tiles along K; SSM_GEMM_FORCE_BN=128|192|256: tile width), overridden at run time
 // by ssm_gemm_set_options (tests and benchmarks).
 static int g_opt_pair = -1, g_opt_split = -1, g_opt_bn = -1;
 static int gemm_pair_mode() {
@@ -970,7 +970,7 @@ static int gemm_pair_mode() {
 }
 static int gemm_pairs_enabled() { return gemm_pair_mode() != 0; }
 static int gemm_split_enabled() {
-  if (g_opt_split < 0) g_opt_split = env_int("SSM_GEMM_SPLIT", 1) ? 1 : 0;
+  if (g_opt_split < 0) { g_opt_split = env_int("SSM_GEMM_SPLIT", 1); if (g_opt_split < 0 || g_opt_split > 2) g_opt_split = 1; }
   return g_opt_split;
 }
 static int gemm_forced_bn() {
@@ -1003,13 +1003,39 @@ struct TileChoice { int bn; int pair; };
 // 128 x 256 single-CTA tile are measured values (a CTA's main loop is bound by the operand bytes it pulls per
 // k-block: 48 KB for 128x256, 32 KB for a 128x128 tile or for its half of a 256x256 pair tile, 24 KB for its half
 // of a 256x128 pair tile).  SSM_GEMM_FORCE_BN=128|192|256 and SSM_GEMM_PAIR=0|1|2 (2 = always) override.
-static TileChoice pick_tile(int M, int N, int K, int b_mn, int allow_pair) {
+// K slices for the `rem` tiles left after the full waves (or for all tiles when there are fewer tiles than units).
+// Cutting a tile into s slices saves (1 - 1/s) of its main loop but adds the exchange of partial sums: every slice
+// writes its fp32 block to scratch and the last arriver reads the others back, a latency-bound pass measured at
+// 8-10 us for a 256 x 256 pair tile (2320 x 4096 x 2048 fp32 out: 59.5 us with the split, 51.7 us without), half of
+// that for a 128-row tile.  Accumulate mode adds its slices into C directly and has no read-back.  Costs are in units
+// of one single-CTA 128 x 256 k-block (about 0.42 us); the split is taken only where it pays.
+static int tail_split(long long rem, int units, int kblocks, int mode, int pair, double cost_kb, double* exchange) {
+  if (exchange) *exchange = 0.0;
+  if (rem <= 0) return 1;
+  int split = (int)(units / rem);
+  const int cap = mode == 2 ? MAX_SPLIT : 4;
+  if (split > cap) split = cap;
+  if (split > kblocks / 4) split = kblocks / 4;
+  if (split <= 1) return 1;
+  const double exch = mode == 2 ? 4.0 : (pair ? 22.0 : 12.0);
+  if (gemm_split_enabled() != 2 && (1.0 - 1.0 / split) * kblocks * cost_kb <= exch) return 1;   // 2: split wherever possible
+  if (exchange) *exchange = exch;
+  return split;
+}
+
+static double tile_cost_kb(int bn, int pair) {
+  // cost of one tile per k-block, relative to the single-CTA 128 x 256 tile
+  if (pair) return bn == 256 ? 0.68 : 0.52;
+  return bn == 256 ? 1.00 : 0.80;
+}
+
+static TileChoice pick_tile(int M, int N, int K, int b_mn, int allow_pair, int mode = 0) {
   const int forced_bn = gemm_forced_bn(), forced_pair = gemm_pair_mode();
   const int sms = g_num_sms > 0 ? g_num_sms : 148;
   const int kblocks = (K + GEMM_BK - 1) / GEMM_BK;
   struct Cand { int bn, pair; double cost; };
-  // cost of one tile per k-block, relative
-  const Cand cands[5] = {{256, 0, 1.00}, {192, 0, 0.80}, {128, 0, 0.80}, {256, 1, 0.68}, {128, 1, 0.52}};
+  const Cand cands[5] = {{256, 0, tile_cost_kb(256, 0)}, {192, 0, tile_cost_kb(192, 0)}, {128, 0, tile_cost_kb(128, 0)},
+                         {256, 1, tile_cost_kb(256, 1)}, {128, 1, tile_cost_kb(128, 1)}};
   TileChoice best = {256, 0};
   double best_t = 1e30;
   for (const Cand& c : cands) {
@@ -1021,15 +1047,14 @@ static TileChoice pick_tile(int M, int N, int K, int b_mn, int allow_pair) {
     const int units = c.pair ? sms / 2 : sms;
     const long long tiles = (long long)((M + tile_m - 1) / tile_m) * ((N + c.bn - 1) / c.bn);
     const long long full = tiles / units, rem = tiles % units;
-    double waves = (double)full;
-    if (rem) {
-      int split = (int)(units / rem);
-      if (split > 4) split = 4;
-      if (split > kblocks / 4) split = kblocks / 4 > 0 ? kblocks / 4 : 1;
-      waves += 1.0 / split + (split > 1 ? 0.08 : 0.0);       // exchange of partial sums
+    double waves = (double)full, exchange = 0.0;
+    if (tiles < units) {
+      waves = 1.0 / tail_split(tiles, units, kblocks, mode, c.pair, c.cost, &exchange);
+    } else if (rem) {
+      waves += 1.0 / tail_split(rem, units, kblocks, mode, c.pair, c.cost, &exchange);
     }
     // per-tile fixed cost (pipeline fill, epilogue tail) in k-block units
-    const double t = waves * (kblocks * c.cost + 6.0);
+    const double t = waves * (kblocks * c.cost + 6.0) + exchange;
     if (t < best_t) { best_t = t; best = {c.bn, c.pair}; }
   }
   (void)b_mn;
@@ -1084,11 +1109,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
   if (gemm_split_enabled() && (p.rem > 0 || tiles < max_units)) {
     // fewer tiles than units: everything is tail (full_tiles = 0) and the idle units take K slices
     if (tiles < max_units) { units = max_units; p.full_tiles = 0; p.rem = tiles; }
-    int split = units / p.rem;
-    const int cap = p.mode == 2 ? MAX_SPLIT : 4;
-    if (split > cap) split = cap;
-    if (split > kblocks / 4) split = kblocks / 4;
-    if (split < 1) split = 1;
+    const int split = tail_split(p.rem, units, kblocks, p.mode, PAIR ? 1 : 0, tile_cost_kb(BN, PAIR ? 1 : 0), nullptr);
     p.split = split;
     if (split > 1 && p.mode != 2) {
       Scratch s;
@@ -1191,7 +1212,7 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
   int allow_pair = gemm_pairs_enabled();
   if (comm != nullptr && comm->ag && comm->rows_per_shard % 256) allow_pair = 0;
   if (comm != nullptr && comm->rs && comm->rows_per_owner % 256) allow_pair = 0;
-  const TileChoice tcw = pick_tile(M, N, K, b_mn, allow_pair);
+  const TileChoice tcw = pick_tile(M, N, K, b_mn, allow_pair, mode);
   const int BN = tcw.bn;
   const bool pair = tcw.pair != 0;
   if (tiles_n_out) *tiles_n_out = (N + BN - 1) / BN;
@@ -1339,7 +1360,7 @@ extern "C" int ssm_gemm_bf16_fused(const void* A, const void* B, void* C, int M,
 // or 128 / 192 / 256.  A negative value leaves that option as it is.
 extern "C" int ssm_gemm_set_options(int pair, int split, int bn) {
   if (pair >= 0) ssm::g_opt_pair = pair;
-  if (split >= 0) ssm::g_opt_split = split ? 1 : 0;
+  if (split >= 0) ssm::g_opt_split = split > 2 ? 1 : split;
   if (bn >= 0) ssm::g_opt_bn = bn;
   return 0;
 }

@@ -63,10 +63,28 @@ def collective_tile_origin(tile: int, tiles_n: int, tiles_per_block: int, nranks
     return block * tiles_per_block + tm_in, tn
 
 
-def gemm_schedule(tiles: int, max_units: int, kblocks: int, accumulate: bool = False, split_enabled: bool = True):
+def gemm_tail_split(rem: int, units: int, kblocks: int, accumulate: bool = False, pair: bool = False,
+                    cost_kb: float = 1.0, always: bool = False) -> int:
+    """Host copy of `tail_split` in ops/csrc/gemm.cu: K slices per tail tile.  The split is taken only where the
+    saved share of the main loop exceeds the exchange of partial sums (22 k-block units for a pair tile, 12 for a
+    single-CTA tile, 4 in accumulate mode) unless `always`."""
+    if rem <= 0:
+        return 1
+    split = min(units // rem, 8 if accumulate else 4, kblocks // 4)
+    if split <= 1:
+        return 1
+    exch = 4.0 if accumulate else (22.0 if pair else 12.0)
+    if not always and (1.0 - 1.0 / split) * kblocks * cost_kb <= exch:
+        return 1
+    return split
+
+
+def gemm_schedule(tiles: int, max_units: int, kblocks: int, accumulate: bool = False, split_enabled: bool = True,
+                  pair: bool = False, cost_kb: float = 1.0, always_split: bool = True):
     """Host copy of the GEMM's work distribution (ops/csrc/gemm.cu `launch_gemm` + `get_work`): returns
     (units, [(unit, tile, kb0, kb1, slice, nslices)]).  Whole tiles go round-robin over the units for as many full
-    waves as there are; the tiles of the last partial wave are cut into K slices, one per otherwise idle unit."""
+    waves as there are; the tiles of the last partial wave are cut into K slices, one per otherwise idle unit
+    (`always_split=False` applies the kernel's pay-off rule, see `gemm_tail_split`)."""
     units = min(tiles, max_units)
     full = (tiles // units) * units
     rem = tiles - full
@@ -74,9 +92,7 @@ def gemm_schedule(tiles: int, max_units: int, kblocks: int, accumulate: bool = F
     if split_enabled and (rem > 0 or tiles < max_units):
         if tiles < max_units:
             units, full, rem = max_units, 0, tiles
-        split = units // rem
-        split = min(split, 8 if accumulate else 4, kblocks // 4)
-        split = max(split, 1)
+        split = gemm_tail_split(rem, units, kblocks, accumulate, pair, cost_kb, always_split)
         if tiles < max_units:
             units = rem * split
     work = []

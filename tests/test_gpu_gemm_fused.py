@@ -69,9 +69,10 @@ def test_gemm_schedules(M, N, K, layout):
     assert abs(ss.item() - want) <= 2e-3 * want
 
 
-@pytest.mark.parametrize("pair,split,bn", [(0, 1, 0), (0, 1, 128), (0, 1, 192), (0, 0, 256), (2, 1, 256), (2, 1, 128), (2, 0, 0)])
+@pytest.mark.parametrize("pair,split,bn", [(0, 1, 0), (0, 2, 128), (0, 2, 192), (0, 0, 256), (2, 2, 256), (2, 2, 128), (2, 0, 0), (1, 1, 0)])
 def test_gemm_forced_tilings(pair, split, bn):
-    """Every tile family with and without the K-split tail, on shapes whose last wave is partial."""
+    """Every tile family without the K-split tail, with it wherever possible (2) and where the cost rule takes it (1),
+    on shapes whose last wave is partial."""
     from state_space_models_neuron_b200.ops import cuda_ops, native
     lib = native.lib()
     lib.ssm_gemm_set_options(pair, split, bn)
