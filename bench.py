@@ -103,7 +103,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "baseline"])
     ap.add_argument("--small", action="store_true", help="tiny model for profiling captures (not a benchmark value)")
     ap.add_argument("--layers", type=int, default=None, help="override layer count (profiling only)")
-    ap.add_argument("--fused_comm", default="on", choices=["on", "off"])
+    ap.add_argument("--fused_comm", default="auto", choices=["auto", "on", "off"],
+                    help="auto: time the whole step with each of the two GEMM + collective kernels fused or as NCCL + "
+                         "GEMM (four combinations, before the warm-up) and run the fastest; on: both fused; off: NCCL")
     ap.add_argument("--no_e2e", action="store_true")
     ap.add_argument("--graph", default="on", choices=["on", "off"],
                     help="replay the whole training step as one CUDA graph (off = eager launches)")
@@ -143,7 +145,7 @@ def main():
         k = args.shard_of
         m.update(num_heads=m["num_heads"] // k, n_groups=max(1, m["n_groups"] // k), vocab_size=m["vocab_size"] // k,
                  expand=2.0 / k, name=m["name"] + f" (1/{k} shard, analysis)")
-    fused = args.fused_comm == "on" and args.impl == "ours"
+    fused = args.fused_comm in ("on", "auto") and args.impl == "ours"
     if args.impl == "baseline":
         from baseline import nccl_cublas
         # one GPU holds all 126 GB of weights, gradients and optimizer state of the 7B model: the saved scan
@@ -202,19 +204,42 @@ def main():
                 pass
             opt.zero_grad()
     step, gstep, graph_note = eager_step, None, "off"
-    if args.graph == "on" and args.impl == "ours":
+    fused_choice = None
+
+    def build_graphed():
         from state_space_models_neuron_b200.parallel.graph import GraphedTrainStep
         try:
-            gstep = GraphedTrainStep(model, opt, {"input_ids": dev[0], "labels": dev[0]})
+            gs = GraphedTrainStep(model, opt, {"input_ids": dev[0], "labels": dev[0]})
         except Exception as e:                       # fall back to eager launches, on every rank or on none
             print(f"[rank {rank}] CUDA graph capture failed, running eager: {e!r}", file=sys.stderr, flush=True)
-            gstep = None
-        ok = torch.tensor([1 if gstep is not None else 0], device="cuda")
+            gs = None
+        ok = torch.tensor([1 if gs is not None else 0], device="cuda")
         if world > 1:
             dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-        if int(ok.item()) == 0:
-            gstep = None
+        return gs if int(ok.item()) else None
+
+    if args.graph == "on" and args.impl == "ours":
+        if fused and tp > 1 and args.fused_comm == "auto":
+            # the whole graphed step is timed under each on/off combination of the two GEMM + collective kernels
+            # (max over ranks, so every rank decides alike); the fastest runs the warm-up and the timed steps
+            from state_space_models_neuron_b200.parallel import fused_tune
+            graphs = {}
+
+            def build_combo():
+                gs = build_graphed()
+                if gs is None:
+                    return None
+                run = lambda: gs({"input_ids": dev[0], "labels": dev[0]})
+                graphs[id(run)] = gs
+                return run
+
+            rep = fused_tune.pick_fastest(build_combo, torch.device("cuda", local), reps=3,
+                                          release=lambda run: graphs.pop(id(run), None))
+            gstep = graphs.pop(id(rep["step"])) if rep["step"] is not None else None
+            fused_choice = {"chosen": rep["chosen"], "ms_per_step": rep["ms"]}
         else:
+            gstep = build_graphed()
+        if gstep is not None:
             graph_note = "whole step (fwd+bwd+optimizer+collectives) captured once, replayed per step"
 
             def step(ids):
@@ -295,12 +320,19 @@ def main():
             out["fused_kernel_launches"] = dict(fused_ops.CALLS)
             if fused_fallback:
                 out["fused_comm_fallback"] = fused_fallback
+            if fused_choice:
+                out["fused_comm_choice"] = fused_choice
         if e2e is not None:
             out["e2e"] = e2e
         if is_headline:
             out["baselines"] = {"pytorch_cublas_nccl_tokens_per_s": base_pt, "own_kernels_nccl_tokens_per_s": base_nccl,
                                 "vs_own_kernels_nccl": (value / base_nccl) if base_nccl else None,
                                 "source": "baseline/measured.json"}
+            nccl_ms = (fused_choice or {}).get("ms_per_step", {}).get("ag_gemm=nccl,gemm_rs=nccl")
+            if nccl_ms:
+                # the same step with both collectives as NCCL + plain GEMM, timed in this run by the tuner (3 replays)
+                out["baselines"]["own_kernels_nccl_same_run_ms_per_step"] = nccl_ms
+                out["baselines"]["vs_own_kernels_nccl_same_run"] = nccl_ms / (ms / args.steps)
         print(json.dumps(out), flush=True)
     # Tear down without destroying NCCL communicators that a live CUDA graph still references (that can block
     # forever): drop the graph, drain the device, meet the other ranks, run the interpreter's registered exit

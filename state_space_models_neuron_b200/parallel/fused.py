@@ -8,6 +8,11 @@ _SMALL_AR = [os.environ.get("SSM_B200_SMALL_AR", "1") != "0"]
 
 
 _ZERO1 = [os.environ.get("SSM_B200_FUSED_ZERO1", "1") != "0"]
+# the two GEMM + collective kernels can be switched off one by one (SSM_B200_FUSED_AG=0 / SSM_B200_FUSED_RS=0 or
+# `set_kernel`): the op then runs as the NCCL collective plus the plain GEMM kernel inside the same autograd
+# functions, so forward and backward uses switch together and the other fused kernels stay on
+_KERNELS = {"ag_gemm": os.environ.get("SSM_B200_FUSED_AG", "1") != "0",
+            "gemm_rs": os.environ.get("SSM_B200_FUSED_RS", "1") != "0"}
 
 
 def is_enabled() -> bool:
@@ -20,6 +25,20 @@ def zero1_enabled() -> bool:
 
 def set_enabled(flag: bool) -> None:
     _ENABLED[0] = bool(flag)
+
+
+def set_kernel(name: str, flag: bool) -> None:
+    if name not in _KERNELS:
+        raise KeyError(f"unknown fused kernel {name!r}; known: {sorted(_KERNELS)}")
+    _KERNELS[name] = bool(flag)
+
+
+def kernel_enabled(name: str) -> bool:
+    return bool(_KERNELS[name])
+
+
+def kernels() -> dict:
+    return dict(_KERNELS)
 
 
 def register(impl) -> None:

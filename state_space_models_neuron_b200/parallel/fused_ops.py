@@ -21,7 +21,9 @@ from __future__ import annotations
 import ctypes
 
 import torch
+import torch.distributed as dist
 
+from . import fused
 from . import state as ps
 from . import symm
 from ..ops import cuda_ops
@@ -65,6 +67,16 @@ def _ag_gemm(x_shard2, w, b_mn, bias, ws, act=0, ce=None):
     T = ws.nranks
     M = T * Ls
     N = w.shape[1] if b_mn else w.shape[0]
+    if not fused.kernel_enabled("ag_gemm"):
+        # library collective + the plain GEMM kernel (same results, same autograd functions around it)
+        gathered = torch.empty(M, K, dtype=x_shard2.dtype, device=x_shard2.device)
+        dist.all_gather_into_tensor(gathered, x_shard2.contiguous(), group=ws.group)
+        CALLS["ag_gemm_library"] = CALLS.get("ag_gemm_library", 0) + 1
+        if ce is not None:
+            labels, vocab_start = ce
+            y, stats = cuda_ops.gemm_ce(gathered, w, labels, vocab_start)
+            return gathered, y, stats
+        return gathered, cuda_ops.gemm(gathered, w, b_mn=b_mn, bias=bias, gelu=bool(act))
     CALLS["ag_gemm"] += 1
     seq, par = ws.next_seq(symm.KIND_AG)
     off = ws.gather_offset(par)
@@ -90,6 +102,14 @@ def _gemm_rs(a2, w, b_mn, ws):
     T = ws.nranks
     Ls = M // T
     N = w.shape[1] if b_mn else w.shape[0]
+    if not fused.kernel_enabled("gemm_rs"):
+        full = cuda_ops.gemm(a2, w, b_mn=b_mn)
+        if not full.is_contiguous():
+            full = full.contiguous()
+        out = torch.empty(Ls, N, dtype=full.dtype, device=full.device)
+        dist.reduce_scatter_tensor(out, full, group=ws.group)
+        CALLS["gemm_rs_library"] = CALLS.get("gemm_rs_library", 0) + 1
+        return out
     CALLS["gemm_rs"] += 1
     seq, par = ws.next_seq(symm.KIND_RS)
     off = ws.land_offset(par)
@@ -358,5 +378,4 @@ class _Impl:
 
 
 def install() -> None:
-    from . import fused
     fused.register(_Impl)

@@ -218,3 +218,46 @@ def test_symmetric_workspace_regions_do_not_overlap():
         assert end <= total
         # flag words of the four kinds x two parities x (eight sources x four row groups) fit in the flag page
         assert ws.flag_base(symm.KIND_EMB, 1) + symm.FLAG_SLOTS == symm.N_FLAGS <= ws.flags_bytes // 4
+
+
+def test_fused_tuner_picks_the_fastest_combination_and_leaves_it_switched_on(monkeypatch):
+    """`fused_tune.pick_fastest` with scripted step times: chooses the minimum, frees every candidate before the
+    next is built, rebuilds the winner, and leaves the two kernel switches on the choice."""
+    from state_space_models_neuron_b200.parallel import fused, fused_tune
+    script = {(True, True): 50.0, (False, True): 41.0, (True, False): 47.0, (False, False): 43.0}
+    built, released, alive = [], [], [0]
+
+    def build():
+        key = (fused.kernel_enabled("ag_gemm"), fused.kernel_enabled("gemm_rs"))
+        built.append(key)
+        alive[0] += 1
+        assert alive[0] == 1, "two captured steps alive at once"
+        step = lambda: None
+        step.key = key
+        return step
+
+    def release(step):
+        released.append(step.key)
+        alive[0] -= 1
+
+    monkeypatch.setattr(fused_tune, "time_steps", lambda run, reps, device: script[run.key])
+    before = fused.kernels()
+    try:
+        rep = fused_tune.pick_fastest(build, "cpu", reps=2, release=release)
+        assert rep["chosen"] == "ag_gemm=nccl,gemm_rs=fused"
+        assert rep["step"].key == (False, True)
+        assert built == list(fused_tune.COMBOS) + [(False, True)] and released == list(fused_tune.COMBOS)
+        assert fused.kernels() == {"ag_gemm": False, "gemm_rs": True}
+        assert rep["ms"]["ag_gemm=fused,gemm_rs=fused"] == 50.0
+        # a combination that cannot be built is skipped
+        alive[0] = 0
+        calls = [0]
+
+        def build_some():
+            calls[0] += 1
+            return None if calls[0] == 1 else build()
+        rep = fused_tune.pick_fastest(build_some, "cpu", release=release)
+        assert rep["ms"]["ag_gemm=fused,gemm_rs=fused"] is None and rep["chosen"] == "ag_gemm=nccl,gemm_rs=fused"
+    finally:
+        for k, v in before.items():
+            fused.set_kernel(k, v)
