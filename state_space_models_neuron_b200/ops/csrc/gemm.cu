@@ -122,6 +122,11 @@ struct RsMaps { CUtensorMap m[MAX_RANKS]; };
 __device__ __forceinline__ void st_release_sys_s32(int* p, int v) {
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+// after ONE system-scope fence, flags for several ranks go out back to back; a loop of release stores pays one NVLink
+// round trip per destination in series
+__device__ __forceinline__ void st_relaxed_sys_s32(int* p, int v) {
+  asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ int ld_acquire_sys_s32(const int* p) {
   int v;
   asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -145,8 +150,9 @@ __device__ __forceinline__ bool wait_flag(const int* flag, int seq, int* status)
   if (status != nullptr) atomicCAS(status, 0, SSM_ERR_TIMEOUT_FLAG);
   return false;
 }
+constexpr int GEMM_TRACE_SLOTS = 24;      // int64 time stamps per CTA in the trace buffer (ssm_gemm_set_trace)
 __device__ __forceinline__ void trace_mark(const GemmParams& p, int slot) {
-  if (p.trace != nullptr) p.trace[(size_t)blockIdx.x * 16 + slot] = global_timer_ns();
+  if (p.trace != nullptr) p.trace[(size_t)blockIdx.x * GEMM_TRACE_SLOTS + slot] = global_timer_ns();
 }
 
 template <int BN, int STAGES, bool PAIR>
@@ -430,29 +436,15 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         uint32_t phase = 0;
         int committed = 0;                          // boxes (bulk groups) committed so far
         bool pok = true;
-        // Column group g + 1 is issued before this CTA waits for its boxes of group g: the link always has work, but
-        // a group's stores get a head start of one group over the next one's, so the first columns of a shard land
-        // (and their flag goes out) after about 1 / ngroups of the transfer.  Issuing every group at once made all
-        // groups complete together, at the end.
-        auto report_group = [&](int g, int pending_after) {
-          // boxes committed after the group's last one may still be in flight
-          if (pending_after <= 0)      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-          else if (pending_after == 1) asm volatile("cp.async.bulk.wait_group 1;" ::: "memory");
-          else if (pending_after == 2) asm volatile("cp.async.bulk.wait_group 2;" ::: "memory");
-          else if (pending_after == 3) asm volatile("cp.async.bulk.wait_group 3;" ::: "memory");
-          else                         asm volatile("cp.async.bulk.wait_group 4;" ::: "memory");
-          fence_proxy_async_all();
-          __threadfence_system();
-          const int done = atomicAdd(cm.ag_counter + g, 1) + 1;
-          if (done == grid) {                       // this CTA completed the group: publish its flag on every rank
-            cm.ag_counter[g] = 0;
-            __threadfence_system();
-            for (int t = 0; t < cm.nranks; ++t)
-              st_release_sys_s32(reinterpret_cast<int*>(cm.flag_ptrs.p[t]) + cm.ag_flag_base + cm.me * AG_MAX_GROUPS + g, seqv);
-          }
-        };
+        // A remote bulk store takes about 10 us until `wait_group` sees it complete (measured at 4 ranks), far longer
+        // than loading a box (about 1 us), so what counts is how many boxes a CTA has in flight.  The two epilogue
+        // staging buffers are cut into as many slots as boxes fit (2 of 128 rows, 4 of 64, 8 of 32): the 3-4 boxes a
+        // CTA typically owns are all issued within a few microseconds, and only then does the CTA wait, group by
+        // group, and report.  (Waiting for group g before issuing group g + 2 was tried: it serialised the store
+        // latency, 10 us per group.)
+        const int nslots = (2 * EPI_BUF_BYTES) / (int)box_bytes;
+        int group_last[AG_MAX_GROUPS];              // value of `committed` after the last box of each column group
         int dealt = 0;                              // boxes dealt so far over all CTAs (round-robin start of a group)
-        int prev_committed = 0;                     // value of `committed` after the previous group's last box
         for (int g = 0; g < ngroups && pok; ++g) {
           const int cols_g = min(cm.ag_group_kb, col_blocks - g * cm.ag_group_kb);
           const int boxes_g = cols_g * row_blocks;
@@ -461,12 +453,17 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           for (int b = start; b < boxes_g; b += grid) {
             const int row = (b / cols_g) * cm.ag_push_rows;
             const int col = (g * cm.ag_group_kb + b % cols_g) * 64;
-            uint8_t* buf = epi_buf + (committed & 1) * EPI_BUF_BYTES;
-            asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");     // the stores that last read this buffer
+            uint8_t* buf = epi_buf + (committed % nslots) * box_bytes;
+            if (committed >= nslots) {              // the stores that last read this slot: nslots - 1 newer groups may pend
+              if (nslots >= 8)      asm volatile("cp.async.bulk.wait_group.read 7;" ::: "memory");
+              else if (nslots >= 4) asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory");
+              else                  asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            }
             mbar_expect_tx(push_bar, box_bytes);
             tma_load_2d(buf, &tmap_push, col, row, push_bar);
             if (!mbar_wait(push_bar, phase, p.status)) { pok = false; break; }
             phase ^= 1;
+            if (committed == 0) trace_mark(p, 16);
             #pragma unroll 1
             for (int k = 1; k <= cm.nranks; ++k) {
               // peers first, the local copy last; rank me - 1 consumes this shard earliest (right after its own)
@@ -477,10 +474,30 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             tma_store_commit();
             ++committed;
           }
-          if (pok && g > 0) report_group(g - 1, committed - prev_committed);
-          prev_committed = committed;
+          group_last[g] = committed;
         }
-        if (pok && ngroups > 0) report_group(ngroups - 1, 0);
+        trace_mark(p, 17);
+        // then, group by group: once this CTA's boxes of the group have landed, report; the CTA that completes the
+        // count publishes the group's flag on every rank
+        for (int g = 0; g < ngroups && pok; ++g) {
+          const int after = committed - group_last[g];      // boxes committed after the group's last one may pend
+          if (after <= 0)      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+          else if (after == 1) asm volatile("cp.async.bulk.wait_group 1;" ::: "memory");
+          else if (after == 2) asm volatile("cp.async.bulk.wait_group 2;" ::: "memory");
+          else if (after == 3) asm volatile("cp.async.bulk.wait_group 3;" ::: "memory");
+          else                 asm volatile("cp.async.bulk.wait_group 4;" ::: "memory");
+          fence_proxy_async_all();
+          __threadfence_system();
+          if (g == 0) trace_mark(p, 18);
+          const int done = atomicAdd(cm.ag_counter + g, 1) + 1;
+          if (done == grid) {                       // this CTA completed the group: publish its flag on every rank
+            if (g == 0) trace_mark(p, 20);
+            cm.ag_counter[g] = 0;
+            __threadfence_system();
+            for (int t = 0; t < cm.nranks; ++t)
+              st_relaxed_sys_s32(reinterpret_cast<int*>(cm.flag_ptrs.p[t]) + cm.ag_flag_base + cm.me * AG_MAX_GROUPS + g, seqv);
+          }
+        }
         tma_store_wait_all();
         trace_mark(p, 11);
       }
@@ -510,7 +527,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         if (done == per_owner) {
           cm.rs_counters[owner_] = 0;
           __threadfence_system();
-          st_release_sys_s32(reinterpret_cast<int*>(cm.flag_ptrs.p[owner_]) + cm.rs_flag_base + cm.me, seqv);
+          st_relaxed_sys_s32(reinterpret_cast<int*>(cm.flag_ptrs.p[owner_]) + cm.rs_flag_base + cm.me, seqv);
         }
       }
     };

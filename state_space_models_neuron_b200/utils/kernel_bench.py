@@ -25,6 +25,9 @@ import torch
 from ..ops import cuda_ops
 
 
+TRACE_SLOTS = 24          # int64 time stamps per CTA written by the GEMM kernel (GEMM_TRACE_SLOTS in ops/csrc/gemm.cu)
+
+
 def _peaks():
     here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     for base in (os.getcwd(), here):
@@ -83,12 +86,12 @@ def trace_gemm(a):
     for _ in range(3):
         cuda_ops.gemm(A, B, out_dtype=odt)
     torch.cuda.synchronize()
-    tr = torch.zeros(148 * 16, dtype=torch.int64, device="cuda")
+    tr = torch.zeros(148 * TRACE_SLOTS, dtype=torch.int64, device="cuda")
     lib.ssm_gemm_set_trace(ctypes.c_void_p(tr.data_ptr()))
     cuda_ops.gemm(A, B, out_dtype=odt)
     torch.cuda.synchronize()
     lib.ssm_gemm_set_trace(ctypes.c_void_p(0))
-    t = tr.view(148, 16).cpu().double()
+    t = tr.view(148, TRACE_SLOTS).cpu().double()
     t0 = t[:, 0][t[:, 0] > 0].min()
     names = [(0, "CTA set-up done"), (8, "first TMA load issued"), (1, "first stage landed"),
              (2, "first tile: MMAs issued"), (4, "first tile: accumulator complete"), (5, "first tile: epilogue done"),
@@ -273,14 +276,15 @@ def bench_fused(a):
             stepped(fused_fn)()
         torch.cuda.synchronize()
         dist.barrier()
-        tr = torch.zeros(148 * 16, dtype=torch.int64, device="cuda")
+        tr = torch.zeros(148 * TRACE_SLOTS, dtype=torch.int64, device="cuda")
         lib.ssm_gemm_set_trace(ctypes.c_void_p(tr.data_ptr()))
         stepped(fused_fn)()
         torch.cuda.synchronize()
         lib.ssm_gemm_set_trace(ctypes.c_void_p(0))
-        t = tr.view(148, 16).cpu().double()
+        t = tr.view(148, TRACE_SLOTS).cpu().double()
         t0 = t[:, 0][t[:, 0] > 0].min()
-        names = [(0, "set-up done"), (11, "push finished"), (12, "first remote group arrived"), (1, "first stage landed"),
+        names = [(0, "set-up done"), (16, "push: first box in shared memory"), (17, "push: all boxes issued"),
+                 (18, "push: own boxes of group 0 complete"), (20, "push: flag of group 0 published"), (11, "push finished"), (12, "first remote group arrived"), (1, "first stage landed"),
                  (4, "first accumulator complete"), (5, "first epilogue done"), (6, "last accumulator complete"),
                  (7, "last epilogue done"), (9, "producer finished"), (14, "tiles stored, flags published"),
                  (13, "tail: all sources seen"), (10, "CTA done")]
@@ -291,6 +295,11 @@ def bench_fused(a):
             if len(col):
                 out["events_us"][name] = [round(float((col.min() - t0) / 1e3), 1), round(float((col.median() - t0) / 1e3), 1),
                                           round(float((col.max() - t0) / 1e3), 1)]
+        if a.trace_dump and dist.get_rank() == 0:
+            # raw per-CTA records of rank 0, microseconds from the first CTA's start (0 = event not reached)
+            rel = torch.where(t > 0, (t - t0) / 1e3, torch.zeros_like(t))
+            with open(a.trace_dump, "w") as f:
+                json.dump({"slots": {str(k): v for k, v in names}, "cta_us": [[round(float(x), 1) for x in row] for row in rel]}, f)
         for r in range(T):
             if r == dist.get_rank():
                 print(json.dumps(out), flush=True)
@@ -330,6 +339,7 @@ def main(argv=None):
     ap.add_argument("--backward", action="store_true")
     ap.add_argument("--trace", action="store_true", help="gemm: print the in-kernel pipeline timeline instead of timing")
     ap.add_argument("--fp32_out", action="store_true", help="gemm --trace: fp32 output (gradient epilogue)")
+    ap.add_argument("--trace_dump", default="", help="ag_gemm / gemm_rs --trace: also write rank 0's per-CTA records to this JSON file")
     ap.add_argument("--iters", type=int, default=10)
     a = ap.parse_args(argv)
     if a.kernel in ("ag_gemm", "gemm_rs"):
