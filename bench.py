@@ -233,10 +233,35 @@ def main():
                 graphs[id(run)] = gs
                 return run
 
-            rep = fused_tune.pick_fastest(build_combo, torch.device("cuda", local), reps=3,
-                                          release=lambda run: graphs.pop(id(run), None))
-            gstep = graphs.pop(id(rep["step"])) if rep["step"] is not None else None
-            fused_choice = {"chosen": rep["chosen"], "ms_per_step": rep["ms"]}
+            def healthy():
+                bad = 0
+                try:
+                    torch.cuda.synchronize()
+                    cuda_ops.check_status()
+                except RuntimeError as e:
+                    print(f"[rank {rank}] fused collectives failed while the step was being tuned: {e!r}", file=sys.stderr, flush=True)
+                    bad = 1
+                flag = torch.tensor([bad], device="cuda")
+                dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+                return int(flag.item()) == 0
+
+            try:
+                rep = fused_tune.pick_fastest(build_combo, torch.device("cuda", local), reps=3,
+                                              release=lambda run: graphs.pop(id(run), None), healthy=healthy)
+                gstep = graphs.pop(id(rep["step"])) if rep["step"] is not None else None
+                graphs.clear()
+                torch.cuda.empty_cache()
+                fused_choice = {"chosen": rep["chosen"], "ms_per_step": rep["ms"]}
+            except fused_tune.CandidateFailed as e:
+                # same decision on every rank (the health check is reduced over the ranks): all collectives through NCCL
+                from state_space_models_neuron_b200.parallel import fused as fused_switch
+                graphs.clear()
+                torch.cuda.empty_cache()
+                fused_switch.set_enabled(False)
+                fused = False
+                fused_fallback = f"{e}; NCCL collectives used"
+                opt.zero_grad()
+                gstep = build_graphed()
         else:
             gstep = build_graphed()
         if gstep is not None:

@@ -17,6 +17,12 @@ import torch.distributed as dist
 
 from . import fused
 
+class CandidateFailed(RuntimeError):
+    """A candidate ran but the caller's health check failed afterwards (e.g. a bounded wait of a fused kernel ran
+    out on some rank).  The symmetric workspace may be inconsistent between ranks then, so the tuner stops instead of
+    trying further candidates; the caller should switch the fused collectives off altogether."""
+
+
 COMBOS: Tuple[Tuple[bool, bool], ...] = ((True, True), (False, True), (True, False), (False, False))
 
 
@@ -48,12 +54,15 @@ def time_steps(run: Callable[[], object], reps: int, device) -> float:
 
 
 def pick_fastest(build: Callable[[], Optional[Callable[[], object]]], device, reps: int = 3,
-                 combos: Sequence[Tuple[bool, bool]] = COMBOS, release: Optional[Callable[[object], None]] = None) -> Dict:
+                 combos: Sequence[Tuple[bool, bool]] = COMBOS, release: Optional[Callable[[object], None]] = None,
+                 healthy: Optional[Callable[[], bool]] = None) -> Dict:
     """`build()` prepares the step under the CURRENT switch settings (e.g. captures it into a CUDA graph) and returns
     a zero-argument callable that runs one step, or None when that combination cannot run.  Each candidate is
     released (`release(step)`, then the caching allocator is emptied) before the next one is built, so only one
     captured step is alive at a time; the winner is built again at the end.  Returns {"chosen": name,
-    "ms": {name: ms per step}, "step": the winner's callable}; the switches are left on the choice."""
+    "ms": {name: ms per step}, "step": the winner's callable}; the switches are left on the choice.  `healthy()`, if
+    given, is called after every candidate's timed calls and must return the same answer on every rank; False raises
+    `CandidateFailed` (after releasing the candidate)."""
     report: Dict = {"ms": {}, "chosen": None, "step": None}
     best = None
     for ag, rs in combos:
@@ -67,12 +76,15 @@ def pick_fastest(build: Callable[[], Optional[Callable[[], object]]], device, re
         step()                                        # one untimed call
         ms = time_steps(step, reps, device)
         report["ms"][name] = round(ms, 3)
-        if best is None or ms < best[0]:
+        ok = healthy() if healthy is not None else True
+        if ok and (best is None or ms < best[0]):
             best = (ms, ag, rs)
         if release is not None:
             release(step)
         del step
         torch.cuda.empty_cache()
+        if not ok:
+            raise CandidateFailed(f"health check failed after the timed steps of {name}")
     if best is None:
         raise RuntimeError("no combination of the fused collective kernels could run")
     _, ag, rs = best

@@ -258,6 +258,13 @@ def test_fused_tuner_picks_the_fastest_combination_and_leaves_it_switched_on(mon
             return None if calls[0] == 1 else build()
         rep = fused_tune.pick_fastest(build_some, "cpu", release=release)
         assert rep["ms"]["ag_gemm=fused,gemm_rs=fused"] is None and rep["chosen"] == "ag_gemm=nccl,gemm_rs=fused"
+        # a failed health check stops the tuner (the candidate is released first)
+        alive[0] = 0
+        released.clear()
+        checks = iter([True, False])
+        with pytest.raises(fused_tune.CandidateFailed):
+            fused_tune.pick_fastest(build, "cpu", release=release, healthy=lambda: next(checks))
+        assert released == list(fused_tune.COMBOS[:2]) and alive[0] == 0
     finally:
         for k, v in before.items():
             fused.set_kernel(k, v)
