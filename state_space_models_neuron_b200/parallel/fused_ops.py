@@ -1,14 +1,19 @@
 """Column-/row-parallel linear layers whose sequence-parallel collective runs inside the GEMM kernel.
 
-    all_gather_linear      y = all_gather_seq(x_shard) W^T     one kernel: the epilogue warps of every CTA push a
-                           slice of the shard into every rank's gather buffer (P2P stores, ready flag per row group)
-                           while the TMA / MMA warps already compute: local rows first, remote rows as they land
-                           backward: dX = reduce_scatter_seq(dY W) (GEMM -> peer landing zones -> in-kernel sum);
-                                     dW += dY^T x_gathered
-    linear_reduce_scatter  y_shard = reduce_scatter_seq(x W^T)  one kernel: the GEMM epilogue TMA-stores every tile
-                           into the owning rank's landing zone; after its tiles every CTA sums a slice of the T
-                           partial blocks that arrived for this rank
-                           backward: dX = all_gather_seq(dY_shard) W (same fused kernel), dW += dY_full^T x
+    all_gather_linear      y = all_gather_seq(x_shard) W^T     one kernel: one thread per CTA moves boxes of the local
+                           shard into every rank's gather buffer (TMA load into the idle epilogue staging buffers,
+                           one TMA store per rank) in up to four column groups with a flag per (source, group), while
+                           the TMA / MMA warps already compute: the local shard first (read in place), a remote
+                           shard's columns as they land
+                           backward: dX = reduce_scatter_seq(dY W) (the kernel below); dW += dY^T x_gathered
+    linear_reduce_scatter  y_shard = reduce_scatter_seq(x W^T)  one kernel: tiles are walked owner by owner, the
+                           epilogue TMA-stores every partial tile into the owning rank's landing slot and reports
+                           the owner as soon as its last tile for it has landed; the sum runs in the same kernel
+                           (two ranks: in the epilogue of the own-row tiles; more: by all CTAs after their tiles)
+                           backward: dX = all_gather_seq(dY_shard) W (the kernel above), dW += dY_full^T x
+
+Either kernel can be switched to "NCCL collective + plain GEMM kernel" (`fused.set_kernel`, `fused_tune.pick_fastest`);
+the autograd functions stay the same.
 
 These replace the pairs (all-gather, GEMM) and (GEMM, reduce-scatter) that the reference leaves to
 neuronx-distributed's ColumnParallelLinear / RowParallelLinear with sequence parallelism
