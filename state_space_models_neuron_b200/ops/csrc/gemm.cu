@@ -1046,6 +1046,24 @@ static double tile_cost_kb(int bn, int pair) {
   return bn == 256 ? 1.00 : 0.80;
 }
 
+// Work distribution of one launch: `units` CTAs (or CTA pairs) take the whole tiles [0, full_tiles) round-robin; the
+// `rem` tiles after them are cut into `split` K slices each, one slice per unit.  With fewer tiles than units all
+// tiles are tail tiles and only the units that get a slice are launched.
+struct Schedule { int units, full_tiles, rem, split; };
+static Schedule plan_schedule(int tiles, int max_units, int kblocks, int mode, int pair, int bn) {
+  Schedule s;
+  s.units = tiles < max_units ? tiles : max_units;
+  s.full_tiles = (tiles / s.units) * s.units;
+  s.rem = tiles - s.full_tiles;
+  s.split = 1;
+  if (gemm_split_enabled() && (s.rem > 0 || tiles < max_units)) {
+    if (tiles < max_units) { s.units = max_units; s.full_tiles = 0; s.rem = tiles; }
+    s.split = tail_split(s.rem, s.units, kblocks, mode, pair, tile_cost_kb(bn, pair), nullptr);
+    if (tiles < max_units) s.units = s.rem * s.split;
+  }
+  return s;
+}
+
 static TileChoice pick_tile(int M, int N, int K, int b_mn, int allow_pair, int mode = 0) {
   const int forced_bn = gemm_forced_bn(), forced_pair = gemm_pair_mode();
   const int sms = g_num_sms > 0 ? g_num_sms : 148;
@@ -1118,23 +1136,19 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
   }
   if (max_units > MAX_UNITS) max_units = MAX_UNITS;
   const int kblocks = (p.K + GEMM_BK - 1) / GEMM_BK;
-  int units = tiles < max_units ? tiles : max_units;
-  p.full_tiles = (tiles / units) * units;
-  p.rem = tiles - p.full_tiles;
-  p.split = 1;
+  Schedule sc = plan_schedule(tiles, max_units, kblocks, p.mode, PAIR ? 1 : 0, BN);
   p.ws = nullptr; p.ws_counters = nullptr;
-  if (gemm_split_enabled() && (p.rem > 0 || tiles < max_units)) {
-    // fewer tiles than units: everything is tail (full_tiles = 0) and the idle units take K slices
-    if (tiles < max_units) { units = max_units; p.full_tiles = 0; p.rem = tiles; }
-    const int split = tail_split(p.rem, units, kblocks, p.mode, PAIR ? 1 : 0, tile_cost_kb(BN, PAIR ? 1 : 0), nullptr);
-    p.split = split;
-    if (split > 1 && p.mode != 2) {
-      Scratch s;
-      if (scratch_for_current_device(&s) != 0) p.split = 1;
-      else { p.ws = s.ws; p.ws_counters = s.counters; }
+  if (sc.split > 1 && p.mode != 2) {             // slices exchange fp32 partial sums through a per-device scratch buffer
+    Scratch s;
+    if (scratch_for_current_device(&s) != 0) {
+      if (tiles < max_units) sc.units = sc.rem;   // no scratch: whole tail tiles, one per unit
+      sc.split = 1;
+    } else {
+      p.ws = s.ws; p.ws_counters = s.counters;
     }
-    if (tiles < max_units) units = p.rem * p.split;          // launch only the units that have work
   }
+  const int units = sc.units;
+  p.full_tiles = sc.full_tiles; p.rem = sc.rem; p.split = sc.split;
   p.units = units;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(units * (PAIR ? 2 : 1)), 1, 1);
@@ -1198,6 +1212,25 @@ extern "C" int ssm_gemm_ce_tiles(int M, int N, int K, int rows_per_shard) {
   }
   const TileChoice c = pick_tile(M, N, K, 0, gemm_pairs_enabled() && rows_per_shard % 256 == 0);
   return (N + c.bn - 1) / c.bn;
+}
+
+// The tiling and work distribution that a plain GEMM of this shape gets, without launching anything (host only; also
+// callable without a GPU, where 148 SMs are assumed): out[8] = {tile width BN, 1 if CTA-pair tiles, tiles along M,
+// tiles along N, units launched, whole tiles in the full waves, tail tiles, K slices per tail tile}.
+// mode as in ssm_gemm_bf16 (2 = accumulate).  For debugging, tests of the schedule and `kernel_bench gemm --plan`.
+extern "C" int ssm_gemm_plan(int M, int N, int K, int mode, int allow_pair, int* out) {
+  using namespace ssm;
+  if (M <= 0 || N <= 0 || K <= 0 || out == nullptr) return -SSM_ERR_BAD_ARG;
+  const int sms = g_num_sms > 0 ? g_num_sms : 148;
+  const TileChoice c = pick_tile(M, N, K, 0, allow_pair && gemm_pairs_enabled(), mode);
+  const int tile_m = c.pair ? 256 : 128;
+  const int tiles_m = (M + tile_m - 1) / tile_m, tiles_n = (N + c.bn - 1) / c.bn;
+  int max_units = c.pair ? sms / 2 : sms;
+  if (max_units > MAX_UNITS) max_units = MAX_UNITS;
+  const Schedule sc = plan_schedule(tiles_m * tiles_n, max_units, (K + GEMM_BK - 1) / GEMM_BK, mode, c.pair, c.bn);
+  out[0] = c.bn; out[1] = c.pair; out[2] = tiles_m; out[3] = tiles_n;
+  out[4] = sc.units; out[5] = sc.full_tiles; out[6] = sc.rem; out[7] = sc.split;
+  return 0;
 }
 
 // bf16 GEMM (mode 0, no bias / activation) whose epilogue also emits cross-entropy statistics of the rows of C:
@@ -1382,12 +1415,13 @@ extern "C" int ssm_gemm_set_options(int pair, int split, int bn) {
   return 0;
 }
 
-// Pipeline analysis: buf = device array of gridDim * 16 uint64 (or null to switch tracing off).  Slots (ns, global
+// Pipeline analysis: buf = device array of gridDim * GEMM_TRACE_SLOTS (24) uint64 (or null to switch tracing off).  Slots (ns, global
 // timer): 0 CTA set-up done, 8 first TMA load issued, 1 first stage landed, 2/3 MMAs of the first / a later tile
 // issued, 4/6 first / later accumulator complete (seen by the epilogue), 5/7 epilogue of that tile done, 9 producer
 // finished, 10 CTA done (after the reduce-scatter tail); collective variants: 11 all-gather push finished, 12 first
 // wait for a remote row group over, 13 reduce-scatter tail: flags of all sources seen, 14 epilogue warps done with
-// their tiles (stores complete, flags published).
+// their tiles (stores complete, flags published); all-gather push thread: 16 first box in shared memory, 17 all boxes
+// issued, 18 own boxes of column group 0 complete, 20 flag of group 0 published (only the CTA that completed the count).
 extern "C" int ssm_gemm_set_trace(void* buf) {
   ssm::g_trace = reinterpret_cast<unsigned long long*>(buf);
   return 0;

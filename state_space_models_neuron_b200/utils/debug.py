@@ -63,6 +63,27 @@ def collective_tile_origin(tile: int, tiles_n: int, tiles_per_block: int, nranks
     return block * tiles_per_block + tm_in, tn
 
 
+def gemm_tile_cost_kb(bn: int, pair: bool) -> float:
+    """Host copy of `tile_cost_kb` in ops/csrc/gemm.cu: cost of one tile per k-block relative to the single-CTA
+    128 x 256 tile."""
+    if pair:
+        return 0.68 if bn == 256 else 0.52
+    return 1.00 if bn == 256 else 0.80
+
+
+def gemm_plan(M: int, N: int, K: int, accumulate: bool = False, allow_pair: bool = True):
+    """What `ssm_gemm_plan` of the native library answers for a plain GEMM of this shape: a dict with the tile width
+    `bn`, `pair`, `tiles_m`, `tiles_n`, `units`, `full_tiles`, `rem`, `split`.  Works without a GPU (148 SMs assumed)."""
+    import ctypes
+    from ..ops import native
+    out = (ctypes.c_int * 8)()
+    code = native.lib().ssm_gemm_plan(int(M), int(N), int(K), 2 if accumulate else 0, int(allow_pair), out)
+    if code != 0:
+        raise ValueError(f"ssm_gemm_plan({M}, {N}, {K}) returned {code}")
+    keys = ("bn", "pair", "tiles_m", "tiles_n", "units", "full_tiles", "rem", "split")
+    return dict(zip(keys, [int(v) for v in out]))
+
+
 def gemm_tail_split(rem: int, units: int, kblocks: int, accumulate: bool = False, pair: bool = False,
                     cost_kb: float = 1.0, always: bool = False) -> int:
     """Host copy of `tail_split` in ops/csrc/gemm.cu: K slices per tail tile.  The split is taken only where the

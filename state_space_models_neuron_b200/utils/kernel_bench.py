@@ -58,6 +58,14 @@ def time_kernel(fn, iters: int, warmup: int = 3, flush: bool = True) -> float:
     return total / iters
 
 
+def plan_gemm(a):
+    """`gemm --plan`: the tiling and work distribution the library picks for this shape (no launch, works without a GPU)."""
+    from . import debug
+    for accumulate in (False, True):
+        print(json.dumps({"kernel": "gemm-plan", "m": a.m, "n": a.n, "k": a.k, "accumulate": accumulate,
+                          **debug.gemm_plan(a.m, a.n, a.k, accumulate=accumulate)}))
+
+
 def bench_gemm(a):
     A = torch.randn(a.m, a.k, device="cuda").bfloat16()
     B = torch.randn(a.n, a.k, device="cuda").bfloat16()
@@ -338,12 +346,15 @@ def main(argv=None):
     ap.add_argument("--group", type=int, default=8192)
     ap.add_argument("--backward", action="store_true")
     ap.add_argument("--trace", action="store_true", help="gemm: print the in-kernel pipeline timeline instead of timing")
+    ap.add_argument("--plan", action="store_true", help="gemm: print the tiling / K-split plan for the shape and exit (no GPU needed)")
     ap.add_argument("--fp32_out", action="store_true", help="gemm --trace: fp32 output (gradient epilogue)")
     ap.add_argument("--trace_dump", default="", help="ag_gemm / gemm_rs --trace: also write rank 0's per-CTA records to this JSON file")
     ap.add_argument("--iters", type=int, default=10)
     a = ap.parse_args(argv)
     if a.kernel in ("ag_gemm", "gemm_rs"):
         return bench_fused(a)
+    if a.kernel == "gemm" and a.plan:
+        return plan_gemm(a)
     if a.kernel == "gemm" and a.trace:
         return trace_gemm(a)
     ms, flops, byts = {"gemm": bench_gemm, "ssd": bench_ssd, "norm": bench_norm, "conv": bench_conv,

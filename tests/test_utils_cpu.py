@@ -268,3 +268,42 @@ def test_fused_tuner_picks_the_fastest_combination_and_leaves_it_switched_on(mon
     finally:
         for k, v in before.items():
             fused.set_kernel(k, v)
+
+
+def test_native_gemm_plan_matches_the_host_model_and_covers_every_tile_once():
+    """The tiling / K-split plan computed by the native library (host code, no GPU needed) agrees with the Python
+    model of the schedule in utils/debug.py, and the resulting work list computes every (tile, k-block) exactly once."""
+    from state_space_models_neuron_b200.ops import native
+    from state_space_models_neuron_b200.utils import debug
+    try:
+        native.lib()
+    except Exception as e:                                   # no nvcc / library on this machine
+        pytest.skip(f"native library not available: {e}")
+    shapes = [(2048, 18560, 4096), (2048, 2320, 4096), (2320, 4096, 2048), (64, 2560, 5120), (2048, 1024, 4096),
+              (18560, 4096, 2048), (2048, 4096, 1024), (128, 128, 64), (300, 6286, 1032), (2048, 50288, 4096),
+              (8192, 8192, 8192), (1, 2560, 5120), (4096, 1024, 2048)]
+    for M, N, K in shapes:
+        for accumulate in (False, True):
+            for allow_pair in (True, False):
+                plan = debug.gemm_plan(M, N, K, accumulate=accumulate, allow_pair=allow_pair)
+                pair = bool(plan["pair"])
+                assert plan["bn"] in (128, 192, 256) and (allow_pair or not pair) and (M > 128 or not pair)
+                tile_m = 256 if pair else 128
+                assert plan["tiles_m"] == -(-M // tile_m) and plan["tiles_n"] == -(-N // plan["bn"])
+                tiles = plan["tiles_m"] * plan["tiles_n"]
+                max_units = 74 if pair else 148
+                kblocks = -(-K // 64)
+                units, work = debug.gemm_schedule(tiles, max_units, kblocks, accumulate=accumulate, pair=pair,
+                                                  cost_kb=debug.gemm_tile_cost_kb(plan["bn"], pair), always_split=False)
+                assert units == plan["units"], (M, N, K, accumulate, allow_pair, plan, units)
+                splits = {w[5] for w in work if w[5] > 1} or {1}
+                assert splits == {plan["split"]}, (M, N, K, plan, splits)
+                assert plan["full_tiles"] + plan["rem"] == tiles and plan["rem"] * plan["split"] <= max(units, 1)
+                # every (tile, k-block) exactly once
+                seen = {}
+                for _, tile, kb0, kb1, sl, ns in work:
+                    assert kb1 > kb0
+                    for kb in range(kb0, kb1):
+                        assert (tile, kb) not in seen
+                        seen[(tile, kb)] = 1
+                assert len(seen) == tiles * kblocks
