@@ -168,3 +168,36 @@ def tile_schedule_is_permutation(tiles_m: int, tiles_n: int, nranks: int, ctas: 
             if any(tm // per != first for tile, (tm, tn) in seen if tile < per * tiles_n):
                 return False
     return True
+
+
+def ag_push_plan(rows_per_shard: int, K: int, n_sms: int = 148, max_groups: int = 4):
+    """Host copy of how the all-gather GEMM cuts the local shard into push boxes (ops/csrc/gemm.cu, host side):
+    box height 128, halved down to 32 while there are fewer than 3 boxes per SM; up to `max_groups` column groups of
+    whole 64-column blocks.  Returns (push_rows, col_blocks, group_kb, ngroups, staging slots per CTA)."""
+    col_blocks = -(-K // 64)
+    push_rows = 128
+    while push_rows > 32 and (rows_per_shard // push_rows) * col_blocks < 3 * n_sms:
+        push_rows //= 2
+    group_kb = -(-col_blocks // max_groups)
+    ngroups = -(-col_blocks // group_kb)
+    nslots = (2 * 128 * 64 * 2) // (push_rows * 128)
+    return push_rows, col_blocks, group_kb, ngroups, nslots
+
+
+def ag_push_boxes(grid: int, rows_per_shard: int, push_rows: int, col_blocks: int, group_kb: int):
+    """Host copy of the dealing of push boxes over the CTAs of the grid (the push loop of `gemm_bf16_tcgen05`):
+    returns per CTA the list of (group, first row, first column) it moves, in issue order.  Groups are dealt
+    round-robin, each group continuing where the previous one stopped."""
+    row_blocks = rows_per_shard // push_rows
+    ngroups = -(-col_blocks // group_kb)
+    per_cta = [[] for _ in range(grid)]
+    for cta in range(grid):
+        dealt = 0
+        for g in range(ngroups):
+            cols_g = min(group_kb, col_blocks - g * group_kb)
+            boxes_g = cols_g * row_blocks
+            start = (cta - dealt % grid + grid) % grid
+            dealt += boxes_g
+            for b in range(start, boxes_g, grid):
+                per_cta[cta].append((g, (b // cols_g) * push_rows, (g * group_kb + b % cols_g) * 64))
+    return per_cta

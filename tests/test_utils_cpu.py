@@ -307,3 +307,27 @@ def test_native_gemm_plan_matches_the_host_model_and_covers_every_tile_once():
                         assert (tile, kb) not in seen
                         seen[(tile, kb)] = 1
                 assert len(seen) == tiles * kblocks
+
+
+def test_all_gather_push_boxes_cover_the_shard_once_and_evenly():
+    """Model of the shard push of the all-gather GEMM: for the shard sizes of TP = 2, 4, 8 (and odd widths) every
+    64-column x push_rows box is moved by exactly one CTA, groups go out in column order, and no CTA moves more than
+    one box more than another."""
+    from state_space_models_neuron_b200.utils import debug
+    for rows, K, grid in [(1024, 4096, 148), (512, 4096, 148), (256, 4096, 148), (256, 4096, 74), (128, 520, 148),
+                          (2048, 1032, 148), (256, 8192, 148), (128, 64, 16)]:
+        push_rows, col_blocks, group_kb, ngroups, nslots = debug.ag_push_plan(rows, K)
+        assert push_rows in (32, 64, 128) and rows % push_rows == 0 and 1 <= ngroups <= 4 and nslots in (2, 4, 8)
+        per_cta = debug.ag_push_boxes(grid, rows, push_rows, col_blocks, group_kb)
+        seen = {}
+        for boxes in per_cta:
+            assert [b[0] for b in boxes] == sorted(b[0] for b in boxes)          # group by group
+            for g, row, col in boxes:
+                assert (row, col) not in seen and col // 64 // group_kb == g and row < rows and col < col_blocks * 64
+                seen[(row, col)] = g
+        assert len(seen) == (rows // push_rows) * col_blocks
+        counts = [len(b) for b in per_cta]
+        assert max(counts) - min(counts) <= 1
+    # the sizes the model step uses: 32-row boxes and eight staging slots at TP=8, one box per CTA and group
+    assert debug.ag_push_plan(256, 4096)[0] == 32 and debug.ag_push_plan(256, 4096)[4] == 8
+    assert debug.ag_push_plan(512, 4096)[0] == 64 and debug.ag_push_plan(1024, 4096)[0] == 128
