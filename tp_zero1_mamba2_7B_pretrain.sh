@@ -37,6 +37,8 @@ DP=$((WORLD / TP_DEGREE))
 ACC_STEPS=$((GBS / MBS / DP))
 # CUDA graphs: every micro-step (forward + backward + fused collectives) and the optimizer update replay as captured
 # graphs, which takes the host out of the loop (thousands of launches per micro-step); CUDA_GRAPH=0 runs eagerly.
+# SSM_B200_FUSED_AG=0 / SSM_B200_FUSED_RS=0 (environment) run the all-gather GEMM / the reduce-scatter GEMM as NCCL
+# collective + plain GEMM kernel; `python bench.py --gpus N` prints the step time of all four combinations on this machine.
 GRAPH_FLAG=""
 if [ "${CUDA_GRAPH:-1}" != "0" ]; then GRAPH_FLAG="--cuda_graph"; fi
 echo "world=$WORLD tp=$TP_DEGREE dp=$DP acc_steps=$ACC_STEPS cuda_graph=${CUDA_GRAPH:-1}"
