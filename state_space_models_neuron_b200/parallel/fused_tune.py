@@ -39,18 +39,29 @@ def _max_over_ranks(ms: float, device) -> float:
 
 
 def time_steps(run: Callable[[], object], reps: int, device) -> float:
-    """Device milliseconds per call of `run` (CUDA events on the current stream, max over ranks)."""
-    torch.cuda.synchronize(device)
-    if dist.is_initialized() and dist.get_world_size() > 1:
+    """Milliseconds per call of `run`, max over ranks: CUDA events on the current stream for a CUDA device, the host
+    clock otherwise (gloo ranks on CPU)."""
+    import time
+    dev = torch.device(device)
+    multi = dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1
+    if dev.type != "cuda":
+        if multi:
+            dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            run()
+        return _max_over_ranks((time.perf_counter() - t0) * 1e3 / reps, dev)
+    torch.cuda.synchronize(dev)
+    if multi:
         dist.barrier()
-        torch.cuda.synchronize(device)
+        torch.cuda.synchronize(dev)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(reps):
         run()
     e1.record()
-    torch.cuda.synchronize(device)
-    return _max_over_ranks(e0.elapsed_time(e1) / reps, device)
+    torch.cuda.synchronize(dev)
+    return _max_over_ranks(e0.elapsed_time(e1) / reps, dev)
 
 
 def pick_fastest(build: Callable[[], Optional[Callable[[], object]]], device, reps: int = 3,
@@ -82,7 +93,8 @@ def pick_fastest(build: Callable[[], Optional[Callable[[], object]]], device, re
         if release is not None:
             release(step)
         del step
-        torch.cuda.empty_cache()
+        if torch.cuda.is_available():
+            torch.cuda.empty_cache()
         if not ok:
             raise CandidateFailed(f"health check failed after the timed steps of {name}")
     if best is None:

@@ -178,3 +178,29 @@ def _gqa_qkv_worker(rank, world):
 
 def test_gqa_qkv_linear_kv_replication():
     run_ranks(_gqa_qkv_worker, 2)
+
+
+def _tuner_agreement_worker(rank, world):
+    """Two ranks whose local timings prefer different combinations must end up with the same choice: the times are
+    reduced with MAX over the ranks before they are compared."""
+    import time
+    from state_space_models_neuron_b200.parallel import fused, fused_tune
+    # milliseconds per step on (rank 0, rank 1): rank 0 alone would pick the first combination, rank 1 the last one;
+    # the slowest rank decides: max = 40, 25, 30, 45 -> the second combination
+    cost = {(True, True): (5, 40), (False, True): (25, 20), (True, False): (30, 30), (False, False): (45, 3)}
+
+    def build():
+        key = (fused.kernel_enabled("ag_gemm"), fused.kernel_enabled("gemm_rs"))
+        step = lambda: time.sleep(cost[key][rank] / 1e3)
+        step.key = key
+        return step
+
+    rep = fused_tune.pick_fastest(build, "cpu", reps=3)
+    assert rep["chosen"] == "ag_gemm=nccl,gemm_rs=fused", rep
+    assert fused.kernels() == {"ag_gemm": False, "gemm_rs": True}
+    ms = rep["ms"]
+    assert ms["ag_gemm=fused,gemm_rs=fused"] >= 39 and ms["ag_gemm=nccl,gemm_rs=nccl"] >= 44 and ms["ag_gemm=nccl,gemm_rs=fused"] < 39
+
+
+def test_fused_tuner_ranks_agree_on_the_slowest_ranks_time():
+    run_ranks(_tuner_agreement_worker, 2)
